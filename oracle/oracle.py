@@ -1,0 +1,108 @@
+"""ctypes front-end of the CPU oracle (test infrastructure only).
+
+The oracle restates pySigLib's CPU arithmetic for ``sig`` and ``sig_backprop``
+(see ``sig_oracle_impl.h`` for the reference file:line map).  Only the test
+suite, the smoke check and the benchmark's CPU-baseline leg import this module.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "libsig_oracle.so")
+_LIB = None
+
+
+def build(force=False):
+    """Compile the oracle with gcc (idempotent)."""
+    src = [os.path.join(_HERE, f) for f in ("sig_oracle.c", "sig_oracle_impl.h")]
+    if (not force and os.path.exists(_LIB_PATH)
+            and all(os.path.getmtime(_LIB_PATH) >= os.path.getmtime(s) for s in src)):
+        return _LIB_PATH
+    subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+def _lib():
+    global _LIB
+    if _LIB is None:
+        build()
+        lib = ctypes.CDLL(_LIB_PATH)
+        u64 = ctypes.c_uint64
+        for suf, real in (("f", ctypes.c_float), ("d", ctypes.c_double)):
+            ptr = ctypes.POINTER(real)
+            fwd = getattr(lib, "oracle_signature_" + suf)
+            fwd.restype = ctypes.c_int
+            fwd.argtypes = [ptr, ptr, u64, u64, u64, u64, ctypes.c_int, ctypes.c_int, real,
+                            ctypes.c_int, ctypes.c_int, ctypes.c_int]
+            bwd = getattr(lib, "oracle_sig_backprop_" + suf)
+            bwd.restype = ctypes.c_int
+            bwd.argtypes = [ptr, ptr, ptr, ptr, u64, u64, u64, u64, ctypes.c_int, ctypes.c_int,
+                            real, ctypes.c_int, ctypes.c_int]
+        lib.oracle_sig_length.restype = u64
+        lib.oracle_sig_length.argtypes = [u64, u64]
+        _LIB = lib
+    return _LIB
+
+
+def _suffix(arr):
+    if arr.dtype == np.float32:
+        return "f", ctypes.c_float
+    if arr.dtype == np.float64:
+        return "d", ctypes.c_double
+    raise TypeError("oracle supports float32 / float64 only")
+
+
+def aug_dim(d, time_aug, lead_lag):
+    return (2 * d if lead_lag else d) + (1 if time_aug else 0)
+
+
+def sig_length(dim, degree, scalar_term=False):
+    n = _lib().oracle_sig_length(dim, degree)
+    return n - (0 if scalar_term else 1)
+
+
+def sig(path, degree, *, time_aug=False, lead_lag=False, end_time=1.0, horner=True,
+        scalar_term=False, n_threads=1):
+    """Oracle signature of ``path`` (B, L, d) or (L, d); numpy in, numpy out."""
+    path = np.ascontiguousarray(path)
+    single = path.ndim == 2
+    p3 = path[None] if single else path
+    B, L, d = p3.shape
+    suf, real = _suffix(p3)
+    n = sig_length(aug_dim(d, time_aug, lead_lag), degree, scalar_term)
+    out = np.empty((B, n), dtype=p3.dtype)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_signature_" + suf)(
+        p3.ctypes.data_as(ptr), out.ctypes.data_as(ptr), B, d, L, degree,
+        int(time_aug), int(lead_lag), real(end_time), int(horner), int(scalar_term), int(n_threads))
+    if rc:
+        raise RuntimeError("oracle_signature failed with code %d" % rc)
+    return out[0] if single else out
+
+
+def sig_backprop(path, sig_, sig_derivs, degree, *, time_aug=False, lead_lag=False,
+                 end_time=1.0, n_threads=1):
+    """Oracle gradient of sum(sig * sig_derivs) w.r.t. ``path``; scalar-term format inferred."""
+    path = np.ascontiguousarray(path)
+    single = path.ndim == 2
+    p3 = path[None] if single else path
+    B, L, d = p3.shape
+    suf, real = _suffix(p3)
+    full = sig_length(aug_dim(d, time_aug, lead_lag), degree, True)
+    s2 = np.ascontiguousarray(sig_, dtype=p3.dtype).reshape(B, -1)
+    g2 = np.ascontiguousarray(sig_derivs, dtype=p3.dtype).reshape(B, -1)
+    if s2.shape[1] not in (full, full - 1) or g2.shape != s2.shape:
+        raise ValueError("sig / sig_derivs have the wrong length")
+    scalar_term = s2.shape[1] == full
+    out = np.empty_like(p3)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_sig_backprop_" + suf)(
+        p3.ctypes.data_as(ptr), out.ctypes.data_as(ptr), g2.ctypes.data_as(ptr),
+        s2.ctypes.data_as(ptr), B, d, L, degree, int(time_aug), int(lead_lag), real(end_time),
+        int(scalar_term), int(n_threads))
+    if rc:
+        raise RuntimeError("oracle_sig_backprop failed with code %d" % rc)
+    return out[0] if single else out

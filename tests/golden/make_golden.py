@@ -1,0 +1,32 @@
+"""Extract the hot-path golden vectors of the reference's test fixture.
+
+Source: the reference's ``tests/fixtures/reference_data.npz`` (generated there by
+iisignature, see the reference's ``tests/fixtures/generate_fixtures_iisig.py:47-82``
+and consumed by its ``tests/test_signature.py:32-110`` and
+``tests/test_sig_backprop.py:69-98``).  Only the keys that pin ``sig`` and
+``sig_backprop`` are kept; the file written here is what the tests read, so the
+suite does not need the reference tree at run time.
+
+Usage (only where the reference tree is mounted):
+    python tests/golden/make_golden.py /path/to/reference
+"""
+import os
+import sys
+
+import numpy as np
+
+KEEP_PREFIXES = ("path", "sig__d", "sig_ta__d", "sig_ll__d", "sig_ta_ll__d",
+                 "sig_bp_derivs__d", "sig_bp_expected__d")
+
+
+def main(reference_root):
+    src = os.path.join(reference_root, "tests", "fixtures", "reference_data.npz")
+    data = np.load(src)
+    keep = {k: data[k] for k in data.files if k.startswith(KEEP_PREFIXES)}
+    dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_sig_vectors.npz")
+    np.savez_compressed(dst, **keep)
+    print("wrote", dst, "with", len(keep), "arrays,", sum(v.nbytes for v in keep.values()), "bytes")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
