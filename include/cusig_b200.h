@@ -1,0 +1,134 @@
+/*
+ * C ABI of libcusig.so, the sm_100a (B200) implementation of pySigLib's batched
+ * truncated path signature and its backward pass.
+ *
+ * Every function returns 0 on success, or: 1 allocation failure, 2 invalid
+ * argument, 3 out of range, 10 runtime error, 11 unknown, 100000 + cudaError_t
+ * for CUDA failures.  A description of the last failure on the calling thread is
+ * returned by cusig_last_error_message().
+ *
+ * Buffers are caller-owned, contiguous and row-major:
+ *   path        (batch, length, dimension)
+ *   out / sig / sig_derivs  (batch, S)  with S = sum_{k=1..degree} d'^k (+1 when
+ *               scalar_term), d' = (lead_lag ? 2*dimension : dimension) + (time_aug ? 1 : 0)
+ * Pointers are either all device pointers (work runs on the device that owns
+ * them) or all host pointers (the library stages the batch through the current
+ * device in overlapped chunks and returns the result in host memory).
+ */
+#ifndef CUSIG_B200_H_
+#define CUSIG_B200_H_
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* --- symbols with the reference's names and signatures ------------------------------- */
+
+/* Truncated signature of a batch of paths.
+ * Replaces: siglib/cusig/cusig.h:312-314 (declaration),
+ *           siglib/cusig/cu_signature.cu:3497-3517 (definition); bound by
+ *           pysiglib/load_siglib.py:484-488.
+ * `horner` is accepted for compatibility; both settings run the Horner kernels.
+ * A non-empty `correction` is rejected with code 2.  Synchronous. */
+int signature_cuda_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
+                     uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, float end_time,
+                     bool horner, bool scalar_term, const float* correction, uint64_t correction_len,
+                     uint64_t correction_batch_stride, uint64_t correction_segment_stride);
+int signature_cuda_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension,
+                     uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, double end_time,
+                     bool horner, bool scalar_term, const double* correction, uint64_t correction_len,
+                     uint64_t correction_batch_stride, uint64_t correction_segment_stride);
+
+/* Gradient of a scalar loss with respect to the path, given dLoss/dSignature.
+ * Replaces: siglib/cusig/cusig.h:342-344, siglib/cusig/cu_signature.cu:3524-3544; bound by
+ *           pysiglib/load_siglib.py:490-494.  Note the order: sig_derivs before sig.
+ * `out` has the shape of `path`.  Synchronous. */
+int sig_backprop_cuda_f(const float* path, float* out, const float* sig_derivs, const float* sig,
+                        uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                        bool time_aug, bool lead_lag, float end_time, bool scalar_term,
+                        const float* correction, uint64_t correction_len,
+                        uint64_t correction_batch_stride, uint64_t correction_segment_stride);
+int sig_backprop_cuda_d(const double* path, double* out, const double* sig_derivs, const double* sig,
+                        uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                        bool time_aug, bool lead_lag, double end_time, bool scalar_term,
+                        const double* correction, uint64_t correction_len,
+                        uint64_t correction_batch_stride, uint64_t correction_segment_stride);
+
+/* Thread-local text of the last error; valid until the next call on this thread.
+ * Replaces: siglib/cusig/cusig.h:43; bound by pysiglib/load_siglib.py:108-110. */
+const char* cusig_last_error_message(void);
+
+/* Releases streams and cached device memory on every device.
+ * Replaces: siglib/cusig/cusig.h:1028 (siglib/cusig/cache_lifecycle/cusig_lifecycle.cu:35-50). */
+void cusig_shutdown(void);
+
+/* --- extensions used by this repository's Python layer and benchmark ------------------ */
+
+/* As signature_cuda_* on an explicit stream (a cudaStream_t passed as void*).
+ * synchronize = 0 returns as soon as the work is enqueued (device pointers only).
+ * nonfinite: optional host int set to 1 when the output holds NaN or Inf (forces a
+ * synchronisation); replaces the two isnan/isinf passes of pysiglib/sig.py:299-302.
+ * The reference has no stream argument (siglib/cusig/cu_runtime_utils.h:53-56 synchronises
+ * the whole device after every call). */
+int sigb200_signature_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
+                        uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, float end_time,
+                        bool scalar_term, void* stream, int synchronize, int* nonfinite);
+int sigb200_signature_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension,
+                        uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, double end_time,
+                        bool scalar_term, void* stream, int synchronize, int* nonfinite);
+int sigb200_sig_backprop_f(const float* path, float* out, const float* sig_derivs, const float* sig,
+                           uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                           bool time_aug, bool lead_lag, float end_time, bool scalar_term, void* stream,
+                           int synchronize);
+int sigb200_sig_backprop_d(const double* path, double* out, const double* sig_derivs, const double* sig,
+                           uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                           bool time_aug, bool lead_lag, double end_time, bool scalar_term, void* stream,
+                           int synchronize);
+
+/* Single-box batch partitioner: host buffers, the batch cut into contiguous shards over
+ * `n_devices` GPUs (device ordinals in `devices`, or 0..n_devices-1 when NULL), one host
+ * thread and one stream set per device, no communication between devices.
+ * No counterpart in the reference (it is single-device). */
+int sigb200_signature_sharded_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
+                                uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
+                                float end_time, bool scalar_term, const int* devices, int n_devices);
+int sigb200_signature_sharded_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension,
+                                uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
+                                double end_time, bool scalar_term, const int* devices, int n_devices);
+int sigb200_sig_backprop_sharded_f(const float* path, float* out, const float* sig_derivs, const float* sig,
+                                   uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                                   bool time_aug, bool lead_lag, float end_time, bool scalar_term,
+                                   const int* devices, int n_devices);
+int sigb200_sig_backprop_sharded_d(const double* path, double* out, const double* sig_derivs, const double* sig,
+                                   uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                                   bool time_aug, bool lead_lag, double end_time, bool scalar_term,
+                                   const int* devices, int n_devices);
+
+/* Number of coefficients of a signature, scalar term included; 0 on overflow.
+ * Same contract as the CPU library's sig_length (siglib/cpsig/cp_utils.cpp:91-105). */
+uint64_t sigb200_sig_length(uint64_t dimension, uint64_t degree);
+
+/* 0 = automatic kernel choice (default), 1 = shape-generic kernels only. */
+void sigb200_set_kernel_policy(int policy);
+
+/* Name of the kernel family the forward (backward = 1) pass would use for this shape:
+ * "trivial", "tile", "generic".  Static string. */
+const char* sigb200_kernel_family(uint64_t dimension, uint64_t degree, bool time_aug, bool lead_lag,
+                                  int is_double, int backward);
+
+/* FMA-pipe peak probe for the benchmark: `blocks` CTAs x 256 threads x iters x 64 independent
+ * register-resident FMAs in float (is_double = 0) or double; `sink` is any 8-byte device
+ * buffer.  Asynchronous on `stream`.  No counterpart in the reference. */
+int sigb200_fma_peak(int is_double, void* sink, int blocks, int iters, void* stream);
+
+/* Number of kernels this library has launched in the calling process (all threads). */
+uint64_t sigb200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CUSIG_B200_H_ */

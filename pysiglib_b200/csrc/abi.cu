@@ -1,0 +1,268 @@
+// extern "C" surface of libcusig.so (declared in include/cusig_b200.h).
+//
+// The four compute symbols, cusig_last_error_message and cusig_shutdown keep the
+// reference's names and signatures (siglib/cusig/cusig.h:43,312-314,342-344,1028)
+// so that pysiglib/load_siglib.py:76-130,484-494 can load this library unchanged.
+// Every other symbol that loader resolves at import time is exported as a stub
+// that fails with code 10, so the import succeeds and only this path is served.
+#include <cstdint>
+#include <thread>
+#include <vector>
+
+#include "../../include/cusig_b200.h"
+#include "dispatch.h"
+#include "kernels.h"
+#include "runtime.h"
+
+using namespace sigb200;
+
+namespace {
+
+CallOptions sync_options() { return CallOptions{}; }
+
+CallOptions stream_options(void* stream, int synchronize, int* nonfinite) {
+    CallOptions o;
+    o.stream = static_cast<cudaStream_t>(stream);
+    o.synchronize = synchronize != 0;
+    o.nonfinite = nonfinite;
+    return o;
+}
+
+// Contiguous shards, remainder to the first shards (the reference's thread split,
+// siglib/cpsig/multithreading.cpp:66-78, applied to devices).
+struct Shard { uint64_t begin, count; int device; };
+
+std::vector<Shard> make_shards(uint64_t batch, const int* devices, int n_devices) {
+    if (n_devices <= 0) throw std::invalid_argument("n_devices must be positive");
+    const int available = device_count();
+    std::vector<Shard> shards;
+    const uint64_t n = std::min<uint64_t>(uint64_t(n_devices), std::max<uint64_t>(batch, 1));
+    const uint64_t chunk = batch / n, rem = batch % n;
+    for (uint64_t g = 0; g < n; ++g) {
+        const int dev = devices ? devices[g] : int(g);
+        if (dev < 0 || dev >= available)
+            throw std::invalid_argument("device ordinal " + std::to_string(dev) + " is not available");
+        const uint64_t begin = g * chunk + std::min(g, rem);
+        shards.push_back({begin, chunk + (g < rem ? 1 : 0), dev});
+    }
+    return shards;
+}
+
+// Runs fn(shard) on one host thread per shard; the first failure (lowest shard) is rethrown.
+template <typename Fn>
+void run_sharded(const std::vector<Shard>& shards, Fn&& fn) {
+    std::vector<std::exception_ptr> errors(shards.size());
+    std::vector<std::thread> threads;
+    for (size_t i = 1; i < shards.size(); ++i)
+        threads.emplace_back([&, i] {
+            try { fn(shards[i]); } catch (...) { errors[i] = std::current_exception(); }
+        });
+    try { fn(shards[0]); } catch (...) { errors[0] = std::current_exception(); }
+    for (auto& t : threads) t.join();
+    for (auto& e : errors) if (e) std::rethrow_exception(e);
+}
+
+template <typename T>
+void signature_sharded(const T* path, T* out, uint64_t batch, uint64_t d, uint64_t L, uint64_t degree,
+                       bool time_aug, bool lead_lag, T end_time, bool scalar_term, const int* devices,
+                       int n_devices) {
+    if (d == 0) throw std::invalid_argument("signature_cuda received path of dimension 0");
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, d, L, degree, time_aug, lead_lag, scalar_term);
+    if (classify_pointer(out).on_device || classify_pointer(path).on_device)
+        throw std::invalid_argument("the sharded entry points take host buffers");
+    run_sharded(make_shards(batch, devices, n_devices), [&](const Shard& sh) {
+        if (sh.count == 0) return;
+        CallOptions o;
+        o.device = sh.device;
+        signature_entry<T>(path + sh.begin * L * d, out + sh.begin * s.stride, sh.count, d, L, degree, time_aug,
+                           lead_lag, end_time, true, scalar_term, nullptr, 0, o);
+    });
+}
+
+template <typename T>
+void sig_backprop_sharded(const T* path, T* out, const T* sig_derivs, const T* sig, uint64_t batch, uint64_t d,
+                          uint64_t L, uint64_t degree, bool time_aug, bool lead_lag, T end_time,
+                          bool scalar_term, const int* devices, int n_devices) {
+    if (d == 0) throw std::invalid_argument("sig_backprop_cuda received path of dimension 0");
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, d, L, degree, time_aug, lead_lag, scalar_term);
+    if (classify_pointer(out).on_device || classify_pointer(path).on_device)
+        throw std::invalid_argument("the sharded entry points take host buffers");
+    run_sharded(make_shards(batch, devices, n_devices), [&](const Shard& sh) {
+        if (sh.count == 0) return;
+        CallOptions o;
+        o.device = sh.device;
+        sig_backprop_entry<T>(path + sh.begin * L * d, out + sh.begin * L * d,
+                              sig_derivs ? sig_derivs + sh.begin * s.stride : nullptr,
+                              sig ? sig + sh.begin * s.stride : nullptr, sh.count, d, L, degree, time_aug,
+                              lead_lag, end_time, scalar_term, nullptr, 0, o);
+    });
+}
+
+int stub_not_built(const char* name) noexcept {
+    clear_last_error();
+    std::string msg = std::string(name) +
+        " is not part of this build of libcusig (only signature_cuda_* and sig_backprop_cuda_* are served)";
+    set_last_error(msg.c_str());
+    return 10;
+}
+
+}  // namespace
+
+#define SIG_API extern "C" __attribute__((visibility("default")))
+
+SIG_API int signature_cuda_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
+                             uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, float end_time,
+                             bool horner, bool scalar_term, const float* correction, uint64_t correction_len,
+                             uint64_t, uint64_t) {
+    SIG_SAFE_CALL(signature_entry<float>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag,
+                                         end_time, horner, scalar_term, correction, correction_len, sync_options()));
+}
+
+SIG_API int signature_cuda_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension,
+                             uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, double end_time,
+                             bool horner, bool scalar_term, const double* correction, uint64_t correction_len,
+                             uint64_t, uint64_t) {
+    SIG_SAFE_CALL(signature_entry<double>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag,
+                                          end_time, horner, scalar_term, correction, correction_len, sync_options()));
+}
+
+SIG_API int sig_backprop_cuda_f(const float* path, float* out, const float* sig_derivs, const float* sig,
+                                uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                                bool time_aug, bool lead_lag, float end_time, bool scalar_term,
+                                const float* correction, uint64_t correction_len, uint64_t, uint64_t) {
+    SIG_SAFE_CALL(sig_backprop_entry<float>(path, out, sig_derivs, sig, batch_size, dimension, length, degree,
+                                            time_aug, lead_lag, end_time, scalar_term, correction, correction_len,
+                                            sync_options()));
+}
+
+SIG_API int sig_backprop_cuda_d(const double* path, double* out, const double* sig_derivs, const double* sig,
+                                uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                                bool time_aug, bool lead_lag, double end_time, bool scalar_term,
+                                const double* correction, uint64_t correction_len, uint64_t, uint64_t) {
+    SIG_SAFE_CALL(sig_backprop_entry<double>(path, out, sig_derivs, sig, batch_size, dimension, length, degree,
+                                             time_aug, lead_lag, end_time, scalar_term, correction, correction_len,
+                                             sync_options()));
+}
+
+SIG_API const char* cusig_last_error_message(void) { return last_error(); }
+
+SIG_API void cusig_shutdown(void) { shutdown_runtime(); }
+
+SIG_API int sigb200_signature_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
+                                uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, float end_time,
+                                bool scalar_term, void* stream, int synchronize, int* nonfinite) {
+    SIG_SAFE_CALL(signature_entry<float>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag,
+                                         end_time, true, scalar_term, nullptr, 0,
+                                         stream_options(stream, synchronize, nonfinite)));
+}
+
+SIG_API int sigb200_signature_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension,
+                                uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, double end_time,
+                                bool scalar_term, void* stream, int synchronize, int* nonfinite) {
+    SIG_SAFE_CALL(signature_entry<double>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag,
+                                          end_time, true, scalar_term, nullptr, 0,
+                                          stream_options(stream, synchronize, nonfinite)));
+}
+
+SIG_API int sigb200_sig_backprop_f(const float* path, float* out, const float* sig_derivs, const float* sig,
+                                   uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                                   bool time_aug, bool lead_lag, float end_time, bool scalar_term, void* stream,
+                                   int synchronize) {
+    SIG_SAFE_CALL(sig_backprop_entry<float>(path, out, sig_derivs, sig, batch_size, dimension, length, degree,
+                                            time_aug, lead_lag, end_time, scalar_term, nullptr, 0,
+                                            stream_options(stream, synchronize, nullptr)));
+}
+
+SIG_API int sigb200_sig_backprop_d(const double* path, double* out, const double* sig_derivs, const double* sig,
+                                   uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                                   bool time_aug, bool lead_lag, double end_time, bool scalar_term, void* stream,
+                                   int synchronize) {
+    SIG_SAFE_CALL(sig_backprop_entry<double>(path, out, sig_derivs, sig, batch_size, dimension, length, degree,
+                                             time_aug, lead_lag, end_time, scalar_term, nullptr, 0,
+                                             stream_options(stream, synchronize, nullptr)));
+}
+
+SIG_API int sigb200_signature_sharded_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
+                                        uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
+                                        float end_time, bool scalar_term, const int* devices, int n_devices) {
+    SIG_SAFE_CALL(signature_sharded<float>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag,
+                                           end_time, scalar_term, devices, n_devices));
+}
+
+SIG_API int sigb200_signature_sharded_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension,
+                                        uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
+                                        double end_time, bool scalar_term, const int* devices, int n_devices) {
+    SIG_SAFE_CALL(signature_sharded<double>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag,
+                                            end_time, scalar_term, devices, n_devices));
+}
+
+SIG_API int sigb200_sig_backprop_sharded_f(const float* path, float* out, const float* sig_derivs,
+                                           const float* sig, uint64_t batch_size, uint64_t dimension,
+                                           uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
+                                           float end_time, bool scalar_term, const int* devices, int n_devices) {
+    SIG_SAFE_CALL(sig_backprop_sharded<float>(path, out, sig_derivs, sig, batch_size, dimension, length, degree,
+                                              time_aug, lead_lag, end_time, scalar_term, devices, n_devices));
+}
+
+SIG_API int sigb200_sig_backprop_sharded_d(const double* path, double* out, const double* sig_derivs,
+                                           const double* sig, uint64_t batch_size, uint64_t dimension,
+                                           uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
+                                           double end_time, bool scalar_term, const int* devices, int n_devices) {
+    SIG_SAFE_CALL(sig_backprop_sharded<double>(path, out, sig_derivs, sig, batch_size, dimension, length, degree,
+                                               time_aug, lead_lag, end_time, scalar_term, devices, n_devices));
+}
+
+SIG_API uint64_t sigb200_sig_length(uint64_t dimension, uint64_t degree) {
+    try { return sig_length_full(dimension, degree); } catch (...) { return 0; }
+}
+
+SIG_API void sigb200_set_kernel_policy(int policy) { set_kernel_policy(policy); }
+
+SIG_API const char* sigb200_kernel_family(uint64_t dimension, uint64_t degree, bool time_aug, bool lead_lag,
+                                          int is_double, int backward) {
+    try {
+        const SigShape s = make_shape(1, dimension, 2, degree, time_aug, lead_lag, false);
+        if (!backward && (degree <= 1 || s.dim == 1)) return "trivial";
+        if (backward && degree == 0) return "trivial";
+        if (kernel_policy() != 0) return "generic";
+        bool tile;
+        if (backward) tile = is_double ? tile_backward_available<double>(s) : tile_backward_available<float>(s);
+        else tile = is_double ? tile_forward_available<double>(s) : tile_forward_available<float>(s);
+        return tile ? "tile" : "generic";
+    } catch (...) {
+        return "invalid";
+    }
+}
+
+SIG_API uint64_t sigb200_launch_count(void) { return launch_count(); }
+
+// ---- stubs for the rest of the reference's CUDA surface (pysiglib/load_siglib.py:165-183,420-641) ----
+
+#define SIG_STUB(name) SIG_API int name(...) { return stub_not_built(#name); }
+#define SIG_STUB_PAIR(name) SIG_STUB(name##_f) SIG_STUB(name##_d)
+
+SIG_STUB_PAIR(transform_path_cuda) SIG_STUB_PAIR(transform_path_backprop_cuda)
+SIG_STUB_PAIR(log_sig_combine_cuda) SIG_STUB_PAIR(log_sig_combine_backprop_cuda)
+SIG_STUB_PAIR(log_sig_from_path_cuda) SIG_STUB_PAIR(log_sig_from_path_backprop_cuda)
+SIG_STUB_PAIR(log_sig_join_cuda) SIG_STUB_PAIR(log_sig_join_backprop_cuda)
+SIG_STUB_PAIR(logsig_to_sig_cuda) SIG_STUB_PAIR(logsig_to_sig_backprop_cuda)
+SIG_STUB_PAIR(sig_combine_cuda) SIG_STUB_PAIR(sig_combine_backprop_cuda)
+SIG_STUB_PAIR(sig_join_cuda) SIG_STUB_PAIR(sig_join_backprop_cuda)
+SIG_STUB_PAIR(sig_coef_cuda) SIG_STUB_PAIR(sig_coef_backprop_cuda)
+SIG_STUB_PAIR(sig_to_log_sig_cuda) SIG_STUB_PAIR(sig_to_log_sig_backprop_cuda)
+SIG_STUB_PAIR(sig_kernel_cuda) SIG_STUB_PAIR(sig_kernel_backprop_cuda)
+SIG_STUB_PAIR(sig_kernel_poly_cuda) SIG_STUB_PAIR(sig_kernel_poly_backprop_cuda)
+SIG_STUB_PAIR(linear_sig_cuda)
+SIG_STUB_PAIR(branched_sig_cuda) SIG_STUB_PAIR(branched_sig_backprop_cuda)
+SIG_STUB_PAIR(branched_sig_coef_cuda) SIG_STUB_PAIR(branched_sig_coef_backprop_cuda)
+SIG_STUB_PAIR(branched_sig_combine_cuda) SIG_STUB_PAIR(branched_sig_combine_backprop_cuda)
+SIG_STUB_PAIR(branched_sig_kernel_cuda) SIG_STUB_PAIR(branched_sig_kernel_backprop_cuda)
+SIG_STUB_PAIR(branched_sig_kernel_poly_cuda) SIG_STUB_PAIR(branched_sig_kernel_poly_backprop_cuda)
+SIG_STUB_PAIR(branched_sig_to_log_sig_cuda) SIG_STUB_PAIR(branched_sig_to_log_sig_backprop_cuda)
+SIG_STUB_PAIR(branched_log_sig_join_cuda) SIG_STUB_PAIR(branched_log_sig_join_backprop_cuda)
+SIG_STUB_PAIR(branched_log_sig_from_path_cuda) SIG_STUB_PAIR(branched_log_sig_from_path_backprop_cuda)
+SIG_STUB(prepare_log_sig_cuda) SIG_STUB(clear_cache_cuda) SIG_STUB(set_cache_dir_cuda)
+SIG_STUB(prepare_branched_sig_cuda) SIG_STUB(prepare_branched_log_sig_cuda)
+SIG_STUB(prepare_branched_sig_coef_cuda)

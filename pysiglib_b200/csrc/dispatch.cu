@@ -1,0 +1,285 @@
+// Host dispatch behind the C ABI: argument validation, closed-form cases, kernel
+// family choice, scratch memory, and the pipelined path for calls that pass host
+// memory (NumPy arrays) instead of device pointers.
+//
+// Replaces siglib/cusig/cu_signature.cu:2592-2657 (signature_cuda_),
+// :2467-2590 (signature_cuda_core_), :3417-3488 (sig_backprop_cuda_) and the
+// algorithm chooser :2980-3415 of the reference.  Differences kept deliberate:
+//   * the device is taken from the pointer, not from cudaGetDevice();
+//   * flags never materialise a transformed path (increments are synthesised in
+//     the kernels), forward and backward;
+//   * horner=false computes the same signature with the Horner kernels;
+//   * host pointers are accepted: the batch is cut into chunks that are copied
+//     in, computed and copied out on three streams so the copies overlap compute.
+#include "dispatch.h"
+
+#include <algorithm>
+#include <vector>
+
+#include "kernels.h"
+#include "runtime.h"
+
+namespace sigb200 {
+
+namespace {
+
+void validate_correction(const void* correction, uint64_t correction_len, bool lead_lag, uint64_t degree) {
+    // siglib/cusig/cu_signature.cu (validate_signature_correction_args_cuda_): a non-empty
+    // correction needs a pointer, degree >= 2 and no lead-lag.
+    if (correction_len == 0) return;
+    if (correction == nullptr) throw std::invalid_argument("correction pointer is null but correction_len != 0");
+    if (lead_lag) throw std::invalid_argument("correction cannot be used with lead_lag");
+    if (degree < 2) throw std::invalid_argument("correction must be empty when degree < 2");
+    throw std::invalid_argument(
+        "per-segment corrections are not implemented in this build of libcusig (sm_100a signature path)");
+}
+
+unsigned generic_ctas(const SigShape& s, int sm_count, uint64_t bytes_per_cta) {
+    uint64_t ctas = std::min<uint64_t>(s.batch, uint64_t(sm_count) * 4);
+    // keep the fallback's scratch under 4 GiB
+    const uint64_t cap = std::max<uint64_t>(1, (4ull << 30) / std::max<uint64_t>(bytes_per_cta, 1));
+    ctas = std::max<uint64_t>(1, std::min(ctas, cap));
+    return static_cast<unsigned>(ctas);
+}
+
+int sm_count_of_current_device() {
+    return device_context(current_device()).sm_count;
+}
+
+// One pipelined pass over the batch for host-resident operands.
+struct HostOperand {
+    const void* host;
+    uint64_t bytes_per_path;
+};
+
+template <typename Compute>
+void run_host_pipeline(uint64_t batch, const std::vector<HostOperand>& inputs, void* host_out,
+                       uint64_t out_bytes_per_path, Compute&& compute) {
+    DeviceContext& ctx = device_context(current_device());
+    std::lock_guard<std::mutex> lock(ctx.mu);
+
+    uint64_t per_path = out_bytes_per_path;
+    for (const auto& in : inputs) per_path += in.bytes_per_path;
+    per_path = std::max<uint64_t>(per_path, 1);
+    // ~8 chunks, each at most 2 GiB of staged operands, at least one path.
+    uint64_t chunk = (batch + 7) / 8;
+    chunk = std::min<uint64_t>(chunk, std::max<uint64_t>(1, (2ull << 30) / per_path));
+    chunk = std::max<uint64_t>(chunk, 1);
+    const uint64_t n_chunks = (batch + chunk - 1) / chunk;
+    const int n_buf = n_chunks > 1 ? 2 : 1;
+
+    struct Slot {
+        std::vector<void*> in;
+        void* out = nullptr;
+        cudaEvent_t computed = nullptr, copied_out = nullptr, copied_in = nullptr;
+    };
+    std::vector<Slot> slots(n_buf);
+    cudaEvent_t ready = nullptr;
+    auto cleanup = [&]() {
+        (void)cudaStreamSynchronize(ctx.copy_in);
+        (void)cudaStreamSynchronize(ctx.compute);
+        (void)cudaStreamSynchronize(ctx.copy_out);
+        for (auto& sl : slots) {
+            for (void* p : sl.in) if (p) (void)cudaFreeAsync(p, ctx.compute);
+            if (sl.out) (void)cudaFreeAsync(sl.out, ctx.compute);
+            if (sl.computed) (void)cudaEventDestroy(sl.computed);
+            if (sl.copied_out) (void)cudaEventDestroy(sl.copied_out);
+            if (sl.copied_in) (void)cudaEventDestroy(sl.copied_in);
+        }
+        if (ready) (void)cudaEventDestroy(ready);
+    };
+    try {
+        for (auto& sl : slots) {
+            sl.in.assign(inputs.size(), nullptr);
+            for (size_t i = 0; i < inputs.size(); ++i) {
+                const uint64_t bytes = std::max<uint64_t>(inputs[i].bytes_per_path * chunk, 16);
+                const cudaError_t err = cudaMallocAsync(&sl.in[i], bytes, ctx.compute);
+                if (err == cudaErrorMemoryAllocation) { (void)cudaGetLastError(); throw std::bad_alloc(); }
+                SIG_CUDA_CHECK(err);
+            }
+            const cudaError_t err = cudaMallocAsync(&sl.out, std::max<uint64_t>(out_bytes_per_path * chunk, 16), ctx.compute);
+            if (err == cudaErrorMemoryAllocation) { (void)cudaGetLastError(); throw std::bad_alloc(); }
+            SIG_CUDA_CHECK(err);
+            SIG_CUDA_CHECK(cudaEventCreateWithFlags(&sl.computed, cudaEventDisableTiming));
+            SIG_CUDA_CHECK(cudaEventCreateWithFlags(&sl.copied_out, cudaEventDisableTiming));
+            SIG_CUDA_CHECK(cudaEventCreateWithFlags(&sl.copied_in, cudaEventDisableTiming));
+        }
+        SIG_CUDA_CHECK(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
+        SIG_CUDA_CHECK(cudaEventRecord(ready, ctx.compute));
+        SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_in, ready, 0));
+        SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_out, ready, 0));
+
+        for (uint64_t c = 0; c < n_chunks; ++c) {
+            Slot& sl = slots[c % n_buf];
+            const uint64_t begin = c * chunk;
+            const uint64_t count = std::min(chunk, batch - begin);
+            if (c >= uint64_t(n_buf)) {
+                // the slot's previous occupant must have been consumed before it is overwritten
+                SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_in, sl.computed, 0));
+                SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.compute, sl.copied_out, 0));
+            }
+            for (size_t i = 0; i < inputs.size(); ++i) {
+                const uint64_t bpp = inputs[i].bytes_per_path;
+                if (bpp == 0) continue;
+                SIG_CUDA_CHECK(cudaMemcpyAsync(sl.in[i], static_cast<const char*>(inputs[i].host) + begin * bpp,
+                                               count * bpp, cudaMemcpyHostToDevice, ctx.copy_in));
+            }
+            SIG_CUDA_CHECK(cudaEventRecord(sl.copied_in, ctx.copy_in));
+            SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.compute, sl.copied_in, 0));
+            compute(sl.in, sl.out, count, ctx.compute);
+            SIG_CUDA_CHECK(cudaEventRecord(sl.computed, ctx.compute));
+            SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_out, sl.computed, 0));
+            if (out_bytes_per_path)
+                SIG_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(host_out) + begin * out_bytes_per_path, sl.out,
+                                               count * out_bytes_per_path, cudaMemcpyDeviceToHost, ctx.copy_out));
+            SIG_CUDA_CHECK(cudaEventRecord(sl.copied_out, ctx.copy_out));
+        }
+        SIG_CUDA_CHECK(cudaStreamSynchronize(ctx.copy_in));
+        SIG_CUDA_CHECK(cudaStreamSynchronize(ctx.compute));
+        SIG_CUDA_CHECK(cudaStreamSynchronize(ctx.copy_out));
+    } catch (...) {
+        cleanup();
+        throw;
+    }
+    cleanup();
+}
+
+}  // namespace
+
+template <typename T>
+void forward_on_device(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream) {
+    if (s.batch == 0 || s.stride == 0) return;
+    if (s.len <= 1 || s.degree <= 1 || s.dim == 1) {
+        launch_trivial_forward<T>(path, out, s, end_time, stream);
+        return;
+    }
+    if (kernel_policy() == 0 && launch_tile_forward<T>(path, out, s, end_time, stream)) return;
+    const uint64_t elems = generic_forward_scratch_elems(s);
+    const unsigned ctas = generic_ctas(s, sm_count_of_current_device(), elems * sizeof(T));
+    Scratch scratch(checked_mul(checked_mul(elems, ctas, "scratch"), sizeof(T), "scratch"), stream);
+    launch_generic_forward<T>(path, out, s, end_time, scratch.as<T>(), ctas, stream);
+}
+
+template <typename T>
+void backward_on_device(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
+                        T end_time, cudaStream_t stream) {
+    const uint64_t out_elems = checked_mul(s.batch, checked_mul(s.data_len, s.data_dim, "path gradient"),
+                                           "path gradient");
+    if (out_elems == 0) return;
+    if (s.len <= 1 || s.degree == 0) {
+        launch_fill<T>(out, out_elems, T(0), stream);
+        return;
+    }
+    if (s.degree > kMaxDegree)
+        throw std::invalid_argument("sig_backprop on CUDA requires degree <= 64. Reduce the truncation level.");
+    if (kernel_policy() == 0 && tile_backward_available<T>(s)) {
+        const uint64_t g_elems = checked_mul(s.batch, checked_mul(s.data_len - 1, s.data_dim, "scratch"), "scratch");
+        Scratch incr(checked_mul(g_elems, sizeof(T), "scratch"), stream);
+        if (launch_tile_backward<T>(path, out, sig_derivs, sig, s, end_time, incr.as<T>(), stream)) return;
+    }
+    const uint64_t elems = generic_backward_scratch_elems(s);
+    const unsigned ctas = generic_ctas(s, sm_count_of_current_device(), elems * sizeof(T));
+    Scratch scratch(checked_mul(checked_mul(elems, ctas, "scratch"), sizeof(T), "scratch"), stream);
+    launch_generic_backward<T>(path, out, sig_derivs, sig, s, end_time, scratch.as<T>(), ctas, stream);
+}
+
+template <typename T>
+void signature_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, uint64_t length,
+                     uint64_t degree, bool time_aug, bool lead_lag, T end_time, bool /*horner*/,
+                     bool scalar_term, const T* correction, uint64_t correction_len, const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("signature_cuda received path of dimension 0");
+    validate_correction(correction, correction_len, lead_lag, degree);
+    if (opt.nonfinite) *opt.nonfinite = 0;
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, dimension, length, degree, time_aug, lead_lag, scalar_term);
+    if (s.stride == 0) return;
+    if (out == nullptr || (path == nullptr && length * dimension != 0))
+        throw std::invalid_argument("signature_cuda received a null pointer");
+
+    const PointerInfo pin = classify_pointer(path), pout = classify_pointer(out);
+    const bool host_call = !pout.on_device;
+    if (length * dimension != 0 && pin.on_device != pout.on_device)
+        throw std::invalid_argument("signature_cuda: path and out must both be device pointers or both host pointers");
+
+    if (!host_call) {
+        DeviceGuard guard(pout.device);
+        forward_on_device<T>(path, out, s, end_time, opt.stream);
+        if (opt.nonfinite) {
+            Scratch flag(sizeof(int), opt.stream);
+            SIG_CUDA_CHECK(cudaMemsetAsync(flag.get(), 0, sizeof(int), opt.stream));
+            launch_nonfinite_scan<T>(out, s.batch * s.stride, flag.as<int>(), opt.stream);
+            SIG_CUDA_CHECK(cudaMemcpyAsync(opt.nonfinite, flag.get(), sizeof(int), cudaMemcpyDeviceToHost, opt.stream));
+            SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        } else if (opt.synchronize) {
+            SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        }
+        return;
+    }
+
+    // host operands: stage through the device selected by the caller (current device)
+    DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
+    std::vector<HostOperand> ins{{path, s.data_len * s.data_dim * sizeof(T)}};
+    run_host_pipeline(batch, ins, out, s.stride * sizeof(T),
+        [&](const std::vector<void*>& din, void* dout, uint64_t count, cudaStream_t stream) {
+            SigShape cs = s;
+            cs.batch = count;
+            forward_on_device<T>(static_cast<const T*>(din[0]), static_cast<T*>(dout), cs, end_time, stream);
+        });
+    if (opt.nonfinite) {
+        bool bad = false;
+        const uint64_t n = s.batch * s.stride;
+        for (uint64_t i = 0; i < n && !bad; ++i) bad = !(std::abs(double(out[i])) <= 1.7976931348623157e308);
+        *opt.nonfinite = bad ? 1 : 0;
+    }
+}
+
+template <typename T>
+void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig, uint64_t batch,
+                        uint64_t dimension, uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
+                        T end_time, bool scalar_term, const T* correction, uint64_t correction_len,
+                        const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("sig_backprop_cuda received path of dimension 0");
+    validate_correction(correction, correction_len, lead_lag, degree);
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, dimension, length, degree, time_aug, lead_lag, scalar_term);
+    if (length == 0) return;
+    if (out == nullptr || path == nullptr) throw std::invalid_argument("sig_backprop_cuda received a null pointer");
+    const bool needs_sig = !(s.len <= 1 || s.degree == 0) && s.stride != 0;
+    if (needs_sig && (sig == nullptr || sig_derivs == nullptr))
+        throw std::invalid_argument("sig_backprop_cuda received a null pointer");
+
+    const PointerInfo pout = classify_pointer(out);
+    if (pout.on_device) {
+        if (!classify_pointer(path).on_device || (needs_sig && (!classify_pointer(sig).on_device ||
+                                                                !classify_pointer(sig_derivs).on_device)))
+            throw std::invalid_argument("sig_backprop_cuda: all buffers must be device pointers or all host pointers");
+        DeviceGuard guard(pout.device);
+        backward_on_device<T>(path, out, sig_derivs, sig, s, end_time, opt.stream);
+        if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        return;
+    }
+
+    DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
+    const uint64_t sig_bytes = needs_sig ? s.stride * sizeof(T) : 0;
+    std::vector<HostOperand> ins{{path, s.data_len * s.data_dim * sizeof(T)}, {sig_derivs, sig_bytes}, {sig, sig_bytes}};
+    run_host_pipeline(batch, ins, out, s.data_len * s.data_dim * sizeof(T),
+        [&](const std::vector<void*>& din, void* dout, uint64_t count, cudaStream_t stream) {
+            SigShape cs = s;
+            cs.batch = count;
+            backward_on_device<T>(static_cast<const T*>(din[0]), static_cast<T*>(dout),
+                                  static_cast<const T*>(din[1]), static_cast<const T*>(din[2]), cs, end_time, stream);
+        });
+}
+
+#define INSTANTIATE(T)                                                                                    \
+    template void forward_on_device<T>(const T*, T*, const SigShape&, T, cudaStream_t);                   \
+    template void backward_on_device<T>(const T*, T*, const T*, const T*, const SigShape&, T, cudaStream_t); \
+    template void signature_entry<T>(const T*, T*, uint64_t, uint64_t, uint64_t, uint64_t, bool, bool, T, bool, \
+                                     bool, const T*, uint64_t, const CallOptions&);                       \
+    template void sig_backprop_entry<T>(const T*, T*, const T*, const T*, uint64_t, uint64_t, uint64_t, uint64_t, \
+                                        bool, bool, T, bool, const T*, uint64_t, const CallOptions&);
+INSTANTIATE(float)
+INSTANTIATE(double)
+#undef INSTANTIATE
+
+}  // namespace sigb200

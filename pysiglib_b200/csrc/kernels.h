@@ -1,0 +1,64 @@
+// Host-side launch interface of the signature kernels.  Every function enqueues
+// work on `stream` for the current device and returns without synchronising.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "common.h"
+
+namespace sigb200 {
+
+constexpr int kMaxDegree = 64;  // level-index table size; d >= 2 overflows 64 bits long before
+
+struct LevelIndex {
+    // li[k] = offset of level k in the scalar-term layout = (d^k - 1) / (d - 1); li[degree+1] = length
+    uint32_t li[kMaxDegree + 2];
+};
+
+LevelIndex make_level_index(uint64_t dim, uint64_t degree);
+
+// ---- closed forms: degree <= 1, augmented length <= 1, augmented dimension 1 ----
+template <typename T>
+void launch_trivial_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream);
+
+// ---- generic (any dimension / degree) level-synchronous kernels, one CTA per path ----
+// scratch: generic_forward_scratch_elems(s) elements per CTA, `ctas` CTAs.
+uint64_t generic_forward_scratch_elems(const SigShape& s);
+uint64_t generic_backward_scratch_elems(const SigShape& s);
+template <typename T>
+void launch_generic_forward(const T* path, T* out, const SigShape& s, T end_time, T* scratch,
+                            unsigned ctas, cudaStream_t stream);
+template <typename T>
+void launch_generic_backward(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
+                             T end_time, T* scratch, unsigned ctas, cudaStream_t stream);
+
+// ---- register-tile kernels for a table of (dimension, degree) shapes ----
+// Return false when the shape is not in the table (nothing is enqueued).
+// The backward variant accumulates increment gradients with atomics into
+// `incr_grad` (batch x (data_len - 1) x data_dim, zeroed here) and then converts
+// them to point gradients in `out`.
+template <typename T>
+bool tile_forward_available(const SigShape& s);
+template <typename T>
+bool launch_tile_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream);
+template <typename T>
+bool tile_backward_available(const SigShape& s);
+template <typename T>
+bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
+                          T end_time, T* incr_grad, cudaStream_t stream);
+
+// out[t] = g[t-1] - g[t] over the raw path (g = increment gradients, (batch, L-1, d))
+template <typename T>
+void launch_increment_to_point_grad(const T* incr_grad, T* out, uint64_t batch, uint64_t L, uint64_t d,
+                                    cudaStream_t stream);
+
+template <typename T>
+void launch_fill(T* dst, uint64_t n, T value, cudaStream_t stream);
+
+// Scans `n` values for NaN / Inf and sets *flag (device int) to 1 if any is found.
+template <typename T>
+void launch_nonfinite_scan(const T* data, uint64_t n, int* flag, cudaStream_t stream);
+
+}  // namespace sigb200

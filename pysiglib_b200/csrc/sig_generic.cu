@@ -1,0 +1,442 @@
+// Shape-generic signature kernels: any augmented dimension and degree.
+//
+// One CTA owns one path at a time and keeps the whole level structure in global
+// memory (served from L1/L2); each Horner level is a data-parallel phase over the
+// words of that level, separated by __syncthreads().  These kernels are the
+// fallback behind the register-tile kernels (sig_tile.cuh), which cover the
+// shapes that matter for throughput; here the goal is exact agreement with the
+// reference's arithmetic for every shape.
+//
+// What is computed (reference: siglib/cpsig/cp_signature.h:426-500 forward,
+// :549-603 in-place step, :1098-1203 reverse sweep; CUDA host dispatch being
+// replaced: siglib/cusig/cu_signature.cu:2467-2657 and :2897-3488):
+//   forward step, for target level T = N..2, with increment z:
+//       W_1 = z / T;  W_{l+1} = ((W_l + S_l) / (T - l)) (x) z  for l = 1..T-2;
+//       S_T += (W_{T-1} + S_{T-1}) (x) z;          finally S_1 += z.
+//   backward step: rewind S with -z, then pull the adjoint through the same
+//   recurrence level by level, accumulating the increment gradient g.
+#include <cstdio>
+
+#include "increments.cuh"
+#include "kernels.h"
+#include "runtime.h"
+
+namespace sigb200 {
+
+namespace {
+
+constexpr int kGenericThreads = 256;
+
+template <typename T>
+__device__ __forceinline__ T fma_t(T a, T b, T c);
+template <>
+__device__ __forceinline__ float fma_t<float>(float a, float b, float c) { return fmaf(a, b, c); }
+template <>
+__device__ __forceinline__ double fma_t<double>(double a, double b, double c) { return fma(a, b, c); }
+
+// ---- closed forms -----------------------------------------------------------
+
+// mode 0: fill with zeros (+1 in the scalar slot); mode 1: degree-1 endpoint
+// difference; mode 2: augmented dimension 1, level k = dx^k / k!.
+template <typename T>
+__global__ void trivial_forward_kernel(PathView<T> pv, T* out, uint64_t total, uint32_t stride, int degree,
+                                       bool scalar, int mode) {
+    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const uint64_t b = idx / stride;
+    const uint32_t i = static_cast<uint32_t>(idx - b * stride);
+    if (scalar && i == 0) { out[idx] = T(1); return; }
+    if (mode == 0) { out[idx] = T(0); return; }
+    const T* x = pv.base + b * pv.path_stride;
+    const int k = static_cast<int>(i) + (scalar ? 0 : 1);  // position in the scalar-term layout
+    if (mode == 1) {
+        const int c = k - 1;
+        T v;
+        if (c < pv.d) v = x[(pv.L - 1) * pv.d + c] - x[c];
+        else if (pv.lead_lag && c < 2 * pv.d) v = x[(pv.L - 1) * pv.d + (c - pv.d)] - x[c - pv.d];
+        else v = pv.dt * T(pv.steps);
+        out[idx] = v;
+        return;
+    }
+    // mode 2: raw dimension 1, no flags (siglib/cpsig/cp_signature.h:770-785)
+    const T inc = x[pv.L - 1] - x[0];
+    T v = T(1);
+    for (int level = 1; level <= k; ++level) v *= inc / T(level);
+    out[idx] = v;
+}
+
+// ---- block-cooperative Horner step on a scalar-term layout signature --------
+
+template <typename T>
+__device__ void horner_step_block(T* S, const T* zs, const T* rcp, int D, int N, const uint32_t* li,
+                                  T* wa, T* wb) {
+    const unsigned tid = threadIdx.x, nt = blockDim.x;
+    for (int target = N; target >= 2; --target) {
+        const T r_target = rcp[target];
+        const T* cur = nullptr;
+        T* nxt = wa;
+        for (int l = 1; l <= target - 2; ++l) {
+            const T scale = rcp[target - l];
+            const uint32_t out_size = (li[l + 1] - li[l]) * uint32_t(D);
+            const T* s_l = S + li[l];
+            for (uint32_t idx = tid; idx < out_size; idx += nt) {
+                const uint32_t w = idx / uint32_t(D);
+                const uint32_t c = idx - w * uint32_t(D);
+                const T wv = (l == 1) ? zs[w] * r_target : cur[w];
+                const T v = (wv + s_l[w]) * scale;
+                nxt[idx] = zs[c] * v;
+            }
+            __syncthreads();
+            cur = nxt;
+            nxt = (nxt == wa) ? wb : wa;
+        }
+        const uint32_t out_size = li[target + 1] - li[target];
+        const T* s_l = S + li[target - 1];
+        T* s_t = S + li[target];
+        for (uint32_t idx = tid; idx < out_size; idx += nt) {
+            const uint32_t w = idx / uint32_t(D);
+            const uint32_t c = idx - w * uint32_t(D);
+            const T wv = (target == 2) ? zs[w] * r_target : cur[w];
+            s_t[idx] = fma_t(zs[c], wv + s_l[w], s_t[idx]);
+        }
+        __syncthreads();
+    }
+    for (uint32_t c = tid; c < uint32_t(D); c += nt) S[1 + c] = fma_t(zs[c], T(1), S[1 + c]);
+    __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads)
+generic_forward_kernel(PathView<T> pv, T* out, uint64_t batch, int N, uint32_t stride, bool scalar,
+                       T* scratch, uint32_t work_elems, LevelIndex lev) {
+    extern __shared__ unsigned char smem_raw[];
+    T* zs = reinterpret_cast<T*>(smem_raw);
+    T* rcp = zs + pv.dim;
+    __shared__ uint32_t li[kMaxDegree + 2];
+    const unsigned tid = threadIdx.x, nt = blockDim.x;
+    const int D = pv.dim;
+    for (unsigned i = tid; i < unsigned(N + 2); i += nt) li[i] = lev.li[i];
+    for (unsigned i = tid; i <= unsigned(N); i += nt) rcp[i] = i ? T(1) / T(i) : T(0);
+    T* wa = scratch + uint64_t(blockIdx.x) * 2 * work_elems;
+    T* wb = wa + work_elems;
+    __syncthreads();
+
+    for (uint64_t b = blockIdx.x; b < batch; b += gridDim.x) {
+        const T* x = pv.base + b * pv.path_stride;
+        T* S = out + b * stride - (scalar ? 0 : 1);
+        // first segment (siglib/cpsig/cp_signature.h:365-389)
+        for (unsigned c = tid; c < unsigned(D); c += nt) {
+            const T z = pv.increment(x, 0, c);
+            zs[c] = z;
+            S[1 + c] = z;
+        }
+        if (scalar && tid == 0) S[0] = T(1);
+        __syncthreads();
+        for (int k = 2; k <= N; ++k) {
+            const uint32_t size = li[k + 1] - li[k];
+            const T r = rcp[k];
+            for (uint32_t idx = tid; idx < size; idx += nt) {
+                const uint32_t w = idx / uint32_t(D);
+                const uint32_t c = idx - w * uint32_t(D);
+                S[li[k] + idx] = zs[c] * (S[li[k - 1] + w] * r);
+            }
+            __syncthreads();
+        }
+        for (int j = 1; j < pv.steps; ++j) {
+            for (unsigned c = tid; c < unsigned(D); c += nt) zs[c] = pv.increment(x, j, c);
+            __syncthreads();
+            horner_step_block(S, zs, rcp, D, N, li, wa, wb);
+        }
+        __syncthreads();
+    }
+}
+
+// column sums gpart[j] = sum_i rows[i*D + j] * val[i]
+template <typename T>
+__device__ void column_sums_block(const T* rows, const T* val, uint32_t size, int D, T* gpart) {
+    const unsigned tid = threadIdx.x, nt = blockDim.x;
+    if (unsigned(D) >= nt) {
+        for (uint32_t j = tid; j < uint32_t(D); j += nt) {
+            T acc = T(0);
+            for (uint32_t i = 0; i < size; ++i) acc = fma_t(rows[uint64_t(i) * D + j], val[i], acc);
+            gpart[j] = acc;
+        }
+    } else {
+        const unsigned groups = nt / unsigned(D);
+        if (tid < groups * unsigned(D)) {
+            const unsigned grp = tid / unsigned(D), j = tid - grp * unsigned(D);
+            if (grp < size) {
+                T acc = T(0);
+                for (uint32_t i = grp; i < size; i += groups) acc = fma_t(rows[uint64_t(i) * D + j], val[i], acc);
+                atomicAdd(&gpart[j], acc);
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads)
+generic_backward_kernel(PathView<T> pv, T* out, const T* sig_derivs, const T* sig, uint64_t batch, int N,
+                        uint32_t stride, bool scalar, T* scratch, uint64_t scratch_per_cta,
+                        uint32_t work_elems, LevelIndex lev) {
+    extern __shared__ unsigned char smem_raw[];
+    const int D = pv.dim;
+    T* zs = reinterpret_cast<T*>(smem_raw);
+    T* g = zs + D;
+    T* gpart = g + D;
+    T* rcp = gpart + D;
+    __shared__ uint32_t li[kMaxDegree + 2];
+    const unsigned tid = threadIdx.x, nt = blockDim.x;
+    for (unsigned i = tid; i < unsigned(N + 2); i += nt) li[i] = lev.li[i];
+    for (unsigned i = tid; i <= unsigned(N); i += nt) rcp[i] = i ? T(1) / T(i) : T(0);
+    __syncthreads();
+    const uint32_t full_len = li[N + 1];
+    T* Sc = scratch + uint64_t(blockIdx.x) * scratch_per_cta;
+    T* dSc = Sc + full_len;
+    T* HS = dSc + full_len;  // work levels 0..N-1, indexed with li[]
+    T* hd0 = HS + li[N];
+    T* hd1 = hd0 + work_elems;
+    const int dd = pv.d;
+
+    for (uint64_t b = blockIdx.x; b < batch; b += gridDim.x) {
+        const T* x = pv.base + b * pv.path_stride;
+        T* outb = out + b * pv.path_stride;
+        const T* sig_b = sig + b * stride - (scalar ? 0 : 1);
+        const T* der_b = sig_derivs + b * stride - (scalar ? 0 : 1);
+        for (uint32_t i = tid; i < full_len; i += nt) {
+            Sc[i] = i ? sig_b[i] : T(1);
+            dSc[i] = i ? der_b[i] : T(0);
+        }
+        for (uint64_t i = tid; i < pv.path_stride; i += nt) outb[i] = T(0);
+        __syncthreads();
+
+        int pos = pv.L - 1;
+        bool parity = false;
+        for (int j = pv.steps - 1; j >= 0; --j) {
+            for (unsigned c = tid; c < unsigned(D); c += nt) zs[c] = -pv.increment(x, j, c);
+            __syncthreads();
+            horner_step_block(Sc, zs, rcp, D, N, li, hd0, hd1);  // rewind to the state before step j
+            for (unsigned c = tid; c < unsigned(D); c += nt) {
+                zs[c] = -zs[c];
+                g[c] = dSc[1 + c];
+            }
+            __syncthreads();
+
+            for (int target = 2; target <= N; ++target) {
+                const T r_target = rcp[target];
+                for (unsigned c = tid; c < unsigned(D); c += nt) HS[1 + c] = zs[c] * r_target;
+                __syncthreads();
+                for (int level = 1; level + 1 < target; ++level) {
+                    const T scale = rcp[target - level];
+                    const uint32_t out_size = (li[level + 1] - li[level]) * uint32_t(D);
+                    for (uint32_t idx = tid; idx < out_size; idx += nt) {
+                        const uint32_t w = idx / uint32_t(D);
+                        const uint32_t c = idx - w * uint32_t(D);
+                        const T value = (HS[li[level] + w] + Sc[li[level] + w]) * scale;
+                        HS[li[level + 1] + idx] = zs[c] * value;
+                    }
+                    __syncthreads();
+                }
+                const T* incoming = dSc + li[target];
+                T* hd_cur = hd0;
+                for (int level = target - 1; level > 0; --level) {
+                    const T scale = rcp[target - level];
+                    const uint32_t size = li[level + 1] - li[level];
+                    for (unsigned c = tid; c < unsigned(D); c += nt) gpart[c] = T(0);
+                    for (uint32_t i = tid; i < size; i += nt) {
+                        const T value = (HS[li[level] + i] + Sc[li[level] + i]) * scale;
+                        const T* row = incoming + uint64_t(i) * D;
+                        T reduced = T(0);
+                        for (int c = 0; c < D; ++c) reduced = fma_t(row[c], zs[c], reduced);
+                        reduced *= scale;
+                        hd_cur[i] = reduced;
+                        dSc[li[level] + i] += reduced;
+                        HS[li[level] + i] = value;
+                    }
+                    __syncthreads();
+                    column_sums_block(incoming, HS + li[level], size, D, gpart);
+                    __syncthreads();
+                    for (unsigned c = tid; c < unsigned(D); c += nt) g[c] += gpart[c];
+                    incoming = hd_cur;
+                    hd_cur = (hd_cur == hd0) ? hd1 : hd0;
+                    __syncthreads();
+                }
+                for (unsigned c = tid; c < unsigned(D); c += nt) g[c] += incoming[c] * r_target;
+                __syncthreads();
+            }
+
+            const int half = (pv.lead_lag && parity) ? dd : 0;
+            for (int c = tid; c < dd; c += nt) {
+                const T s = g[c + half];
+                outb[pos * dd + c] += s;
+                outb[(pos - 1) * dd + c] -= s;
+            }
+            if (j > 0) {
+                if (!pv.lead_lag || parity) pos -= 1;
+                parity = !parity;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+template <typename T>
+__global__ void increment_to_point_grad_kernel(const T* __restrict__ g, T* __restrict__ out, uint64_t total,
+                                               uint32_t L, uint32_t d) {
+    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const uint64_t row = idx / d;  // b * L + t
+    const uint32_t c = static_cast<uint32_t>(idx - row * d);
+    const uint64_t b = row / L;
+    const uint32_t t = static_cast<uint32_t>(row - b * L);
+    const T* gb = g + b * uint64_t(L - 1) * d;
+    T v = T(0);
+    if (t > 0) v += gb[uint64_t(t - 1) * d + c];
+    if (t + 1 < L) v -= gb[uint64_t(t) * d + c];
+    out[idx] = v;
+}
+
+template <typename T>
+__global__ void fill_kernel(T* dst, uint64_t n, T value) {
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x)
+        dst[i] = value;
+}
+
+template <typename T>
+__global__ void nonfinite_scan_kernel(const T* __restrict__ data, uint64_t n, int* flag) {
+    bool bad = false;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) {
+        const T v = data[i];
+        bad |= !(fabs(double(v)) <= 1.7976931348623157e308);
+    }
+    if (__syncthreads_or(bad) && threadIdx.x == 0) *flag = 1;
+}
+
+unsigned grid_1d(uint64_t total, unsigned block) {
+    const uint64_t blocks = (total + block - 1) / block;
+    if (blocks > 0x7fffffffull) throw std::out_of_range("launch grid too large");
+    return static_cast<unsigned>(blocks ? blocks : 1);
+}
+
+uint32_t work_elems_of(const SigShape& s) {
+    // size of level N-1 (largest Horner work level); at least 1 so pointers stay valid
+    const uint64_t w = s.degree >= 2 ? ipow(s.dim, s.degree - 1) : 1;
+    return static_cast<uint32_t>(w ? w : 1);
+}
+
+void check_generic_limits(const SigShape& s) {
+    if (s.degree > kMaxDegree) throw std::invalid_argument("signature degree must be <= 64 on CUDA");
+    if (s.full_len >= (1ull << 31) || s.dim >= (1ull << 24) || s.len >= (1ull << 30))
+        throw std::invalid_argument("signature too large for the CUDA kernels (2^31 coefficients per path)");
+}
+
+}  // namespace
+
+LevelIndex make_level_index(uint64_t dim, uint64_t degree) {
+    LevelIndex l{};
+    uint64_t v = 0;
+    for (uint64_t k = 0; k <= degree + 1 && k < kMaxDegree + 2; ++k) {
+        l.li[k] = static_cast<uint32_t>(v);
+        v = v * dim + 1;
+    }
+    return l;
+}
+
+uint64_t generic_forward_scratch_elems(const SigShape& s) { return 2ull * work_elems_of(s); }
+
+uint64_t generic_backward_scratch_elems(const SigShape& s) {
+    const LevelIndex l = make_level_index(s.dim, s.degree);
+    return 2ull * s.full_len + l.li[s.degree] + 2ull * work_elems_of(s);
+}
+
+template <typename T>
+void launch_trivial_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream) {
+    const uint64_t total = checked_mul(s.batch, s.stride, "signature output");
+    if (total == 0) return;
+    if (s.stride >= (1ull << 32)) throw std::invalid_argument("signature too large for the CUDA kernels");
+    int mode;
+    if (s.len <= 1 || s.degree == 0) mode = 0;
+    else if (s.dim == 1) mode = 2;
+    else mode = 1;  // degree == 1
+    const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
+    trivial_forward_kernel<T><<<grid_1d(total, 128), 128, 0, stream>>>(
+        pv, out, total, static_cast<uint32_t>(s.stride), static_cast<int>(s.degree), s.scalar_term, mode);
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T>
+void launch_generic_forward(const T* path, T* out, const SigShape& s, T end_time, T* scratch, unsigned ctas,
+                            cudaStream_t stream) {
+    check_generic_limits(s);
+    const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
+    const size_t smem = (s.dim + s.degree + 1) * sizeof(T);
+    if (smem > 48 * 1024)
+        SIG_CUDA_CHECK(cudaFuncSetAttribute(generic_forward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(smem)));
+    generic_forward_kernel<T><<<ctas, kGenericThreads, smem, stream>>>(
+        pv, out, s.batch, static_cast<int>(s.degree), static_cast<uint32_t>(s.stride), s.scalar_term, scratch,
+        work_elems_of(s), make_level_index(s.dim, s.degree));
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T>
+void launch_generic_backward(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
+                             T end_time, T* scratch, unsigned ctas, cudaStream_t stream) {
+    check_generic_limits(s);
+    const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
+    const size_t smem = (3 * s.dim + s.degree + 1) * sizeof(T);
+    if (smem > 48 * 1024)
+        SIG_CUDA_CHECK(cudaFuncSetAttribute(generic_backward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(smem)));
+    generic_backward_kernel<T><<<ctas, kGenericThreads, smem, stream>>>(
+        pv, out, sig_derivs, sig, s.batch, static_cast<int>(s.degree), static_cast<uint32_t>(s.stride),
+        s.scalar_term, scratch, generic_backward_scratch_elems(s), work_elems_of(s),
+        make_level_index(s.dim, s.degree));
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T>
+void launch_increment_to_point_grad(const T* incr_grad, T* out, uint64_t batch, uint64_t L, uint64_t d,
+                                    cudaStream_t stream) {
+    const uint64_t total = checked_mul(batch, checked_mul(L, d, "path gradient"), "path gradient");
+    if (total == 0) return;
+    increment_to_point_grad_kernel<T><<<grid_1d(total, 256), 256, 0, stream>>>(
+        incr_grad, out, total, static_cast<uint32_t>(L), static_cast<uint32_t>(d));
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T>
+void launch_fill(T* dst, uint64_t n, T value, cudaStream_t stream) {
+    if (n == 0) return;
+    const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>((n + 255) / 256, 148 * 8));
+    fill_kernel<T><<<blocks, 256, 0, stream>>>(dst, n, value);
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T>
+void launch_nonfinite_scan(const T* data, uint64_t n, int* flag, cudaStream_t stream) {
+    if (n == 0) return;
+    const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>((n + 255) / 256, 148 * 8));
+    nonfinite_scan_kernel<T><<<blocks, 256, 0, stream>>>(data, n, flag);
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+#define INSTANTIATE(T)                                                                                   \
+    template void launch_trivial_forward<T>(const T*, T*, const SigShape&, T, cudaStream_t);             \
+    template void launch_generic_forward<T>(const T*, T*, const SigShape&, T, T*, unsigned, cudaStream_t); \
+    template void launch_generic_backward<T>(const T*, T*, const T*, const T*, const SigShape&, T, T*,   \
+                                             unsigned, cudaStream_t);                                    \
+    template void launch_increment_to_point_grad<T>(const T*, T*, uint64_t, uint64_t, uint64_t, cudaStream_t); \
+    template void launch_fill<T>(T*, uint64_t, T, cudaStream_t);                                         \
+    template void launch_nonfinite_scan<T>(const T*, uint64_t, int*, cudaStream_t);
+INSTANTIATE(float)
+INSTANTIATE(double)
+#undef INSTANTIATE
+
+}  // namespace sigb200

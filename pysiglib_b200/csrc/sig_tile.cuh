@@ -1,0 +1,301 @@
+// Register-tile signature kernels for sm_100a: forward Horner sweep and reverse
+// (state-reconstructing) sweep, compiled per (dimension, degree, chain length, group).
+//
+// Mapping.  One CUDA thread = one execution unit of tile_math.h; the units of a path are
+// laid out over ceil(UNITS / 32) warps, and every warp works on exactly one path, so all
+// 32 lanes read the same increment and shared-memory reads of it are broadcasts.  Warps
+// are fully independent: each one stages the increments of CH consecutive steps of its
+// path into its own slice of shared memory with coalesced loads, synchronises with
+// __syncwarp() only, and then runs the CH steps out of registers.  There is no block-wide
+// barrier in either kernel.
+//
+// Forward: state in registers for the whole path, written once at the end.
+// Backward: final signature and seeds loaded into registers; per step the state is
+// rewound with the negated increment, the adjoint is pulled back, and the per-unit
+// d'-vector of increment gradients is summed over the warp with a halving butterfly
+// (d' - 1 shuffles instead of 5 d'), buffered per chunk in shared memory and added to the
+// global increment-gradient buffer with one atomic per (step, channel, warp).
+//
+// These kernels replace the reference's thread-per-prefix kernels
+// (siglib/cusig/cu_signature.cu:183-298 signature_per_word_ker,
+// siglib/cusig/cu_signature_horner.cuh:219-249 forward_kernel, :309-363 backward_kernel).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "increments.cuh"
+#include "tile_math.h"
+
+namespace sigb200 {
+
+constexpr int kTileChunk = 32;  // steps staged per warp and chunk
+
+template <typename T> struct VecOf;
+template <> struct VecOf<float> { using type = float4; static constexpr int n = 4; };
+template <> struct VecOf<double> { using type = double2; static constexpr int n = 2; };
+
+template <typename T, int D>
+struct RowPad {
+    static constexpr int V = VecOf<T>::n;
+    static constexpr int DP = (D + V - 1) / V * V;  // padded row length (elements)
+};
+
+// dst[0..n) = src[0..n) with 16-byte shared-memory loads; src must be 16-byte aligned and
+// readable up to the next multiple of the vector width.
+template <typename T, int n>
+__device__ __forceinline__ void load_row_vec(T (&dst)[n], const T* src) {
+    using V = typename VecOf<T>::type;
+    constexpr int W = VecOf<T>::n;
+    constexpr int NV = (n + W - 1) / W;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const V v = reinterpret_cast<const V*>(src)[i];
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int k = 0; k < W; ++k)
+            if (i * W + k < n) dst[i * W + k] = e[k];
+    }
+}
+
+template <typename T, typename Sh>
+struct StepOperands {
+    T z[Sh::D];
+    T zg[Sh::G];
+    T zc[Sh::P > 0 ? Sh::P : 1];
+};
+
+template <typename T, typename Sh, bool NEGATE>
+__device__ __forceinline__ void load_step(StepOperands<T, Sh>& op, const T* row, const UnitIndex<Sh>& ix) {
+    load_row_vec<T, Sh::D>(op.z, row);
+    if constexpr (Sh::G == Sh::D) {
+#pragma unroll
+        for (int j = 0; j < Sh::G; ++j) op.zg[j] = op.z[j];
+    } else if constexpr (Sh::G % VecOf<T>::n == 0) {
+        load_row_vec<T, Sh::G>(op.zg, row + ix.c0);
+    } else {
+#pragma unroll
+        for (int j = 0; j < Sh::G; ++j) op.zg[j] = row[ix.c0 + j];
+    }
+#pragma unroll
+    for (int k = 0; k < Sh::P; ++k) op.zc[k] = row[ix.p[k]];
+    if constexpr (NEGATE) {
+#pragma unroll
+        for (int c = 0; c < Sh::D; ++c) op.z[c] = -op.z[c];
+#pragma unroll
+        for (int j = 0; j < Sh::G; ++j) op.zg[j] = -op.zg[j];
+#pragma unroll
+        for (int k = 0; k < Sh::P; ++k) op.zc[k] = -op.zc[k];
+    }
+}
+
+// Stage the increments of augmented steps [j0, j0 + cnt) of path x into zs (row stride DP).
+template <typename T, typename Sh, bool FLAGS>
+__device__ __forceinline__ void stage_increments(T* zs, const PathView<T>& pv, const T* x, int j0, int cnt,
+                                                 int lane) {
+    constexpr int D = Sh::D;
+    constexpr int DP = RowPad<T, D>::DP;
+    const int total = cnt * D;
+    if constexpr (FLAGS) {
+        for (int i = lane; i < total; i += 32) {
+            const int step = i / D, c = i - step * D;
+            zs[step * DP + c] = pv.increment(x, j0 + step, c);
+        }
+    } else {
+        const T* src = x + size_t(j0) * D;
+        for (int i = lane; i < total; i += 32) {
+            const int step = i / D, c = i - step * D;
+            zs[step * DP + c] = src[i + D] - src[i];
+        }
+    }
+}
+
+template <typename T, typename Sh, bool FLAGS, int WPB>
+__global__ void __launch_bounds__(WPB * 32)
+tile_forward_kernel(PathView<T> pv, T* __restrict__ out, uint64_t batch, uint32_t stride, bool scalar) {
+    constexpr int DP = RowPad<T, Sh::D>::DP;
+    constexpr int WPP = (Sh::UNITS + 31) / 32;  // warps per path
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * DP;
+
+    const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
+    if (gw >= batch * WPP) return;
+    const uint64_t b = gw / WPP;
+    const int u = int(gw - b * WPP) * 32 + lane;
+    const bool active = u < Sh::UNITS;
+    const UnitIndex<Sh> ix = decode_unit<Sh>(active ? u : 0);
+    const T* x = pv.base + b * pv.path_stride;
+
+    TileState<T, Sh> st;
+    StepOperands<T, Sh> op;
+    for (int j0 = 0; j0 < pv.steps; j0 += kTileChunk) {
+        const int cnt = min(kTileChunk, pv.steps - j0);
+        __syncwarp();
+        stage_increments<T, Sh, FLAGS>(zs, pv, x, j0, cnt, lane);
+        __syncwarp();
+        int step = 0;
+        if (j0 == 0) {
+            load_step<T, Sh, false>(op, zs, ix);
+            tile_init_first<T, Sh>(st, op.z, op.zg, op.zc);
+            step = 1;
+        }
+        for (; step < cnt; ++step) {
+            load_step<T, Sh, false>(op, zs + step * DP, ix);
+            tile_update<T, Sh>(st, op.z, op.zg, op.zc);
+        }
+    }
+    if (active) {
+        T* S = out + b * stride - (scalar ? 0 : 1);
+        tile_store<T, Sh>(st, ix, S);
+        if (scalar && u == 0) S[0] = T(1);
+    }
+}
+
+constexpr int next_pow2(int v) { return v <= 1 ? 1 : 2 * next_pow2((v + 1) / 2); }
+constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v / 2); }
+
+// Sum v[0..DP2) over the 32 lanes of a warp.  After the call, lane l holds in
+// v[0..max(1, DP2/32)) the totals of letters first_letter(l) .. ; every letter's total is
+// replicated over 32 / min(DP2, 32) lanes.  Each stage halves the number of values a lane
+// carries (the lane keeps one half and trades the other), so the whole reduction costs
+// about DP2 shuffles instead of 5 * DP2.
+template <typename T, int DP2, int NCUR, int MASK>
+__device__ __forceinline__ void warp_halving_stage(T (&v)[DP2], int lane) {
+    if constexpr (MASK >= 1) {
+        if constexpr (NCUR > 1) {
+            constexpr int HALF = NCUR / 2;
+            const bool upper = (lane & MASK) != 0;
+#pragma unroll
+            for (int i = 0; i < HALF; ++i) {
+                const T send = upper ? v[i] : v[i + HALF];
+                const T keep = upper ? v[i + HALF] : v[i];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, MASK);
+            }
+            warp_halving_stage<T, DP2, HALF, MASK / 2>(v, lane);
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], MASK);
+            warp_halving_stage<T, DP2, 1, MASK / 2>(v, lane);
+        }
+    }
+}
+
+template <typename T, int DP2>
+__device__ __forceinline__ void warp_halving_reduce(T (&v)[DP2], int lane) {
+    warp_halving_stage<T, DP2, DP2, 16>(v, lane);
+}
+
+template <int DP2>
+__device__ __forceinline__ int reduced_first_letter(int lane) {
+    if constexpr (DP2 >= 32) return lane * (DP2 / 32);
+    else return lane >> (5 - ilog2(DP2));
+}
+
+template <typename T, typename Sh, bool FLAGS, int WPB>
+__global__ void __launch_bounds__(WPB * 32)
+tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restrict__ derivs,
+                     T* __restrict__ incr_grad, uint64_t batch, uint32_t stride, bool scalar) {
+    constexpr int D = Sh::D, G = Sh::G, P = Sh::P;
+    constexpr int DP = RowPad<T, D>::DP;
+    constexpr int DP2 = next_pow2(D);
+    constexpr int WPP = (Sh::UNITS + 31) / 32;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * (DP + D);
+    T* gbuf = zs + kTileChunk * DP;
+
+    const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
+    if (gw >= batch * WPP) return;
+    const uint64_t b = gw / WPP;
+    const int u = int(gw - b * WPP) * 32 + lane;
+    const bool active = u < Sh::UNITS;
+    const UnitIndex<Sh> ix = decode_unit<Sh>(active ? u : 0);
+    const int grp = ix.c0 / G;
+    const T* x = pv.base + b * pv.path_stride;
+    T* gout = incr_grad + b * uint64_t(pv.L - 1) * pv.d;
+
+    TileState<T, Sh> st;
+    TileAdjoint<T, Sh> ad;
+    tile_load<T, Sh>(st, ad, ix, sig + b * stride - (scalar ? 0 : 1), derivs + b * stride - (scalar ? 0 : 1));
+    if (!active) {
+        // idle lanes carry a zero adjoint so that they add nothing to the warp sums
+#pragma unroll
+        for (int k = 0; k <= P; ++k) ad.ac[k] = T(0);
+#pragma unroll
+        for (int i = 0; i < Sh::TS; ++i) ad.a[i] = T(0);
+    }
+
+    StepOperands<T, Sh> op;
+    for (int j1 = pv.steps; j1 > 0;) {
+        const int j0 = max(0, j1 - kTileChunk);
+        const int cnt = j1 - j0;
+        __syncwarp();
+        stage_increments<T, Sh, FLAGS>(zs, pv, x, j0, cnt, lane);
+        __syncwarp();
+        for (int step = cnt - 1; step >= 0; --step) {
+            load_step<T, Sh, true>(op, zs + step * DP, ix);
+            tile_update<T, Sh>(st, op.z, op.zg, op.zc);  // rewind to the state before this step
+            load_step<T, Sh, false>(op, zs + step * DP, ix);
+            TileGrad<T, Sh> g;
+#pragma unroll
+            for (int c = 0; c < D; ++c) g.gz[c] = T(0);
+#pragma unroll
+            for (int j = 0; j < G; ++j) g.gg[j] = T(0);
+#pragma unroll
+            for (int k = 0; k < (P > 0 ? P : 1); ++k) g.gc[k] = T(0);
+            tile_pullback<T, Sh>(st, ad, g, op.z, op.zg, op.zc);
+
+            // fold the letter classes into one d'-vector per lane
+            T v[DP2];
+#pragma unroll
+            for (int c = 0; c < DP2; ++c) v[c] = c < D ? g.gz[c] : T(0);
+#pragma unroll
+            for (int c = 0; c < D; ++c)
+                if (c / G == grp) v[c] += g.gg[c % G];
+#pragma unroll
+            for (int k = 0; k < P; ++k) {
+#pragma unroll
+                for (int c = 0; c < D; ++c)
+                    if (ix.p[k] == c) v[c] += g.gc[k];
+            }
+            warp_halving_reduce<T, DP2>(v, lane);
+            constexpr int REP = DP2 >= 32 ? 1 : 32 / DP2;   // lanes holding the same letter
+            constexpr int PER = DP2 >= 32 ? DP2 / 32 : 1;   // letters per lane
+            if ((lane & (REP - 1)) == 0) {
+                const int first = reduced_first_letter<DP2>(lane);
+#pragma unroll
+                for (int i = 0; i < PER; ++i)
+                    if (first + i < D) gbuf[step * D + first + i] = v[i];
+            }
+        }
+        __syncwarp();
+        // flush the chunk: one atomic per (step, channel)
+        for (int i = lane; i < cnt * D; i += 32) {
+            const int step = i / D, c = i - step * D;
+            const int j = j0 + step;
+            int m, cc;
+            bool keep;
+            if constexpr (FLAGS) {
+                if (pv.lead_lag) {
+                    m = j >> 1;
+                    const bool odd = j & 1;
+                    keep = odd ? (c < pv.d) : (c >= pv.d && c < 2 * pv.d);
+                    cc = odd ? c : c - pv.d;
+                } else {
+                    m = j;
+                    cc = c;
+                    keep = c < pv.d;
+                }
+            } else {
+                m = j;
+                cc = c;
+                keep = true;
+            }
+            if (keep) atomicAdd(gout + size_t(m) * pv.d + cc, gbuf[i]);
+        }
+        j1 = j0;
+    }
+}
+
+}  // namespace sigb200

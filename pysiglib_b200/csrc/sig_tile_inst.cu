@@ -1,0 +1,21 @@
+// One part of the register-tile kernel table (tile_table.h).  This file is compiled
+// SIG_TILE_PARTS times with -DSIG_TILE_PART=<k> so the variants build in parallel.
+#include "sig_tile_launch.cuh"
+#include "tile_table.h"
+
+#ifndef SIG_TILE_PART
+#error "compile with -DSIG_TILE_PART=<k>"
+#endif
+
+#define SIG_CAT2(a, b) a##b
+#define SIG_CAT(a, b) SIG_CAT2(a, b)
+
+namespace sigb200 {
+
+void SIG_CAT(register_tile_part_, SIG_TILE_PART)(std::vector<TileEntry>& table) {
+#define X(T, BWD, D, N, P, G) table.push_back(make_tile_entry<T, D, N, P, G>(BWD != 0));
+    SIG_CAT(SIG_TILE_PART_, SIG_TILE_PART)(X)
+#undef X
+}
+
+}  // namespace sigb200

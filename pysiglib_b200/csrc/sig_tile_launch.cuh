@@ -1,0 +1,85 @@
+// Host launchers and the registry entry type of the register-tile kernels.
+#pragma once
+
+#include <vector>
+
+#include "kernels.h"
+#include "runtime.h"
+#include "sig_tile.cuh"
+
+namespace sigb200 {
+
+constexpr int kTileWarpsPerBlock = 4;
+
+struct TileEntry {
+    bool is_double;
+    bool backward;
+    int D, N, P, G;
+    int units;       // execution units (threads) per path
+    int tile_values; // register-resident coefficients per unit
+    // forward:  fn(pv, out, nullptr, nullptr, ...);  backward: fn(pv, incr_grad, sig, derivs, ...)
+    void (*launch)(const void* pv, void* out, const void* sig, const void* derivs, uint64_t batch,
+                   uint32_t stride, bool scalar, bool flags, cudaStream_t stream);
+};
+
+inline unsigned tile_grid(uint64_t batch, int units) {
+    const uint64_t warps = batch * uint64_t((units + 31) / 32);
+    const uint64_t blocks = (warps + kTileWarpsPerBlock - 1) / kTileWarpsPerBlock;
+    if (blocks > 0x7fffffffull) throw std::out_of_range("launch grid too large");
+    return static_cast<unsigned>(blocks);
+}
+
+template <typename Kernel>
+inline void tile_set_smem(Kernel kernel, size_t smem) {
+    if (smem > 48 * 1024)
+        SIG_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+}
+
+template <typename T, int D, int N, int P, int G>
+void tile_forward_launch(const void* pv_, void* out, const void*, const void*, uint64_t batch, uint32_t stride,
+                         bool scalar, bool flags, cudaStream_t stream) {
+    using Sh = TileShape<D, N, P, G>;
+    constexpr int W = kTileWarpsPerBlock;
+    const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
+    const size_t smem = size_t(W) * kTileChunk * RowPad<T, D>::DP * sizeof(T);
+    const unsigned grid = tile_grid(batch, Sh::UNITS);
+    if (flags) {
+        tile_set_smem(tile_forward_kernel<T, Sh, true, W>, smem);
+        tile_forward_kernel<T, Sh, true, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), batch, stride, scalar);
+    } else {
+        tile_set_smem(tile_forward_kernel<T, Sh, false, W>, smem);
+        tile_forward_kernel<T, Sh, false, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), batch, stride, scalar);
+    }
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T, int D, int N, int P, int G>
+void tile_backward_launch(const void* pv_, void* incr_grad, const void* sig, const void* derivs, uint64_t batch,
+                          uint32_t stride, bool scalar, bool flags, cudaStream_t stream) {
+    using Sh = TileShape<D, N, P, G>;
+    constexpr int W = kTileWarpsPerBlock;
+    const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
+    const size_t smem = size_t(W) * kTileChunk * (RowPad<T, D>::DP + D) * sizeof(T);
+    const unsigned grid = tile_grid(batch, Sh::UNITS);
+    if (flags) {
+        tile_set_smem(tile_backward_kernel<T, Sh, true, W>, smem);
+        tile_backward_kernel<T, Sh, true, W><<<grid, W * 32, smem, stream>>>(
+            pv, static_cast<const T*>(sig), static_cast<const T*>(derivs), static_cast<T*>(incr_grad), batch, stride, scalar);
+    } else {
+        tile_set_smem(tile_backward_kernel<T, Sh, false, W>, smem);
+        tile_backward_kernel<T, Sh, false, W><<<grid, W * 32, smem, stream>>>(
+            pv, static_cast<const T*>(sig), static_cast<const T*>(derivs), static_cast<T*>(incr_grad), batch, stride, scalar);
+    }
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T, int D, int N, int P, int G>
+TileEntry make_tile_entry(bool backward) {
+    using Sh = TileShape<D, N, P, G>;
+    return TileEntry{sizeof(T) == 8, backward, D, N, P, G, Sh::UNITS, Sh::TS,
+                     backward ? &tile_backward_launch<T, D, N, P, G> : &tile_forward_launch<T, D, N, P, G>};
+}
+
+}  // namespace sigb200

@@ -1,0 +1,378 @@
+// Register-tile arithmetic of the signature kernels, shared by device code and by
+// a host build used for CPU-side testing of the tiling logic.
+//
+// Decomposition.  A level-k coefficient of the signature, indexed by the word
+// w = (i_1 .. i_k), is updated by one Horner step from the coefficients of the
+// prefixes of w only.  So the level structure splits into independent pieces: one
+// execution unit (a CUDA thread) owns
+//     * a prefix word p of length P ("chain": the P coefficients S(p_1), S(p_1 p_2), ..,
+//       kept redundantly by every unit that shares a prefix), and
+//     * below p, G consecutive children c0 .. c0+G-1 at level P+1 with their complete
+//       subtrees down to level N ("tile", depth Q = N - P, TS values held in registers).
+// Units never communicate in the forward pass.  In the backward pass the adjoint of a
+// chain coefficient is the sum of per-unit partial adjoints (the pull-back is linear in
+// the adjoint), so units again work independently and only the d'-vector of increment
+// gradients is summed across units.
+//
+// Arithmetic (reference: siglib/cpsig/cp_signature.h:464-499 forward step,
+// :1137-1187 reverse step; the thread-per-prefix idea is the one of
+// siglib/cusig/cu_signature_horner.cuh:27-216, re-tiled here so that a thread's useful
+// FMAs dominate the redundant chain work):
+//   for T = N..1:  W_1 = z/T, W_{l+1} = ((W_l + S_l)/(T-l)) (x) z,  S_T += (W_{T-1} + S_{T-1}) (x) z
+// The operation order inside a coefficient equals the reference's CPU order, so float32
+// results track it closely.
+#pragma once
+
+#if defined(__CUDACC__)
+#define SIG_HD __host__ __device__ __forceinline__
+#else
+#include <cmath>
+#define SIG_HD inline
+#endif
+
+namespace sigb200 {
+
+constexpr int cpow(int d, int k) {
+    int r = 1;
+    for (int i = 0; i < k; ++i) r *= d;
+    return r;
+}
+// 1 + d + .. + d^(k-1)
+constexpr int cgeom(int d, int k) {
+    int r = 0;
+    for (int i = 0; i < k; ++i) r = r * d + 1;
+    return r;
+}
+
+template <typename T> SIG_HD T sig_fma(T a, T b, T c);
+#if defined(__CUDA_ARCH__)
+template <> SIG_HD float sig_fma<float>(float a, float b, float c) { return fmaf(a, b, c); }
+template <> SIG_HD double sig_fma<double>(double a, double b, double c) { return fma(a, b, c); }
+#else
+template <> SIG_HD float sig_fma<float>(float a, float b, float c) { return ::fmaf(a, b, c); }
+template <> SIG_HD double sig_fma<double>(double a, double b, double c) { return ::fma(a, b, c); }
+#endif
+
+template <int D_, int N_, int P_, int G_>
+struct TileShape {
+    static constexpr int D = D_;   // augmented path dimension
+    static constexpr int N = N_;   // signature degree
+    static constexpr int P = P_;   // chain (prefix) length, 0 <= P < N
+    static constexpr int G = G_;   // children owned at level P+1, G divides D
+    static constexpr int Q = N - P;          // tile depth
+    static constexpr int NG = D / G;         // child groups per prefix
+    static constexpr int UNITS = cpow(D, P) * NG;  // execution units per path
+    // tile nodes at depth q (1..Q): G * D^(q-1); offset of depth q inside the tile array
+    static constexpr int nodes(int q) { return G * cpow(D, q - 1); }
+    static constexpr int off(int q) { return G * cgeom(D, q - 1); }
+    static constexpr int TS = G * cgeom(D, Q);       // tile values per unit
+    static constexpr int WS = G * cgeom(D, Q - 1) > G ? G * cgeom(D, Q - 1) : G;  // work values (depth < Q)
+    static_assert(P >= 0 && P < N, "chain length out of range");
+    static_assert(D % G == 0, "G must divide D");
+};
+
+template <typename T> SIG_HD T rcp_of(int k) { return T(1) / T(k); }
+
+// Per-unit state: chain coefficients ch[0..P] (ch[0] = 1) and the tile s[0..TS).
+template <typename T, typename Sh>
+struct TileState {
+    T ch[Sh::P + 1];
+    T s[Sh::TS];
+};
+
+// First segment: S_k = S_{k-1} (x) z / k   (siglib/cpsig/cp_signature.h:365-389)
+template <typename T, typename Sh>
+SIG_HD void tile_init_first(TileState<T, Sh>& st, const T (&z)[Sh::D], const T (&zg)[Sh::G],
+                            const T* zc /* [P] */) {
+    st.ch[0] = T(1);
+#pragma unroll
+    for (int k = 1; k <= Sh::P; ++k) st.ch[k] = zc[k - 1] * (st.ch[k - 1] * rcp_of<T>(k));
+#pragma unroll
+    for (int j = 0; j < Sh::G; ++j) st.s[j] = zg[j] * (st.ch[Sh::P] * rcp_of<T>(Sh::P + 1));
+#pragma unroll
+    for (int q = 2; q <= Sh::Q; ++q) {
+#pragma unroll
+        for (int j = 0; j < Sh::nodes(q - 1); ++j) {
+            const T v = st.s[Sh::off(q - 1) + j] * rcp_of<T>(Sh::P + q);
+#pragma unroll
+            for (int c = 0; c < Sh::D; ++c) st.s[Sh::off(q) + j * Sh::D + c] = z[c] * v;
+        }
+    }
+}
+
+// Chain part of target level T: returns h = W^{(T)}_{K}[p_1..p_K] and fills hist[k] = W_k + S_k.
+template <typename T, typename Sh, int K>
+SIG_HD T tile_chain(const T* ch, const T* zc, int target, T* hist) {
+    T h = T(0);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        const T a = h + ch[k];
+        if (hist) hist[k] = a;
+        h = zc[k] * (a * rcp_of<T>(target - k));
+    }
+    return h;
+}
+
+// One Horner step with increment z (zg = z at the unit's children, zc = z at its chain letters).
+template <typename T, typename Sh>
+SIG_HD void tile_update(TileState<T, Sh>& st, const T (&z)[Sh::D], const T (&zg)[Sh::G], const T* zc) {
+    constexpr int P = Sh::P, Q = Sh::Q, D = Sh::D, G = Sh::G;
+    T w[Sh::WS];
+#pragma unroll
+    for (int t = Q; t >= 1; --t) {
+        const int target = P + t;
+        const T base = tile_chain<T, Sh, P>(st.ch, zc, target, nullptr) + st.ch[P];
+        if (t == 1) {
+#pragma unroll
+            for (int j = 0; j < G; ++j) st.s[j] = sig_fma(zg[j], base, st.s[j]);
+        } else {
+            const T v0 = base * rcp_of<T>(t);
+#pragma unroll
+            for (int j = 0; j < G; ++j) w[j] = zg[j] * v0;
+#pragma unroll
+            for (int q = 2; q <= Q - 1; ++q) {
+                if (q <= t - 1) {
+#pragma unroll
+                    for (int j = 0; j < Sh::nodes(q - 1); ++j) {
+                        const T v = (w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j]) * rcp_of<T>(t - q + 1);
+#pragma unroll
+                        for (int c = 0; c < D; ++c) w[Sh::off(q) + j * D + c] = z[c] * v;
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 2; q <= Q; ++q) {
+                if (q == t) {
+#pragma unroll
+                    for (int j = 0; j < Sh::nodes(q - 1); ++j) {
+                        const T v = w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j];
+#pragma unroll
+                        for (int c = 0; c < D; ++c)
+                            st.s[Sh::off(q) + j * D + c] = sig_fma(z[c], v, st.s[Sh::off(q) + j * D + c]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int target = P; target >= 1; --target) {
+        T h = T(0);
+#pragma unroll
+        for (int k = 0; k < P; ++k)
+            if (k < target - 1) h = zc[k] * ((h + st.ch[k]) * rcp_of<T>(target - k));
+        st.ch[target] = sig_fma(zc[target - 1], h + st.ch[target - 1], st.ch[target]);
+    }
+}
+
+// Which words a unit owns.  Units of a path are numbered u = pw * NG + grp with pw the
+// chain word read as a base-D number (first letter most significant).
+template <typename Sh>
+struct UnitIndex {
+    int p[Sh::P > 0 ? Sh::P : 1];  // chain letters
+    int pw;                        // chain word
+    int c0;                        // first owned child letter at level P+1
+    bool chain_owner[Sh::P + 1];   // chain_owner[k]: this unit reports / seeds the level-k chain coefficient
+};
+
+template <typename Sh>
+SIG_HD UnitIndex<Sh> decode_unit(int u) {
+    UnitIndex<Sh> ix;
+    const int grp = u % Sh::NG;
+    ix.pw = u / Sh::NG;
+    ix.c0 = grp * Sh::G;
+    int rest = ix.pw;
+#pragma unroll
+    for (int k = Sh::P - 1; k >= 0; --k) {
+        ix.p[k] = rest % Sh::D;
+        rest /= Sh::D;
+    }
+    // level-k chain word is pw / D^(P-k); exactly one unit (all later letters and the group zero) owns it
+    ix.chain_owner[0] = false;
+#pragma unroll
+    for (int k = 1; k <= Sh::P; ++k) ix.chain_owner[k] = grp == 0 && (ix.pw % cpow(Sh::D, Sh::P - k)) == 0;
+    return ix;
+}
+
+// Writes the unit's coefficients into a signature laid out with the scalar term at S[0]
+// (S may point one element before a scalar-free buffer; S[0] is then never touched here).
+template <typename T, typename Sh>
+SIG_HD void tile_store(const TileState<T, Sh>& st, const UnitIndex<Sh>& ix, T* S) {
+#pragma unroll
+    for (int k = 1; k <= Sh::P; ++k)
+        if (ix.chain_owner[k]) S[cgeom(Sh::D, k) + ix.pw / cpow(Sh::D, Sh::P - k)] = st.ch[k];
+#pragma unroll
+    for (int q = 1; q <= Sh::Q; ++q) {
+        T* dst = S + cgeom(Sh::D, Sh::P + q) + (ix.pw * Sh::D + ix.c0) * cpow(Sh::D, q - 1);
+#pragma unroll
+        for (int j = 0; j < Sh::nodes(q); ++j) dst[j] = st.s[Sh::off(q) + j];
+    }
+}
+
+// Adjoint state of one unit: partial adjoints of the chain (ac[0] unused) and the tile.
+template <typename T, typename Sh>
+struct TileAdjoint {
+    T ac[Sh::P + 1];
+    T a[Sh::TS];
+};
+
+// Loads the final signature and the seeds (dLoss/dSignature) of a unit; chain adjoints
+// are taken by the owning unit only, so that their sum over units is the true adjoint.
+template <typename T, typename Sh>
+SIG_HD void tile_load(TileState<T, Sh>& st, TileAdjoint<T, Sh>& ad, const UnitIndex<Sh>& ix, const T* S,
+                      const T* dS) {
+    st.ch[0] = T(1);
+    ad.ac[0] = T(0);
+#pragma unroll
+    for (int k = 1; k <= Sh::P; ++k) {
+        const int idx = cgeom(Sh::D, k) + ix.pw / cpow(Sh::D, Sh::P - k);
+        st.ch[k] = S[idx];
+        ad.ac[k] = ix.chain_owner[k] ? dS[idx] : T(0);
+    }
+#pragma unroll
+    for (int q = 1; q <= Sh::Q; ++q) {
+        const int base = cgeom(Sh::D, Sh::P + q) + (ix.pw * Sh::D + ix.c0) * cpow(Sh::D, q - 1);
+#pragma unroll
+        for (int j = 0; j < Sh::nodes(q); ++j) {
+            st.s[Sh::off(q) + j] = S[base + j];
+            ad.a[Sh::off(q) + j] = dS[base + j];
+        }
+    }
+}
+
+// Per-step increment gradient of one unit, by letter class:
+//   gz[c]  letters 0..D-1 reached through tile depths >= 2 (static indices),
+//   gg[j]  letter c0 + j (the unit's own children at depth 1),
+//   gc[k]  chain letter p_{k+1}.
+template <typename T, typename Sh>
+struct TileGrad {
+    T gz[Sh::D];
+    T gg[Sh::G];
+    T gc[Sh::P > 0 ? Sh::P : 1];
+};
+
+// Pull the adjoint back through one Horner step taken with increment z from the
+// (already rewound) state st.  Accumulates into ad and into g (which the caller zeroes).
+template <typename T, typename Sh>
+SIG_HD void tile_pullback(const TileState<T, Sh>& st, TileAdjoint<T, Sh>& ad, TileGrad<T, Sh>& g,
+                          const T (&z)[Sh::D], const T (&zg)[Sh::G], const T* zc) {
+    constexpr int P = Sh::P, Q = Sh::Q, D = Sh::D, G = Sh::G;
+    T hist[P > 0 ? P : 1];
+    // targets inside the chain, ascending
+#pragma unroll
+    for (int target = 1; target <= P; ++target) {
+        // forward: ch[target] += (h_{target-1} + ch[target-1]) * zc[target-1]
+        T h = T(0);
+#pragma unroll
+        for (int k = 0; k < P; ++k)
+            if (k < target) {
+                hist[k] = h + st.ch[k];
+                if (k < target - 1) h = zc[k] * (hist[k] * rcp_of<T>(target - k));
+            }
+        T y = ad.ac[target];
+        g.gc[target - 1] = sig_fma(y, hist[target - 1], g.gc[target - 1]);
+        y *= zc[target - 1];
+#pragma unroll
+        for (int k = P - 1; k >= 0; --k)
+            if (k <= target - 2) {
+                ad.ac[k + 1] += y;  // adjoint of ch[k+1] through hist[k+1]
+                const T r = rcp_of<T>(target - k);
+                g.gc[k] = sig_fma(y, hist[k] * r, g.gc[k]);
+                y *= r * zc[k];
+            }
+        // for k == target-1 the adjoint of ch[target-1] is added here:
+        // (the loop above adds into ac[k+1] for k <= target-2, i.e. ac[1..target-1])
+    }
+    // targets inside the tile, ascending depth
+    T w[Sh::WS];
+    T wa[Sh::WS];
+#pragma unroll
+    for (int t = 1; t <= Q; ++t) {
+        const int target = P + t;
+        const T hP = tile_chain<T, Sh, P>(st.ch, zc, target, hist);
+        const T base = hP + st.ch[P];
+        T wa0 = T(0);
+        if (t == 1) {
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                g.gg[j] = sig_fma(ad.a[j], base, g.gg[j]);
+                wa0 = sig_fma(ad.a[j], zg[j], wa0);
+            }
+        } else {
+            const T v0 = base * rcp_of<T>(t);
+#pragma unroll
+            for (int j = 0; j < G; ++j) w[j] = zg[j] * v0;
+#pragma unroll
+            for (int q = 2; q <= Q - 1; ++q) {
+                if (q <= t - 1) {
+#pragma unroll
+                    for (int j = 0; j < Sh::nodes(q - 1); ++j) {
+                        const T v = (w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j]) * rcp_of<T>(t - q + 1);
+#pragma unroll
+                        for (int c = 0; c < D; ++c) w[Sh::off(q) + j * D + c] = z[c] * v;
+                    }
+                }
+            }
+            // depth t: S_t[j, c] += (w_{t-1}[j] + s_{t-1}[j]) * z[c]
+#pragma unroll
+            for (int q = 2; q <= Q; ++q) {
+                if (q == t) {
+#pragma unroll
+                    for (int j = 0; j < Sh::nodes(q - 1); ++j) {
+                        const T v = w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j];
+                        T acc = T(0);
+#pragma unroll
+                        for (int c = 0; c < D; ++c) {
+                            const T a = ad.a[Sh::off(q) + j * D + c];
+                            g.gz[c] = sig_fma(a, v, g.gz[c]);
+                            acc = sig_fma(a, z[c], acc);
+                        }
+                        wa[Sh::off(q - 1) + j] = acc;
+                    }
+                }
+            }
+            // depths t-1 .. 2: node (j, c) = child c of depth-(q-1) node j
+#pragma unroll
+            for (int q = Q - 1; q >= 2; --q) {
+                if (q <= t - 1) {
+                    const T r = rcp_of<T>(t - q + 1);
+#pragma unroll
+                    for (int j = 0; j < Sh::nodes(q - 1); ++j) {
+                        const T v = (w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j]) * r;
+                        T acc = T(0);
+#pragma unroll
+                        for (int c = 0; c < D; ++c) {
+                            const T x = wa[Sh::off(q) + j * D + c];
+                            ad.a[Sh::off(q) + j * D + c] += x;
+                            g.gz[c] = sig_fma(x, v, g.gz[c]);
+                            acc = sig_fma(x, z[c], acc);
+                        }
+                        wa[Sh::off(q - 1) + j] = acc * r;
+                    }
+                }
+            }
+            // depth 1: w_1[j] = zg[j] * (base / t)
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                const T x = wa[j];
+                ad.a[j] += x;
+                g.gg[j] = sig_fma(x, v0, g.gg[j]);
+                wa0 = sig_fma(x, zg[j], wa0);
+            }
+            wa0 *= rcp_of<T>(t);
+        }
+        // chain: base = h_P + ch[P]
+        if (P > 0) {
+            T y = wa0;
+            ad.ac[P] += y;
+#pragma unroll
+            for (int k = P - 1; k >= 0; --k) {
+                const T r = rcp_of<T>(target - k);
+                g.gc[k] = sig_fma(y, hist[k] * r, g.gc[k]);
+                y *= r * zc[k];
+                if (k >= 1) ad.ac[k] += y;
+            }
+        }
+    }
+}
+
+}  // namespace sigb200

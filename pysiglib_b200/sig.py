@@ -1,0 +1,96 @@
+"""``sig``: truncated signature of a path or a batch of paths, computed on a B200.
+
+Python surface of the reference's ``pysiglib.sig`` (``pysiglib/sig.py:128-312``): same
+parameters, defaults, type checks, error texts and result layout."""
+import ctypes
+import warnings
+from typing import Union
+
+import numpy as np
+import torch
+
+from . import load_cusig
+from .data_handlers import Output, PathInput, check_correction_unsupported
+from .error_codes import err_msg
+from .param_checks import check_n_jobs, check_non_neg, check_type
+from .sig_length import sig_length
+
+NONFINITE_WARNING = ("sig produced NaN or Inf values. This is typically caused by paths with large "
+                     "increments, leading to numerical overflow. Consider normalizing your paths.")
+
+
+def _current_stream(array):
+    if isinstance(array, torch.Tensor) and array.is_cuda:
+        return ctypes.c_void_p(torch.cuda.current_stream(array.device).cuda_stream)
+    return ctypes.c_void_p(None)
+
+
+def sig(
+        path: Union[np.ndarray, torch.Tensor],
+        degree: int,
+        *,
+        time_aug: bool = False,
+        lead_lag: bool = False,
+        end_time: float = 1.,
+        horner: bool = True,
+        scalar_term: bool = False,
+        correction=None,
+        n_jobs: int = 1
+) -> Union[np.ndarray, torch.Tensor]:
+    """Truncated signature of ``path`` up to level ``degree``.
+
+    ``path`` has shape ``(length, dimension)`` or ``(..., length, dimension)``; the result has
+    shape ``(..., S)`` with ``S = sum_{k=1..degree} D^k`` where ``D`` is the dimension after the
+    optional transforms.  Level ``k`` occupies ``D^k`` consecutive entries; inside a level the
+    coefficient of the word ``(i_1, .., i_k)`` sits at ``i_1 D^(k-1) + .. + i_k``.
+
+    :param path: ``numpy.ndarray`` or ``torch.Tensor`` of dtype float32 / float64.  CUDA tensors
+        are processed in place on their device; NumPy arrays and CPU tensors are streamed
+        through the current CUDA device and the result is returned on the host.
+    :param degree: truncation level, a non-negative ``int``.
+    :param time_aug: append time as a last channel, running from 0 to ``end_time``.
+    :param lead_lag: apply the lead-lag transform (``2*length - 1`` points, channels
+        ``[lag, lead]``) before taking the signature.
+    :param end_time: final time of the time channel (``float``).
+    :param horner: accepted for compatibility; the Horner scheme is always used.
+    :param scalar_term: include the constant 1 of level 0 as the first entry.
+    :param correction: must be ``None`` or empty (per-segment corrections are not implemented).
+    :param n_jobs: accepted for compatibility (validated, otherwise ignored on the GPU).
+    :return: array of the same kind, dtype and device as ``path``.
+
+    A ``RuntimeWarning`` is issued when the result contains NaN or Inf.
+
+    Example::
+
+        import torch, pysiglib_b200
+        x = torch.rand(32, 100, 5, device="cuda")
+        s = pysiglib_b200.sig(x, 4)            # (32, 780)
+    """
+    check_type(degree, "degree", int)
+    check_non_neg(degree, "degree")
+    check_type(horner, "horner", bool)
+    check_type(time_aug, "time_aug", bool)
+    check_type(lead_lag, "lead_lag", bool)
+    check_type(end_time, "end_time", float)
+    check_type(scalar_term, "scalar_term", bool)
+    check_n_jobs(n_jobs)
+    check_correction_unsupported(correction)
+
+    data = PathInput(path, time_aug, lead_lag, end_time)
+    n = sig_length(data.dimension, degree, scalar_term=scalar_term)
+    result = Output(data, (n,))
+    if data.batch_size == 0:
+        return result.array
+
+    bad = ctypes.c_int(0)
+    code = load_cusig.fn("sigb200_signature", data.dtype)(
+        data.pointer, result.pointer, data.batch_size, data.data_dimension, data.data_length, degree,
+        time_aug, lead_lag, end_time, scalar_term, _current_stream(data.array), 1, ctypes.byref(bad))
+    if code:
+        raise Exception("Error in pysiglib.sig: " + err_msg(code))
+    if bad.value:
+        warnings.warn(NONFINITE_WARNING, RuntimeWarning, stacklevel=2)
+    return result.array
+
+
+signature = sig
