@@ -179,8 +179,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--batch", type=int, default=None, help="override the batch size (profiling on a small case)")
+    ap.add_argument("--length", type=int, default=None, help="override the path length (profiling on a small case)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
+    if args.batch:
+        cfg["B"] = args.batch
+    if args.length:
+        cfg["L"] = args.length
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

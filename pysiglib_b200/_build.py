@@ -41,8 +41,8 @@ def _units():
     return units
 
 
-def _stamp():
-    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+def _stamp(dev=False):
+    h = hashlib.sha256((" ".join(NVCC_FLAGS) + (" dev" if dev else "")).encode())
     for name in sorted(os.listdir(CSRC)):
         if name.endswith((".h", ".cuh", ".cu")):
             with open(os.path.join(CSRC, name), "rb") as f:
@@ -54,6 +54,7 @@ def _stamp():
 
 def _compile(unit):
     obj, src, extra = unit
+    extra = extra + _EXTRA
     cmd = [_nvcc()] + NVCC_FLAGS + extra + ["-c", os.path.join(CSRC, src), "-o", os.path.join(OBJ, obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
@@ -61,11 +62,20 @@ def _compile(unit):
     return obj
 
 
-def build(force=False, jobs=None, verbose=False):
-    """Compile every CUDA translation unit for sm_100a and link libcusig.so; returns its path."""
+_EXTRA = []
+
+
+def build(force=False, jobs=None, verbose=False, dev=None):
+    """Compile every CUDA translation unit for sm_100a and link libcusig.so; returns its path.
+
+    dev=True (or SIGB200_TILE_DEV=1) compiles only the development subset of the
+    register-tile table (tile_table_dev.h) for quick iteration; the default is the full table."""
+    if dev is None:
+        dev = os.environ.get("SIGB200_TILE_DEV", "0") == "1"
+    _EXTRA[:] = ["-DSIG_TILE_DEV"] if dev else []
     os.makedirs(OBJ, exist_ok=True)
     os.makedirs(LIB_DIR, exist_ok=True)
-    stamp, stamp_file = _stamp(), os.path.join(LIB_DIR, "stamp.txt")
+    stamp, stamp_file = _stamp(dev), os.path.join(LIB_DIR, "stamp.txt")
     if not force and os.path.exists(LIB) and os.path.exists(stamp_file):
         with open(stamp_file) as f:
             if f.read().strip() == stamp:
@@ -90,5 +100,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--jobs", type=int, default=None)
+    ap.add_argument("--dev", action="store_true", help="compile only the development subset of the tile table")
     args = ap.parse_args()
-    print(build(force=args.force, jobs=args.jobs, verbose=True))
+    print(build(force=args.force, jobs=args.jobs, verbose=True, dev=True if args.dev else None))

@@ -226,12 +226,18 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
         for (int i = 0; i < Sh::TS; ++i) ad.a[i] = T(0);
     }
 
+    // 1 for the unit's own child group, 0 for the others (folds gg into the static letters)
+    T gmask[Sh::NG];
+#pragma unroll
+    for (int m = 0; m < Sh::NG; ++m) gmask[m] = grp == m ? T(1) : T(0);
+
     StepOperands<T, Sh> op;
     for (int j1 = pv.steps; j1 > 0;) {
         const int j0 = max(0, j1 - kTileChunk);
         const int cnt = j1 - j0;
         __syncwarp();
         stage_increments<T, Sh, FLAGS>(zs, pv, x, j0, cnt, lane);
+        for (int i = lane; i < cnt * D; i += 32) gbuf[i] = T(0);
         __syncwarp();
         for (int step = cnt - 1; step >= 0; --step) {
             load_step<T, Sh, true>(op, zs + step * DP, ix);
@@ -246,27 +252,44 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
             for (int k = 0; k < (P > 0 ? P : 1); ++k) g.gc[k] = T(0);
             tile_pullback<T, Sh>(st, ad, g, op.z, op.zg, op.zc);
 
-            // fold the letter classes into one d'-vector per lane
+            // Sum the per-unit gradients over the warp into gbuf[step][letter] (zeroed at the
+            // start of the chunk; every contribution below is a shared-memory atomic add).
+            // (1) letters with static indices, plus the unit's own children through a 0/1 mask
             T v[DP2];
 #pragma unroll
-            for (int c = 0; c < DP2; ++c) v[c] = c < D ? g.gz[c] : T(0);
-#pragma unroll
-            for (int c = 0; c < D; ++c)
-                if (c / G == grp) v[c] += g.gg[c % G];
-#pragma unroll
-            for (int k = 0; k < P; ++k) {
-#pragma unroll
-                for (int c = 0; c < D; ++c)
-                    if (ix.p[k] == c) v[c] += g.gc[k];
+            for (int c = 0; c < DP2; ++c) {
+                if (c >= D) v[c] = T(0);
+                else if constexpr (Sh::NG == 1) v[c] = g.gz[c] + g.gg[c];
+                else v[c] = sig_fma(gmask[c / G], g.gg[c % G], g.gz[c]);
             }
             warp_halving_reduce<T, DP2>(v, lane);
             constexpr int REP = DP2 >= 32 ? 1 : 32 / DP2;   // lanes holding the same letter
             constexpr int PER = DP2 >= 32 ? DP2 / 32 : 1;   // letters per lane
+            T* grow = gbuf + step * D;
             if ((lane & (REP - 1)) == 0) {
                 const int first = reduced_first_letter<DP2>(lane);
 #pragma unroll
                 for (int i = 0; i < PER; ++i)
-                    if (first + i < D) gbuf[step * D + first + i] = v[i];
+                    if (first + i < D) atomicAdd(grow + first + i, v[i]);
+            }
+            // (2) chain letters: units sharing letter p[k] are STRIDE consecutive units, so a
+            // partial butterfly sums them before one lane per group adds the total
+#pragma unroll
+            for (int k = 0; k < P; ++k) {
+                const int stride = cpow(D, P - 1 - k) * Sh::NG;
+                T x = g.gc[k];
+                if (stride % 32 == 0) {
+#pragma unroll
+                    for (int m = 16; m >= 1; m >>= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
+                    if (lane == 0) atomicAdd(grow + ix.p[k], x);
+                } else if (32 % stride == 0) {
+#pragma unroll
+                    for (int m = 1; m < 32; m <<= 1)
+                        if (m < stride) x += __shfl_xor_sync(0xffffffffu, x, m);
+                    if ((lane & (stride - 1)) == 0) atomicAdd(grow + ix.p[k], x);
+                } else {
+                    atomicAdd(grow + ix.p[k], x);
+                }
             }
         }
         __syncwarp();

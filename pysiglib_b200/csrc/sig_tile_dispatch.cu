@@ -3,7 +3,11 @@
 #include <mutex>
 
 #include "sig_tile_launch.cuh"
+#ifdef SIG_TILE_DEV
+#include "tile_table_dev.h"  // development subset (quick builds)
+#else
 #include "tile_table.h"
+#endif
 
 namespace sigb200 {
 

@@ -68,3 +68,24 @@ def assert_grad_close(actual, expected, rtol, what="grad"):
     err = np.abs(a - b) / np.maximum(np.maximum(np.abs(b), floor), 1e-300)
     worst = err.max() if err.size else 0.0
     assert worst <= rtol, "%s: max scaled rel err %.3e > %.1e" % (what, worst, rtol)
+
+
+def assert_grad_parity(actual, oracle_same_dtype, oracle_f64, rtol, what="grad"):
+    """Gradient parity.  float64: per-coefficient relative check against the oracle.
+    float32: the reverse sweep subtracts increment gradients that can be orders of
+    magnitude larger than the result, so two correct float32 implementations differ by
+    rounding noise on the scale of those intermediates.  The check is then twofold: close
+    to the float32 oracle up to that noise, and no less accurate than it when both are
+    measured against the float64 oracle (error <= 3x the oracle's own float32 error + rtol)."""
+    a = np.asarray(actual, dtype=np.float64)
+    if np.asarray(actual).dtype == np.float64:
+        assert_grad_close(a, oracle_same_dtype, rtol, what)
+        return
+    truth = np.asarray(oracle_f64, dtype=np.float64).reshape(a.shape[0], -1)
+    ref32 = np.asarray(oracle_same_dtype, dtype=np.float64).reshape(a.shape[0], -1)
+    a = a.reshape(a.shape[0], -1)
+    floor = np.maximum(np.abs(truth).max(axis=1, keepdims=True), 1e-300)
+    err_ours = (np.abs(a - truth) / floor).max()
+    err_ref = (np.abs(ref32 - truth) / floor).max()
+    assert err_ours <= 3 * err_ref + rtol, "%s: float32 error %.3e vs reference-order float32 error %.3e" % (
+        what, err_ours, err_ref)
