@@ -107,6 +107,26 @@ int sigb200_sig_backprop_sharded_d(const double* path, double* out, const double
                                    bool time_aug, bool lead_lag, double end_time, bool scalar_term,
                                    const int* devices, int n_devices);
 
+/* sig_backprop without any device-memory allocation, for hosts that cannot allocate when they
+ * need the gradient: processes whose own allocator already owns the GPU's memory (a late
+ * cudaMalloc can fail there), and latency-critical loops (cudaMalloc / cudaFree synchronise the
+ * device).  This entry point has no counterpart in the reference.
+ * The increment-gradient scratch (batch * (length-1) * dimension values) lives in a static
+ * 32 MiB device buffer inside the library (sigb200_noalloc_scratch_bytes()); larger requests,
+ * host pointers and shapes outside the register-tile kernel table are rejected with code 2.
+ * The first call on a device looks the buffer up (cudaGetSymbolAddress) and should come before
+ * any stream capture.  All calls share the buffer: the used part is cleared on `stream` first,
+ * and calls whose GPU work overlaps race on it.  Asynchronous on `stream` unless synchronize != 0. */
+int sigb200_sig_backprop_noalloc_f(const float* path, float* out, const float* sig_derivs, const float* sig,
+                                   uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                                   bool time_aug, bool lead_lag, float end_time, bool scalar_term, void* stream,
+                                   int synchronize);
+int sigb200_sig_backprop_noalloc_d(const double* path, double* out, const double* sig_derivs, const double* sig,
+                                   uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
+                                   bool time_aug, bool lead_lag, double end_time, bool scalar_term, void* stream,
+                                   int synchronize);
+uint64_t sigb200_noalloc_scratch_bytes(void);
+
 /* Number of coefficients of a signature, scalar term included; 0 on overflow.
  * Same contract as the CPU library's sig_length (siglib/cpsig/cp_utils.cpp:91-105). */
 uint64_t sigb200_sig_length(uint64_t dimension, uint64_t degree);

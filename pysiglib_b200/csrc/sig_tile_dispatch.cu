@@ -83,6 +83,27 @@ bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* s
     return true;
 }
 
+// Tile backward for callers that bring their own scratch and SM count (used by the
+// no-alloc entry points; touches neither the device context nor the memory pool).
+template <typename T>
+bool launch_tile_backward_prealloc(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
+                                   T end_time, T* incr_grad, int sm_count, cudaStream_t stream) {
+    const TileEntry* e = choose(sizeof(T) == 8, true, s, sm_count);
+    if (!e) return false;
+    const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
+    const uint64_t g_elems = s.batch * (s.data_len - 1) * s.data_dim;
+    SIG_CUDA_CHECK(cudaMemsetAsync(incr_grad, 0, g_elems * sizeof(T), stream));
+    e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term,
+              s.time_aug || s.lead_lag, stream);
+    launch_increment_to_point_grad<T>(incr_grad, out, s.batch, s.data_len, s.data_dim, stream);
+    return true;
+}
+
+template bool launch_tile_backward_prealloc<float>(const float*, float*, const float*, const float*, const SigShape&,
+                                                   float, float*, int, cudaStream_t);
+template bool launch_tile_backward_prealloc<double>(const double*, double*, const double*, const double*,
+                                                    const SigShape&, double, double*, int, cudaStream_t);
+
 #define INSTANTIATE(T)                                                                              \
     template bool tile_forward_available<T>(const SigShape&);                                       \
     template bool tile_backward_available<T>(const SigShape&);                                      \

@@ -50,6 +50,8 @@ def _bind(lib):
     lib.sigb200_kernel_family.restype = c_char_p
     lib.sigb200_fma_peak.argtypes = (c_int, c_void_p, c_int, c_int, c_void_p)
     lib.sigb200_fma_peak.restype = c_int
+    lib.sigb200_noalloc_scratch_bytes.argtypes = ()
+    lib.sigb200_noalloc_scratch_bytes.restype = c_uint64
     lib.sigb200_launch_count.argtypes = ()
     lib.sigb200_launch_count.restype = c_uint64
     for suffix, real in (("f", c_float), ("d", c_double)):
@@ -69,6 +71,10 @@ def _bind(lib):
                       c_void_p, c_int, POINTER(c_int))
         f.restype = c_int
         f = getattr(lib, "sigb200_sig_backprop_" + suffix)
+        f.argtypes = (ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real, c_bool,
+                      c_void_p, c_int)
+        f.restype = c_int
+        f = getattr(lib, "sigb200_sig_backprop_noalloc_" + suffix)
         f.argtypes = (ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real, c_bool,
                       c_void_p, c_int)
         f.restype = c_int
