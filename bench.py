@@ -354,13 +354,12 @@ def main():
         pass
     path_bytes, sig_bytes = b_local * L * d * esize, b_local * S * esize
     roof_f = roof(i_fwd, f_fwd, fwd_ms, path_bytes + sig_bytes)
-    roof_f["kernel"] = "tile_forward_kernel" if load_cusig.kernel_family(d, N, dtype=name) == "tile" else "generic_forward_kernel"
+    roof_f["kernel"] = load_cusig.describe_plan(b_local, d, L, N, dtype=name)
     roofline = roof_f
     roof_b = None
     if fwdbwd:
         roof_b = roof(i_bwd, f_bwd, bwd_ms, 2 * path_bytes + 2 * sig_bytes)
-        roof_b["kernel"] = ("tile_backward_kernel" if load_cusig.kernel_family(d, N, dtype=name, backward=True) == "tile"
-                            else "generic_backward_kernel")
+        roof_b["kernel"] = load_cusig.describe_plan(b_local, d, L, N, dtype=name, backward=True)
         if dominant_bwd:
             roofline = roof_b
     roofline["peak_source"] = ("FMA-pipe peak measured in this run (register-resident FMA loop); HBM peak %s"

@@ -134,10 +134,21 @@ uint64_t sigb200_sig_length(uint64_t dimension, uint64_t degree);
 /* 0 = automatic kernel choice (default), 1 = shape-generic kernels only. */
 void sigb200_set_kernel_policy(int policy);
 
+/* Register-tile variant choice, for tests and tuning: 0 automatic (default), 1 always the biggest
+ * tile, 2 always the smallest, 3 automatic but without time segmentation of the forward sweep,
+ * 4 biggest tile with the forward sweep always cut into three time segments (1-3 never segment). */
+void sigb200_set_tile_preference(int preference);
+
 /* Name of the kernel family the forward (backward = 1) pass would use for this shape:
  * "trivial", "tile", "generic".  Static string. */
 const char* sigb200_kernel_family(uint64_t dimension, uint64_t degree, bool time_aug, bool lead_lag,
                                   int is_double, int backward);
+
+/* Writes a description of the kernel variant this call shape would run on the current device
+ * (tile parameters, time segments, resident CTAs per SM) into `buffer`.  Diagnostic only. */
+int sigb200_describe_plan(char* buffer, uint64_t buffer_len, uint64_t batch_size, uint64_t dimension,
+                          uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, int is_double,
+                          int backward);
 
 /* FMA-pipe peak probe for the benchmark: `blocks` CTAs x 256 threads x iters x 64 independent
  * register-resident FMAs in float (is_double = 0) or double; `sink` is any 8-byte device

@@ -5,7 +5,10 @@
 // so that pysiglib/load_siglib.py:76-130,484-494 can load this library unchanged.
 // Every other symbol that loader resolves at import time is exported as a stub
 // that fails with code 10, so the import succeeds and only this path is served.
+#include <algorithm>
 #include <cstdint>
+#include <cstring>
+#include <string>
 #include <thread>
 #include <vector>
 
@@ -220,6 +223,8 @@ SIG_API uint64_t sigb200_sig_length(uint64_t dimension, uint64_t degree) {
 
 SIG_API void sigb200_set_kernel_policy(int policy) { set_kernel_policy(policy); }
 
+SIG_API void sigb200_set_tile_preference(int preference) { set_tile_preference(preference); }
+
 SIG_API const char* sigb200_kernel_family(uint64_t dimension, uint64_t degree, bool time_aug, bool lead_lag,
                                           int is_double, int backward) {
     try {
@@ -234,6 +239,23 @@ SIG_API const char* sigb200_kernel_family(uint64_t dimension, uint64_t degree, b
     } catch (...) {
         return "invalid";
     }
+}
+
+SIG_API int sigb200_describe_plan(char* buffer, uint64_t buffer_len, uint64_t batch_size, uint64_t dimension,
+                                  uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, int is_double,
+                                  int backward) {
+    SIG_SAFE_CALL(
+        const SigShape s = make_shape(batch_size, dimension, length, degree, time_aug, lead_lag, false);
+        std::string text;
+        if (!backward && (s.len <= 1 || degree <= 1 || s.dim == 1)) text = "closed form";
+        else if (backward && (s.len <= 1 || degree == 0)) text = "zero fill";
+        else if (kernel_policy() != 0) text = "generic";
+        else text = describe_tile_plan(is_double != 0, backward != 0, s);
+        if (buffer && buffer_len) {
+            const size_t n = std::min<size_t>(text.size(), buffer_len - 1);
+            std::memcpy(buffer, text.data(), n);
+            buffer[n] = 0;
+        });
 }
 
 SIG_API uint64_t sigb200_launch_count(void) { return launch_count(); }

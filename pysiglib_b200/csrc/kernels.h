@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <string>
 
 #include "common.h"
 
@@ -48,6 +49,16 @@ bool tile_backward_available(const SigShape& s);
 template <typename T>
 bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
                           T end_time, T* incr_grad, cudaStream_t stream);
+
+// What the tile dispatcher would launch for this shape on the current device ("generic" if none).
+std::string describe_tile_plan(bool is_double, bool backward, const SigShape& s);
+
+// out[b] <- seg[b][0] (x) seg[b][1] (x) .. (x) seg[b][nseg-1]  (Chen products truncated at the
+// degree), pairwise in ceil(log2 nseg) launches.  seg is (batch, nseg, S) without scalar terms;
+// tmp holds chen_combine_tmp_elems(s, nseg) values.
+uint64_t chen_combine_tmp_elems(const SigShape& s, int nseg);
+template <typename T>
+void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int nseg, cudaStream_t stream);
 
 // out[t] = g[t-1] - g[t] over the raw path (g = increment gradients, (batch, L-1, d))
 template <typename T>

@@ -15,6 +15,7 @@ std::mutex g_contexts_mu;
 std::map<int, std::unique_ptr<DeviceContext>> g_contexts;
 std::atomic<int> g_policy{0};
 std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_tile_pref{0};
 
 }  // namespace
 
@@ -29,6 +30,9 @@ const char* last_error() noexcept { return tls_error; }
 
 void set_kernel_policy(int policy) noexcept { g_policy.store(policy); }
 int kernel_policy() noexcept { return g_policy.load(); }
+
+void set_tile_preference(int pref) noexcept { g_tile_pref.store(pref); }
+int tile_preference() noexcept { return g_tile_pref.load(); }
 
 void count_launch(uint64_t n) noexcept { g_launches.fetch_add(n, std::memory_order_relaxed); }
 uint64_t launch_count() noexcept { return g_launches.load(std::memory_order_relaxed); }

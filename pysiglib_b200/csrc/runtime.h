@@ -73,6 +73,11 @@ void shutdown_runtime() noexcept;
 // to exercise the fallback on shapes the tile kernels would otherwise take).
 void set_kernel_policy(int policy) noexcept;
 
+// Tile-variant override for tests and tuning: 0 automatic, 1 biggest tile, 2 smallest tile,
+// 3 automatic without time segmentation, 4 biggest tile with forced time segmentation.
+void set_tile_preference(int pref) noexcept;
+int tile_preference() noexcept;
+
 // Launch accounting (sigb200_launch_count).
 void count_launch(uint64_t n = 1) noexcept;
 uint64_t launch_count() noexcept;

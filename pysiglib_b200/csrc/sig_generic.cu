@@ -280,6 +280,45 @@ generic_backward_kernel(PathView<T> pv, T* out, const T* sig_derivs, const T* si
     }
 }
 
+// One round of the pairwise joining of segment signatures with Chen's identity
+// (reference arithmetic: siglib/cpsig/cp_sig_combine.h:34-66; here out of place, one thread
+// per output coefficient, so all levels and all pairs of the batch run in one launch).
+// in: (batch, n, slen) scalar-free; out: (batch, ceil(n/2), .): out[b][j] = in[b][2j] (x) in[b][2j+1]
+// (a last unpaired segment is copied).
+//   C_m[w] = A_m[w] + sum_{i=m-1..1} A_i[w_1..w_i] * B_{m-i}[w_{i+1}..w_m] + B_m[w]
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads)
+chen_pair_kernel(const T* __restrict__ in, int n, T* __restrict__ out, uint64_t out_stride, bool out_scalar,
+                 uint64_t total, uint32_t slen, int N, LevelIndex lev) {
+    __shared__ uint32_t li[kMaxDegree + 2];
+    for (unsigned i = threadIdx.x; i < unsigned(N + 2); i += blockDim.x) li[i] = lev.li[i];
+    __syncthreads();
+    const uint64_t gid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= total) return;
+    const int n2 = (n + 1) / 2;
+    const uint64_t vb = gid / slen;                       // b * n2 + j
+    const uint32_t pos = uint32_t(gid - vb * slen) + 1;   // position in the scalar-term layout
+    const uint64_t b = vb / uint64_t(n2);
+    const int j = int(vb - b * uint64_t(n2));
+    const T* a = in + (b * uint64_t(n) + uint64_t(2 * j)) * slen - 1;
+    T acc = a[pos];
+    if (2 * j + 1 < n) {
+        const T* bb = a + slen;
+        int m = 1;
+        while (m < N && pos >= li[m + 1]) ++m;
+        const uint32_t idx = pos - li[m];
+        for (int i = m - 1; i >= 1; --i) {
+            const uint32_t pw = li[m - i + 1] - li[m - i];  // d^(m-i)
+            const uint32_t left = idx / pw;
+            acc = fma_t(a[li[i] + left], bb[li[m - i] + (idx - left * pw)], acc);
+        }
+        acc += bb[pos];
+    }
+    T* c = out + vb * out_stride - (out_scalar ? 0 : 1);
+    c[pos] = acc;
+    if (out_scalar && pos == 1) c[0] = T(1);
+}
+
 template <typename T>
 __global__ void increment_to_point_grad_kernel(const T* __restrict__ g, T* __restrict__ out, uint64_t total,
                                                uint32_t L, uint32_t d) {
@@ -398,6 +437,35 @@ void launch_generic_backward(const T* path, T* out, const T* sig_derivs, const T
     count_launch();
 }
 
+uint64_t chen_combine_tmp_elems(const SigShape& s, int nseg) {
+    // two ping-pong buffers: ceil(nseg/2) and ceil(nseg/4) signatures per path
+    return s.batch * (s.full_len - 1) * uint64_t((nseg + 1) / 2 + (nseg + 3) / 4);
+}
+
+template <typename T>
+void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int nseg, cudaStream_t stream) {
+    if (nseg <= 1 || s.batch == 0) return;
+    check_generic_limits(s);
+    const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
+    const LevelIndex lev = make_level_index(s.dim, s.degree);
+    T* buf[2] = {tmp, tmp + s.batch * slen * uint64_t((nseg + 1) / 2)};
+    const T* cur = seg;
+    int n = nseg, round = 0;
+    while (n > 1) {
+        const int n2 = (n + 1) / 2;
+        const bool final = n2 == 1;
+        T* dst = final ? out : buf[round & 1];
+        const uint64_t total = checked_mul(s.batch * uint64_t(n2), slen, "signature output");
+        chen_pair_kernel<T><<<grid_1d(total, kGenericThreads), kGenericThreads, 0, stream>>>(
+            cur, n, dst, final ? s.stride : slen, final && s.scalar_term, total, slen, static_cast<int>(s.degree), lev);
+        SIG_CUDA_CHECK(cudaGetLastError());
+        count_launch();
+        cur = dst;
+        n = n2;
+        ++round;
+    }
+}
+
 template <typename T>
 void launch_increment_to_point_grad(const T* incr_grad, T* out, uint64_t batch, uint64_t L, uint64_t d,
                                     cudaStream_t stream) {
@@ -433,6 +501,7 @@ void launch_nonfinite_scan(const T* data, uint64_t n, int* flag, cudaStream_t st
     template void launch_generic_backward<T>(const T*, T*, const T*, const T*, const SigShape&, T, T*,   \
                                              unsigned, cudaStream_t);                                    \
     template void launch_increment_to_point_grad<T>(const T*, T*, uint64_t, uint64_t, uint64_t, cudaStream_t); \
+    template void launch_chen_combine<T>(T*, const T*, T*, const SigShape&, int, cudaStream_t);                   \
     template void launch_fill<T>(T*, uint64_t, T, cudaStream_t);                                         \
     template void launch_nonfinite_scan<T>(const T*, uint64_t, int*, cudaStream_t);
 INSTANTIATE(float)

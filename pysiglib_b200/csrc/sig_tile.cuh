@@ -90,10 +90,40 @@ __device__ __forceinline__ void load_step(StepOperands<T, Sh>& op, const T* row,
     }
 }
 
-// Stage the increments of augmented steps [j0, j0 + cnt) of path x into zs (row stride DP).
-template <typename T, typename Sh, bool FLAGS>
-__device__ __forceinline__ void stage_increments(T* zs, const PathView<T>& pv, const T* x, int j0, int cnt,
-                                                 int lane) {
+// Staging of the increments of augmented steps [j0, j0 + cnt) of path x into zs (row stride
+// DP), split in two so the global loads of the next chunk are in flight while the current
+// chunk is computed: prefetch() issues the loads into registers, commit() takes the
+// differences and writes them to shared memory.  With flags the increments are synthesised
+// from scattered points (increments.cuh) and everything happens in commit().
+template <typename T, typename Sh>
+struct ChunkRegs {
+    static constexpr int K = (kTileChunk * Sh::D + 31) / 32;  // elements per lane and chunk
+    T lo[K];
+    T hi[K];
+};
+
+// EAGER = false (flags, or prefetch switched off for the kernel): nothing is loaded here and
+// commit_increments() reads global memory itself.
+template <typename T, typename Sh, bool EAGER>
+__device__ __forceinline__ void prefetch_increments(ChunkRegs<T, Sh>& r, const T* x, int j0, int cnt, int lane) {
+    if constexpr (EAGER) {
+        constexpr int D = Sh::D;
+        const T* src = x + size_t(j0) * D;
+        const int total = cnt * D;
+#pragma unroll
+        for (int k = 0; k < ChunkRegs<T, Sh>::K; ++k) {
+            const int i = lane + 32 * k;
+            if (i < total) {
+                r.lo[k] = src[i];
+                r.hi[k] = src[i + D];
+            }
+        }
+    }
+}
+
+template <typename T, typename Sh, bool FLAGS, bool EAGER>
+__device__ __forceinline__ void commit_increments(T* zs, const ChunkRegs<T, Sh>& r, const PathView<T>& pv,
+                                                  const T* x, int j0, int cnt, int lane) {
     constexpr int D = Sh::D;
     constexpr int DP = RowPad<T, D>::DP;
     const int total = cnt * D;
@@ -101,6 +131,15 @@ __device__ __forceinline__ void stage_increments(T* zs, const PathView<T>& pv, c
         for (int i = lane; i < total; i += 32) {
             const int step = i / D, c = i - step * D;
             zs[step * DP + c] = pv.increment(x, j0 + step, c);
+        }
+    } else if constexpr (EAGER) {
+#pragma unroll
+        for (int k = 0; k < ChunkRegs<T, Sh>::K; ++k) {
+            const int i = lane + 32 * k;
+            if (i < total) {
+                const int step = i / D, c = i - step * D;
+                zs[step * DP + c] = r.hi[k] - r.lo[k];
+            }
         }
     } else {
         const T* src = x + size_t(j0) * D;
@@ -111,32 +150,47 @@ __device__ __forceinline__ void stage_increments(T* zs, const PathView<T>& pv, c
     }
 }
 
+// Forward sweep.  With nseg > 1 every path is cut into nseg time segments that are swept
+// independently (more warps for small batches) and written to `seg_out` ((batch, nseg, S),
+// scalar-free); Chen-product launches then join them into `out`.
 template <typename T, typename Sh, bool FLAGS, int WPB>
 __global__ void __launch_bounds__(WPB * 32)
-tile_forward_kernel(PathView<T> pv, T* __restrict__ out, uint64_t batch, uint32_t stride, bool scalar) {
+tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out, uint64_t batch, uint32_t stride,
+                    bool scalar, int nseg) {
     constexpr int DP = RowPad<T, Sh::D>::DP;
-    constexpr int WPP = (Sh::UNITS + 31) / 32;  // warps per path
+    constexpr int WPP = (Sh::UNITS + 31) / 32;  // warps per (path, segment)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * DP;
 
     const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
-    if (gw >= batch * WPP) return;
-    const uint64_t b = gw / WPP;
-    const int u = int(gw - b * WPP) * 32 + lane;
+    if (gw >= batch * uint64_t(nseg) * WPP) return;
+    const uint64_t vp = gw / WPP;               // virtual path = b * nseg + segment
+    const uint64_t b = vp / uint64_t(nseg);
+    const int seg = int(vp - b * uint64_t(nseg));
+    const int j_begin = int(int64_t(pv.steps) * seg / nseg);
+    const int j_end = int(int64_t(pv.steps) * (seg + 1) / nseg);
+    const int u = int(gw - vp * WPP) * 32 + lane;
     const bool active = u < Sh::UNITS;
     const UnitIndex<Sh> ix = decode_unit<Sh>(active ? u : 0);
     const T* x = pv.base + b * pv.path_stride;
 
     TileState<T, Sh> st;
     StepOperands<T, Sh> op;
-    for (int j0 = 0; j0 < pv.steps; j0 += kTileChunk) {
-        const int cnt = min(kTileChunk, pv.steps - j0);
+    // Register prefetch of the next chunk: pays in float32 (measured +4..9 % on B200); in
+    // float64 the extra registers cost more than the hidden latency gains.
+    constexpr bool EAGER = !FLAGS && sizeof(T) == 4;
+    ChunkRegs<T, Sh> pre;
+    prefetch_increments<T, Sh, EAGER>(pre, x, j_begin, min(kTileChunk, j_end - j_begin), lane);
+    for (int j0 = j_begin; j0 < j_end; j0 += kTileChunk) {
+        const int cnt = min(kTileChunk, j_end - j0);
         __syncwarp();
-        stage_increments<T, Sh, FLAGS>(zs, pv, x, j0, cnt, lane);
+        commit_increments<T, Sh, FLAGS, EAGER>(zs, pre, pv, x, j0, cnt, lane);
         __syncwarp();
+        if (j0 + kTileChunk < j_end)
+            prefetch_increments<T, Sh, EAGER>(pre, x, j0 + kTileChunk, min(kTileChunk, j_end - j0 - kTileChunk), lane);
         int step = 0;
-        if (j0 == 0) {
+        if (j0 == j_begin) {
             load_step<T, Sh, false>(op, zs, ix);
             tile_init_first<T, Sh>(st, op.z, op.zg, op.zc);
             step = 1;
@@ -147,9 +201,15 @@ tile_forward_kernel(PathView<T> pv, T* __restrict__ out, uint64_t batch, uint32_
         }
     }
     if (active) {
-        T* S = out + b * stride - (scalar ? 0 : 1);
-        tile_store<T, Sh>(st, ix, S);
-        if (scalar && u == 0) S[0] = T(1);
+        if (nseg == 1) {
+            T* S = out + b * stride - (scalar ? 0 : 1);
+            tile_store<T, Sh>(st, ix, S);
+            if (scalar && u == 0) S[0] = T(1);
+        } else {
+            const uint32_t slen = stride - (scalar ? 1 : 0);
+            T* S = seg_out + vp * slen - 1;
+            tile_store<T, Sh>(st, ix, S);
+        }
     }
 }
 
@@ -231,18 +291,66 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
 #pragma unroll
     for (int m = 0; m < Sh::NG; ++m) gmask[m] = grp == m ? T(1) : T(0);
 
+    // Warp-wide sum of one step's per-unit gradients into gbuf[step][letter] (zeroed at the
+    // start of the chunk; every contribution is a shared-memory atomic add).
+    auto reduce_step = [&](T (&v)[DP2], const T* gc, int step) {
+        // (1) letters with static indices (the unit's own children were folded in by the caller)
+        warp_halving_reduce<T, DP2>(v, lane);
+        constexpr int REP = DP2 >= 32 ? 1 : 32 / DP2;   // lanes holding the same letter
+        constexpr int PER = DP2 >= 32 ? DP2 / 32 : 1;   // letters per lane
+        T* grow = gbuf + step * D;
+        if ((lane & (REP - 1)) == 0) {
+            const int first = reduced_first_letter<DP2>(lane);
+#pragma unroll
+            for (int i = 0; i < PER; ++i)
+                if (first + i < D) atomicAdd(grow + first + i, v[i]);
+        }
+        // (2) chain letters: units sharing letter p[k] are STRIDE consecutive units, so a
+        // partial butterfly sums them before one lane per group adds the total
+#pragma unroll
+        for (int k = 0; k < P; ++k) {
+            const int stride = cpow(D, P - 1 - k) * Sh::NG;
+            T xk = gc[k];
+            if (stride % 32 == 0) {
+#pragma unroll
+                for (int m = 16; m >= 1; m >>= 1) xk += __shfl_xor_sync(0xffffffffu, xk, m);
+                if (lane == 0) atomicAdd(grow + ix.p[k], xk);
+            } else if (32 % stride == 0) {
+#pragma unroll
+                for (int m = 1; m < 32; m <<= 1)
+                    if (m < stride) xk += __shfl_xor_sync(0xffffffffu, xk, m);
+                if ((lane & (stride - 1)) == 0) atomicAdd(grow + ix.p[k], xk);
+            } else {
+                atomicAdd(grow + ix.p[k], xk);
+            }
+        }
+    };
+
+    // (Neither a register prefetch of the next chunk nor a one-step-late reduction pays here:
+    // both were measured on B200 and cost a resident CTA per SM, 233 -> 293 ms on the C5 shape.)
     StepOperands<T, Sh> op;
+    ChunkRegs<T, Sh> pre;
     for (int j1 = pv.steps; j1 > 0;) {
         const int j0 = max(0, j1 - kTileChunk);
         const int cnt = j1 - j0;
         __syncwarp();
-        stage_increments<T, Sh, FLAGS>(zs, pv, x, j0, cnt, lane);
+        commit_increments<T, Sh, FLAGS, false>(zs, pre, pv, x, j0, cnt, lane);
         for (int i = lane; i < cnt * D; i += 32) gbuf[i] = T(0);
         __syncwarp();
         for (int step = cnt - 1; step >= 0; --step) {
-            load_step<T, Sh, true>(op, zs + step * DP, ix);
-            tile_update<T, Sh>(st, op.z, op.zg, op.zc);  // rewind to the state before this step
             load_step<T, Sh, false>(op, zs + step * DP, ix);
+            {
+                // rewind to the state before this step: Horner step with the negated increment
+                // (the negations fold into the operand modifiers of the consuming instructions)
+                StepOperands<T, Sh> neg;
+#pragma unroll
+                for (int c = 0; c < D; ++c) neg.z[c] = -op.z[c];
+#pragma unroll
+                for (int j = 0; j < G; ++j) neg.zg[j] = -op.zg[j];
+#pragma unroll
+                for (int k = 0; k < P; ++k) neg.zc[k] = -op.zc[k];
+                tile_update<T, Sh>(st, neg.z, neg.zg, neg.zc);
+            }
             TileGrad<T, Sh> g;
 #pragma unroll
             for (int c = 0; c < D; ++c) g.gz[c] = T(0);
@@ -252,9 +360,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
             for (int k = 0; k < (P > 0 ? P : 1); ++k) g.gc[k] = T(0);
             tile_pullback<T, Sh>(st, ad, g, op.z, op.zg, op.zc);
 
-            // Sum the per-unit gradients over the warp into gbuf[step][letter] (zeroed at the
-            // start of the chunk; every contribution below is a shared-memory atomic add).
-            // (1) letters with static indices, plus the unit's own children through a 0/1 mask
+            // fold the unit's own children (letters c0 + j) into the static letters with a 0/1 mask
             T v[DP2];
 #pragma unroll
             for (int c = 0; c < DP2; ++c) {
@@ -262,35 +368,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
                 else if constexpr (Sh::NG == 1) v[c] = g.gz[c] + g.gg[c];
                 else v[c] = sig_fma(gmask[c / G], g.gg[c % G], g.gz[c]);
             }
-            warp_halving_reduce<T, DP2>(v, lane);
-            constexpr int REP = DP2 >= 32 ? 1 : 32 / DP2;   // lanes holding the same letter
-            constexpr int PER = DP2 >= 32 ? DP2 / 32 : 1;   // letters per lane
-            T* grow = gbuf + step * D;
-            if ((lane & (REP - 1)) == 0) {
-                const int first = reduced_first_letter<DP2>(lane);
-#pragma unroll
-                for (int i = 0; i < PER; ++i)
-                    if (first + i < D) atomicAdd(grow + first + i, v[i]);
-            }
-            // (2) chain letters: units sharing letter p[k] are STRIDE consecutive units, so a
-            // partial butterfly sums them before one lane per group adds the total
-#pragma unroll
-            for (int k = 0; k < P; ++k) {
-                const int stride = cpow(D, P - 1 - k) * Sh::NG;
-                T x = g.gc[k];
-                if (stride % 32 == 0) {
-#pragma unroll
-                    for (int m = 16; m >= 1; m >>= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
-                    if (lane == 0) atomicAdd(grow + ix.p[k], x);
-                } else if (32 % stride == 0) {
-#pragma unroll
-                    for (int m = 1; m < 32; m <<= 1)
-                        if (m < stride) x += __shfl_xor_sync(0xffffffffu, x, m);
-                    if ((lane & (stride - 1)) == 0) atomicAdd(grow + ix.p[k], x);
-                } else {
-                    atomicAdd(grow + ix.p[k], x);
-                }
-            }
+            reduce_step(v, g.gc, step);
         }
         __syncwarp();
         // flush the chunk: one atomic per (step, channel)

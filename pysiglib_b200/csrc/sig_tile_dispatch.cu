@@ -1,6 +1,10 @@
 // Run-time choice among the compiled register-tile variants (tile_table.h).
 #include <algorithm>
+#include <cmath>
+#include <map>
 #include <mutex>
+#include <string>
+#include <tuple>
 
 #include "sig_tile_launch.cuh"
 #ifdef SIG_TILE_DEV
@@ -32,53 +36,137 @@ const std::vector<TileEntry>& tile_table() {
     return table;
 }
 
-// Picks the variant for this shape: the biggest tile whose warp count fills the GPU
-// (8 warps per SM), else the variant with the most warps.
-const TileEntry* choose(bool is_double, bool backward, const SigShape& s, int sm_count) {
-    if (s.dim > 64 || s.degree > 16 || s.full_len >= (1ull << 31)) return nullptr;
-    const TileEntry* best = nullptr;
-    const uint64_t want = uint64_t(sm_count > 0 ? sm_count : 148) * 8;
+struct Plan {
+    const TileEntry* entry = nullptr;
+    int nseg = 1;
+};
+
+// Resident CTAs per SM of a variant on a device, queried once and cached.
+int occupancy_of(const TileEntry& e, bool flags, int device) {
+    static std::mutex mu;
+    static std::map<std::tuple<const TileEntry*, bool, int>, int> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_tuple(&e, flags, device);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    const int occ = e.occupancy(flags);
+    cache.emplace(key, occ);
+    return occ;
+}
+
+// Issue-slot utilisation reached with w resident warps per SM sub-partition.  Calibrated on
+// B200 with these kernels: a warp with a big register tile has many independent FMAs in flight
+// and needs few neighbours to hide its latencies (136 values: 0.87 at w = 2), a small tile is
+// dominated by its dependent chain (36 values: 0.67 at w = 2).  FP64 FMAs occupy their pipe
+// for two issue cycles, so utilisation above one half cannot be used.
+double issue_utilisation(int w, int tile_values, bool is_double) {
+    const double k = std::min(1.1, 0.35 + 0.005 * tile_values);
+    const double u = std::min(0.92, 1.0 - std::exp(-k * w));
+    return is_double ? std::min(u, 0.5) : u;
+}
+
+// Modelled sweep time (arbitrary units) of `blocks` CTAs of 4 warps, each running `steps`
+// steps of `instr` issue slots, on `sms` SMs holding at most `occ` CTAs each.
+double modelled_time(uint64_t blocks, int occ, int sms, double steps, const TileEntry& e) {
+    const uint64_t capacity = uint64_t(occ) * sms;
+    const uint64_t full = blocks / capacity, rem = blocks % capacity;
+    double t = double(full) * occ / issue_utilisation(occ, e.tile_values, e.is_double);
+    if (rem) {
+        const int r = int((rem + sms - 1) / sms);
+        t += r / issue_utilisation(r, e.tile_values, e.is_double);
+    }
+    return t * steps * e.est_instr;
+}
+
+// Chooses the tile variant (and, forward only, the number of time segments) with the
+// smallest modelled time.  tile_preference(): 1 = biggest tile, 2 = smallest, 3 = no
+// segmentation, 4 = biggest tile with three segments (tests).
+Plan choose(bool is_double, bool backward, const SigShape& s, int sm_count, bool flags, int device) {
+    Plan plan;
+    if (s.dim > 64 || s.degree > 16 || s.full_len >= (1ull << 31)) return plan;
+    const int pref = tile_preference();
+    const int sms = sm_count > 0 ? sm_count : 148;
+    const uint64_t steps = s.len > 1 ? s.len - 1 : 1;
+    const uint64_t seg_bytes = s.batch * (s.full_len - 1) * (is_double ? 8 : 4);
+    static const int kSegments[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32};
+    double best = 0;
+    const TileEntry* first = nullptr;
+    const TileEntry* last = nullptr;
     for (const TileEntry& e : tile_table()) {
         if (e.is_double != is_double || e.backward != backward || e.D != int(s.dim) || e.N != int(s.degree)) continue;
-        const uint64_t warps = s.batch * uint64_t((e.units + 31) / 32);
-        if (warps >= want) return &e;
-        if (!best || (e.units + 31) / 32 > (best->units + 31) / 32) best = &e;
+        if (!first) first = &e;
+        last = &e;
+        if (pref == 1 || pref == 2 || pref == 4 || device < 0) continue;
+        const int occ = occupancy_of(e, flags, device);
+        const uint64_t wpp = uint64_t((e.units + 31) / 32);
+        for (int nseg : kSegments) {
+            if (nseg > 1 && (backward || pref == 3 || steps / nseg < 64 || seg_bytes * 2 * nseg > (1ull << 30))) break;
+            const uint64_t blocks = (s.batch * nseg * wpp + kTileWarpsPerBlock - 1) / kTileWarpsPerBlock;
+            // time segmentation only pays while one sweep leaves SMs idle
+            if (nseg > 1 && (s.batch * (nseg - 1) * wpp + kTileWarpsPerBlock - 1) / kTileWarpsPerBlock >=
+                                uint64_t(occ) * sms) break;
+            double t = modelled_time(blocks, occ, sms, double((steps + nseg - 1) / nseg), e);
+            // joining the segments: about nseg - 1 products over the whole signature
+            if (nseg > 1) t += (nseg - 1) * (double(s.full_len) * s.degree / 32.0 * s.batch / (4.0 * sms) * 6.0 + 4000.0);
+            if (!plan.entry || t < best) {
+                best = t;
+                plan.entry = &e;
+                plan.nseg = nseg;
+            }
+        }
     }
-    return best;
+    if (pref == 1 || pref == 4 || (device < 0 && first)) plan.entry = first, plan.nseg = 1;
+    if (pref == 2) plan.entry = last, plan.nseg = 1;
+    if (pref == 4 && !backward && plan.entry) plan.nseg = int(std::min<uint64_t>(3, steps));
+    return plan;
 }
 
 }  // namespace
 
 template <typename T>
 bool tile_forward_available(const SigShape& s) {
-    return choose(sizeof(T) == 8, false, s, 0) != nullptr;
+    return choose(sizeof(T) == 8, false, s, 0, false, -1).entry != nullptr;
 }
 
 template <typename T>
 bool tile_backward_available(const SigShape& s) {
-    return choose(sizeof(T) == 8, true, s, 0) != nullptr;
+    return choose(sizeof(T) == 8, true, s, 0, false, -1).entry != nullptr;
 }
 
 template <typename T>
 bool launch_tile_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream) {
-    const TileEntry* e = choose(sizeof(T) == 8, false, s, device_context(current_device()).sm_count);
-    if (!e) return false;
+    const int device = current_device();
+    const bool flags = s.time_aug || s.lead_lag;
+    const Plan plan = choose(sizeof(T) == 8, false, s, device_context(device).sm_count, flags, device);
+    if (!plan.entry) return false;
     const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
-    e->launch(&pv, out, nullptr, nullptr, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term,
-              s.time_aug || s.lead_lag, stream);
+    if (plan.nseg > 1) {
+        // Small batch, long path: time is cut into segments swept by independent warps and the
+        // segment signatures are joined with Chen's identity.
+        const uint64_t per_buffer = s.batch * (s.full_len - 1);
+        Scratch seg((per_buffer * uint64_t(plan.nseg) + chen_combine_tmp_elems(s, plan.nseg)) * sizeof(T), stream);
+        plan.entry->launch(&pv, out, nullptr, nullptr, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term, flags,
+                           plan.nseg, seg.get(), stream);
+        launch_chen_combine<T>(out, seg.as<T>(), seg.as<T>() + per_buffer * uint64_t(plan.nseg), s, plan.nseg, stream);
+        return true;
+    }
+    plan.entry->launch(&pv, out, nullptr, nullptr, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term, flags, 1,
+                       nullptr, stream);
     return true;
 }
 
 template <typename T>
 bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
                           T end_time, T* incr_grad, cudaStream_t stream) {
-    const TileEntry* e = choose(sizeof(T) == 8, true, s, device_context(current_device()).sm_count);
+    const int device = current_device();
+    const TileEntry* e = choose(sizeof(T) == 8, true, s, device_context(device).sm_count, s.time_aug || s.lead_lag,
+                                device).entry;
     if (!e) return false;
     const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
     const uint64_t g_elems = s.batch * (s.data_len - 1) * s.data_dim;
     SIG_CUDA_CHECK(cudaMemsetAsync(incr_grad, 0, g_elems * sizeof(T), stream));
     e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term,
-              s.time_aug || s.lead_lag, stream);
+              s.time_aug || s.lead_lag, 1, nullptr, stream);
     launch_increment_to_point_grad<T>(incr_grad, out, s.batch, s.data_len, s.data_dim, stream);
     return true;
 }
@@ -88,13 +176,15 @@ bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* s
 template <typename T>
 bool launch_tile_backward_prealloc(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
                                    T end_time, T* incr_grad, int sm_count, cudaStream_t stream) {
-    const TileEntry* e = choose(sizeof(T) == 8, true, s, sm_count);
+    int device = 0;
+    SIG_CUDA_CHECK(cudaGetDevice(&device));
+    const TileEntry* e = choose(sizeof(T) == 8, true, s, sm_count, s.time_aug || s.lead_lag, device).entry;
     if (!e) return false;
     const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
     const uint64_t g_elems = s.batch * (s.data_len - 1) * s.data_dim;
     SIG_CUDA_CHECK(cudaMemsetAsync(incr_grad, 0, g_elems * sizeof(T), stream));
     e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term,
-              s.time_aug || s.lead_lag, stream);
+              s.time_aug || s.lead_lag, 1, nullptr, stream);
     launch_increment_to_point_grad<T>(incr_grad, out, s.batch, s.data_len, s.data_dim, stream);
     return true;
 }
@@ -103,6 +193,19 @@ template bool launch_tile_backward_prealloc<float>(const float*, float*, const f
                                                    float, float*, int, cudaStream_t);
 template bool launch_tile_backward_prealloc<double>(const double*, double*, const double*, const double*,
                                                     const SigShape&, double, double*, int, cudaStream_t);
+
+// Human-readable description of what would be launched for a shape on the current device.
+std::string describe_tile_plan(bool is_double, bool backward, const SigShape& s) {
+    const int device = current_device();
+    const bool flags = s.time_aug || s.lead_lag;
+    const Plan plan = choose(is_double, backward, s, device_context(device).sm_count, flags, device);
+    if (!plan.entry) return "generic";
+    const TileEntry& e = *plan.entry;
+    return std::string(backward ? "tile_backward" : "tile_forward") + "<D=" + std::to_string(e.D) + ",N=" +
+           std::to_string(e.N) + ",P=" + std::to_string(e.P) + ",G=" + std::to_string(e.G) + "> units=" +
+           std::to_string(e.units) + " segments=" + std::to_string(plan.nseg) + " ctas_per_sm=" +
+           std::to_string(occupancy_of(e, flags, device));
+}
 
 #define INSTANTIATE(T)                                                                              \
     template bool tile_forward_available<T>(const SigShape&);                                       \

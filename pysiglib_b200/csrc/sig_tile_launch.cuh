@@ -17,9 +17,12 @@ struct TileEntry {
     int D, N, P, G;
     int units;       // execution units (threads) per path
     int tile_values; // register-resident coefficients per unit
+    int est_instr;   // estimated issue slots per unit and step (cost model)
+    int (*occupancy)(bool flags);  // resident CTAs per SM of the kernel on the current device
     // forward:  fn(pv, out, nullptr, nullptr, ...);  backward: fn(pv, incr_grad, sig, derivs, ...)
+    // nseg / seg_out: time segmentation of the forward sweep (1 / nullptr = off; ignored backward)
     void (*launch)(const void* pv, void* out, const void* sig, const void* derivs, uint64_t batch,
-                   uint32_t stride, bool scalar, bool flags, cudaStream_t stream);
+                   uint32_t stride, bool scalar, bool flags, int nseg, void* seg_out, cudaStream_t stream);
 };
 
 inline unsigned tile_grid(uint64_t batch, int units) {
@@ -37,18 +40,18 @@ inline void tile_set_smem(Kernel kernel, size_t smem) {
 
 template <typename T, int D, int N, int P, int G>
 void tile_forward_launch(const void* pv_, void* out, const void*, const void*, uint64_t batch, uint32_t stride,
-                         bool scalar, bool flags, cudaStream_t stream) {
+                         bool scalar, bool flags, int nseg, void* seg_out, cudaStream_t stream) {
     using Sh = TileShape<D, N, P, G>;
     constexpr int W = kTileWarpsPerBlock;
     const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
     const size_t smem = size_t(W) * kTileChunk * RowPad<T, D>::DP * sizeof(T);
-    const unsigned grid = tile_grid(batch, Sh::UNITS);
+    const unsigned grid = tile_grid(batch * uint64_t(nseg), Sh::UNITS);
     if (flags) {
         tile_set_smem(tile_forward_kernel<T, Sh, true, W>, smem);
-        tile_forward_kernel<T, Sh, true, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), batch, stride, scalar);
+        tile_forward_kernel<T, Sh, true, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), static_cast<T*>(seg_out), batch, stride, scalar, nseg);
     } else {
         tile_set_smem(tile_forward_kernel<T, Sh, false, W>, smem);
-        tile_forward_kernel<T, Sh, false, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), batch, stride, scalar);
+        tile_forward_kernel<T, Sh, false, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), static_cast<T*>(seg_out), batch, stride, scalar, nseg);
     }
     SIG_CUDA_CHECK(cudaGetLastError());
     count_launch();
@@ -56,7 +59,7 @@ void tile_forward_launch(const void* pv_, void* out, const void*, const void*, u
 
 template <typename T, int D, int N, int P, int G>
 void tile_backward_launch(const void* pv_, void* incr_grad, const void* sig, const void* derivs, uint64_t batch,
-                          uint32_t stride, bool scalar, bool flags, cudaStream_t stream) {
+                          uint32_t stride, bool scalar, bool flags, int, void*, cudaStream_t stream) {
     using Sh = TileShape<D, N, P, G>;
     constexpr int W = kTileWarpsPerBlock;
     const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
@@ -75,10 +78,35 @@ void tile_backward_launch(const void* pv_, void* incr_grad, const void* sig, con
     count_launch();
 }
 
+template <typename Kernel>
+inline int tile_occupancy_of(Kernel kernel, size_t smem) {
+    tile_set_smem(kernel, smem);
+    int n = 0;
+    SIG_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kTileWarpsPerBlock * 32, smem));
+    return n > 0 ? n : 1;
+}
+
 template <typename T, int D, int N, int P, int G>
-TileEntry make_tile_entry(bool backward) {
+int tile_forward_occupancy(bool flags) {
     using Sh = TileShape<D, N, P, G>;
-    return TileEntry{sizeof(T) == 8, backward, D, N, P, G, Sh::UNITS, Sh::TS,
+    const size_t smem = size_t(kTileWarpsPerBlock) * kTileChunk * RowPad<T, D>::DP * sizeof(T);
+    return flags ? tile_occupancy_of(tile_forward_kernel<T, Sh, true, kTileWarpsPerBlock>, smem)
+                 : tile_occupancy_of(tile_forward_kernel<T, Sh, false, kTileWarpsPerBlock>, smem);
+}
+
+template <typename T, int D, int N, int P, int G>
+int tile_backward_occupancy(bool flags) {
+    using Sh = TileShape<D, N, P, G>;
+    const size_t smem = size_t(kTileWarpsPerBlock) * kTileChunk * (RowPad<T, D>::DP + D) * sizeof(T);
+    return flags ? tile_occupancy_of(tile_backward_kernel<T, Sh, true, kTileWarpsPerBlock>, smem)
+                 : tile_occupancy_of(tile_backward_kernel<T, Sh, false, kTileWarpsPerBlock>, smem);
+}
+
+template <typename T, int D, int N, int P, int G>
+TileEntry make_tile_entry(bool backward, int est_instr) {
+    using Sh = TileShape<D, N, P, G>;
+    return TileEntry{sizeof(T) == 8, backward, D, N, P, G, Sh::UNITS, Sh::TS, est_instr,
+                     backward ? &tile_backward_occupancy<T, D, N, P, G> : &tile_forward_occupancy<T, D, N, P, G>,
                      backward ? &tile_backward_launch<T, D, N, P, G> : &tile_forward_launch<T, D, N, P, G>};
 }
 

@@ -46,8 +46,13 @@ def _bind(lib):
     lib.sigb200_sig_length.restype = c_uint64
     lib.sigb200_set_kernel_policy.argtypes = (c_int,)
     lib.sigb200_set_kernel_policy.restype = None
+    lib.sigb200_set_tile_preference.argtypes = (c_int,)
+    lib.sigb200_set_tile_preference.restype = None
     lib.sigb200_kernel_family.argtypes = (c_uint64, c_uint64, c_bool, c_bool, c_int, c_int)
     lib.sigb200_kernel_family.restype = c_char_p
+    lib.sigb200_describe_plan.argtypes = (ctypes.c_char_p, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_bool,
+                                          c_bool, c_int, c_int)
+    lib.sigb200_describe_plan.restype = c_int
     lib.sigb200_fma_peak.argtypes = (c_int, c_void_p, c_int, c_int, c_void_p)
     lib.sigb200_fma_peak.restype = c_int
     lib.sigb200_noalloc_scratch_bytes.argtypes = ()
@@ -105,6 +110,21 @@ def launch_count():
 def set_kernel_policy(policy):
     """0: automatic choice between the register-tile and the generic kernels; 1: generic only."""
     library().sigb200_set_kernel_policy(int(policy))
+
+
+def describe_plan(batch, dimension, length, degree, *, time_aug=False, lead_lag=False, dtype="float32",
+                  backward=False):
+    """Kernel variant a call of this shape would run on the current CUDA device."""
+    buf = ctypes.create_string_buffer(256)
+    code = library().sigb200_describe_plan(buf, 256, batch, dimension, length, degree, time_aug, lead_lag,
+                                           1 if dtype == "float64" else 0, 1 if backward else 0)
+    return buf.value.decode() if code == 0 else "error %d: %s" % (code, last_error_message())
+
+
+def set_tile_preference(preference):
+    """0 automatic, 1 biggest register tile, 2 smallest, 3 automatic without time segmentation,
+    4 biggest tile with forced time segmentation of the forward sweep."""
+    library().sigb200_set_tile_preference(int(preference))
 
 
 def kernel_family(dimension, degree, *, time_aug=False, lead_lag=False, dtype="float32", backward=False):

@@ -146,6 +146,30 @@ def test_generic_kernels_match_oracle(shape, dtype):
         load_cusig.set_kernel_policy(0)
 
 
+@pytest.mark.parametrize("pref", [1, 2, 4], ids=["biggest", "smallest", "segmented"])
+@pytest.mark.parametrize("shape", [(3, 41, 16, 4), (2, 37, 8, 4), (2, 50, 2, 12), (2, 33, 5, 7), (2, 21, 10, 5),
+                                   (5, 29, 3, 4), (2, 40, 9, 4)], ids=lambda s: "B%d_L%d_d%d_N%d" % s)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_tile_variants_and_time_segmentation(pref, shape, dtype):
+    """Every compiled tile variant of a shape (biggest / smallest register tile) and the
+    time-segmented forward sweep (segments joined by Chen products) give the oracle's result."""
+    B, L, d, N = shape
+    load_cusig.set_tile_preference(pref)
+    try:
+        path = brownian_paths(B + L, B, L, d, dtype) * 2.0
+        expect = oracle.sig(path, N)
+        assert_sig_close(run_forward(path, N), expect, d, N, RTOL[dtype])
+        assert_sig_close(run_forward(path, N, time_aug=True, scalar_term=True),
+                         oracle.sig(path, N, time_aug=True, scalar_term=True), d + 1, N, RTOL[dtype], True)
+        seeds = np.ascontiguousarray(np.random.default_rng(B).normal(size=expect.shape).astype(dtype))
+        want = oracle.sig_backprop(path, expect, seeds, N)
+        p64 = path.astype(np.float64)
+        truth = oracle.sig_backprop(p64, oracle.sig(p64, N), seeds.astype(np.float64), N)
+        assert_grad_parity(run_backward(path, expect, seeds, N), want, truth, RTOL[dtype])
+    finally:
+        load_cusig.set_tile_preference(0)
+
+
 def test_float32_forward_tracks_reference_operation_order():
     """The kernels keep the reference's per-coefficient operation order (only nvcc's
     multiply-add contraction differs), so float32 forward results sit within a few ulp of
