@@ -179,6 +179,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-refcuda", action="store_true", help="skip timing the reference's own CUDA kernels")
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (profiling on a small case)")
     ap.add_argument("--length", type=int, default=None, help="override the path length (profiling on a small case)")
     args = ap.parse_args()
@@ -326,6 +327,36 @@ def main():
                "d2h_bytes_per_step": sig_bytes + (path_bytes if fwdbwd else 0),
                "steps": e2e_steps, "timer": "host clock around synchronous C-ABI calls, device-synchronised, max over ranks"}
 
+    # ---- the reference's own CUDA kernels on the same GPU and inputs (baseline beside ours) ----
+    ref_cuda = None
+    if rank == 0 and not args.no_refcuda:
+        from oracle import refcuda
+        if refcuda.available():
+            try:
+                ref_sig = torch.empty_like(sig)
+                ref_grad = torch.empty_like(path) if fwdbwd else None
+                times = []
+                for it in range(3):
+                    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                    e0.record(stream)
+                    refcuda.sig(path, N, out=ref_sig)
+                    e1.record(stream)
+                    if fwdbwd:
+                        refcuda.sig_backprop(path, ref_sig, seeds, N, out=ref_grad)
+                    e2.record(stream)
+                    torch.cuda.synchronize(dev)
+                    if it:
+                        times.append((e0.elapsed_time(e1), e1.elapsed_time(e2)))
+                rf = sum(t[0] for t in times) / len(times)
+                rb = sum(t[1] for t in times) / len(times) if fwdbwd else None
+                ref_cuda = {"fwd_ms": rf, "bwd_ms": rb, "value": b_local / ((rf + (rb or 0.0)) * 1e-3), "unit": "paths/s",
+                            "what": "reference cu_signature.cu kernels compiled for sm_100a, this rank's shard, "
+                                    "device-resident, 2 timed repetitions",
+                            "max_abs_diff_fwd": float((ref_sig - sig).abs().max().item())}
+                del ref_sig, ref_grad
+            except Exception as exc:  # a failing baseline must not take the benchmark down
+                ref_cuda = {"unavailable": str(exc)[:200]}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -375,6 +406,8 @@ def main():
     }
     if e2e is not None:
         out["e2e"] = e2e
+    if ref_cuda is not None:
+        out["reference_cuda"] = ref_cuda
     if not args.no_cpu and world == 1:
         cores = os.cpu_count() or 1
         v, n, dt = cpu_baseline(cfg, cores)

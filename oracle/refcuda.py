@@ -1,0 +1,72 @@
+"""Checker and timed baseline (test infrastructure, never used by the product): the reference's own CUDA kernels, built unmodified from its two
+translation units by oracle/build_ref_cuda.sh into oracle/_ref/libcusig_ref.so.  Used only as
+a checker and as a timed baseline; absent file -> callers skip."""
+import ctypes
+import os
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PATH = os.path.join(ROOT, "oracle", "_ref", "libcusig_ref.so")
+_lib = None
+
+
+def available():
+    return os.path.exists(PATH)
+
+
+def library():
+    global _lib
+    if _lib is None:
+        lib = ctypes.CDLL(PATH)
+        u64, b = ctypes.c_uint64, ctypes.c_bool
+        for suf, real in (("f", ctypes.c_float), ("d", ctypes.c_double)):
+            p = ctypes.POINTER(real)
+            f = getattr(lib, "signature_cuda_" + suf)
+            f.argtypes = (p, p, u64, u64, u64, u64, b, b, real, b, b, p, u64, u64, u64)
+            f.restype = ctypes.c_int
+            g = getattr(lib, "sig_backprop_cuda_" + suf)
+            g.argtypes = (p, p, p, p, u64, u64, u64, u64, b, b, real, b, p, u64, u64, u64)
+            g.restype = ctypes.c_int
+        _lib = lib
+    return _lib
+
+
+def _real(t):
+    import torch
+    return ctypes.c_float if t.dtype == torch.float32 else ctypes.c_double
+
+
+def _ptr(t):
+    return ctypes.cast(t.data_ptr(), ctypes.POINTER(_real(t)))
+
+
+def sig(path, degree, *, time_aug=False, lead_lag=False, end_time=1.0, scalar_term=False, out=None):
+    """Reference signature_cuda_* on a contiguous CUDA tensor (B, L, d)."""
+    import torch
+    B, L, d = path.shape
+    D = (2 * d if lead_lag else d) + (1 if time_aug else 0)
+    n = sum(D ** k for k in range(1, degree + 1)) + (1 if scalar_term else 0)
+    if out is None:
+        out = torch.empty((B, n), dtype=path.dtype, device=path.device)
+    real = _real(path)
+    suf = "f" if real is ctypes.c_float else "d"
+    rc = getattr(library(), "signature_cuda_" + suf)(_ptr(path), _ptr(out), B, d, L, degree, time_aug, lead_lag,
+                                                      real(end_time), True, scalar_term, None, 0, 0, 0)
+    if rc:
+        raise RuntimeError("reference signature_cuda failed with code %d" % rc)
+    return out
+
+
+def sig_backprop(path, sig_, derivs, degree, *, time_aug=False, lead_lag=False, end_time=1.0, scalar_term=False,
+                 out=None):
+    import torch
+    B, L, d = path.shape
+    if out is None:
+        out = torch.empty_like(path)
+    real = _real(path)
+    suf = "f" if real is ctypes.c_float else "d"
+    rc = getattr(library(), "sig_backprop_cuda_" + suf)(_ptr(path), _ptr(out), _ptr(derivs), _ptr(sig_), B, d, L,
+                                                         degree, time_aug, lead_lag, real(end_time), scalar_term,
+                                                         None, 0, 0, 0)
+    if rc:
+        raise RuntimeError("reference sig_backprop_cuda failed with code %d" % rc)
+    return out
