@@ -60,6 +60,16 @@ uint64_t chen_combine_tmp_elems(const SigShape& s, int nseg);
 template <typename T>
 void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int nseg, cudaStream_t stream);
 
+// C = A (x) B and the adjoint of the left factor, dX[u] = sum_v dS[u v] A[v], for batches of
+// scalar-free signatures; every pointer addresses the first level-1 coefficient of path 0 and
+// has its own batch stride (in elements).
+template <typename T>
+void launch_chen_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_stride, T* C, uint64_t c_stride,
+                         const SigShape& s, cudaStream_t stream);
+template <typename T>
+void launch_chen_left_adjoint(const T* dS, uint64_t ds_stride, const T* A, uint64_t a_stride, T* dX,
+                              uint64_t dx_stride, const SigShape& s, cudaStream_t stream);
+
 // out[t] = g[t-1] - g[t] over the raw path (g = increment gradients, (batch, L-1, d))
 template <typename T>
 void launch_increment_to_point_grad(const T* incr_grad, T* out, uint64_t batch, uint64_t L, uint64_t d,

@@ -319,6 +319,63 @@ chen_pair_kernel(const T* __restrict__ in, int n, T* __restrict__ out, uint64_t 
     if (out_scalar && pos == 1) c[0] = T(1);
 }
 
+// C = A (x) B for batches of scalar-free signatures with independent batch strides
+// (the pointers address the first level-1 coefficient of path 0).
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads)
+chen_product_kernel(const T* __restrict__ A, uint64_t a_stride, const T* __restrict__ B, uint64_t b_stride,
+                    T* __restrict__ C, uint64_t c_stride, uint64_t total, uint32_t slen, int N, LevelIndex lev) {
+    __shared__ uint32_t li[kMaxDegree + 2];
+    for (unsigned i = threadIdx.x; i < unsigned(N + 2); i += blockDim.x) li[i] = lev.li[i];
+    __syncthreads();
+    const uint64_t gid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= total) return;
+    const uint64_t b = gid / slen;
+    const uint32_t pos = uint32_t(gid - b * slen) + 1;
+    const T* a = A + b * a_stride - 1;
+    const T* bb = B + b * b_stride - 1;
+    int m = 1;
+    while (m < N && pos >= li[m + 1]) ++m;
+    const uint32_t idx = pos - li[m];
+    T acc = a[pos];
+    for (int i = m - 1; i >= 1; --i) {
+        const uint32_t pw = li[m - i + 1] - li[m - i];
+        const uint32_t left = idx / pw;
+        acc = fma_t(a[li[i] + left], bb[li[m - i] + (idx - left * pw)], acc);
+    }
+    (C + b * c_stride - 1)[pos] = acc + bb[pos];
+}
+
+// Adjoint of the left factor of a Chen product: for S = X (x) A and a loss adjoint dS,
+//   dX[u] = dS[u] + sum_{m >= 1, |u| + m <= N} sum_{|v| = m} dS[u v] * A[v].
+// One thread per coefficient of dX.
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads)
+chen_left_adjoint_kernel(const T* __restrict__ dS, uint64_t ds_stride, const T* __restrict__ A, uint64_t a_stride,
+                         T* __restrict__ dX, uint64_t dx_stride, uint64_t total, uint32_t slen, int N,
+                         LevelIndex lev) {
+    __shared__ uint32_t li[kMaxDegree + 2];
+    for (unsigned i = threadIdx.x; i < unsigned(N + 2); i += blockDim.x) li[i] = lev.li[i];
+    __syncthreads();
+    const uint64_t gid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= total) return;
+    const uint64_t b = gid / slen;
+    const uint32_t pos = uint32_t(gid - b * slen) + 1;
+    const T* ds = dS + b * ds_stride - 1;
+    const T* a = A + b * a_stride - 1;
+    int n = 1;
+    while (n < N && pos >= li[n + 1]) ++n;
+    const uint32_t idx = pos - li[n];
+    T acc = ds[pos];
+    for (int m = 1; n + m <= N; ++m) {
+        const uint32_t pw = li[m + 1] - li[m];  // d^m
+        const T* row = ds + li[n + m] + uint64_t(idx) * pw;
+        const T* av = a + li[m];
+        for (uint32_t v = 0; v < pw; ++v) acc = fma_t(row[v], av[v], acc);
+    }
+    (dX + b * dx_stride - 1)[pos] = acc;
+}
+
 template <typename T>
 __global__ void increment_to_point_grad_kernel(const T* __restrict__ g, T* __restrict__ out, uint64_t total,
                                                uint32_t L, uint32_t d) {
@@ -467,6 +524,34 @@ void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int ns
 }
 
 template <typename T>
+void launch_chen_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_stride, T* C, uint64_t c_stride,
+                         const SigShape& s, cudaStream_t stream) {
+    check_generic_limits(s);
+    const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
+    const uint64_t total = checked_mul(s.batch, slen, "signature output");
+    if (total == 0) return;
+    chen_product_kernel<T><<<grid_1d(total, kGenericThreads), kGenericThreads, 0, stream>>>(
+        A, a_stride, B, b_stride, C, c_stride, total, slen, static_cast<int>(s.degree),
+        make_level_index(s.dim, s.degree));
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T>
+void launch_chen_left_adjoint(const T* dS, uint64_t ds_stride, const T* A, uint64_t a_stride, T* dX,
+                              uint64_t dx_stride, const SigShape& s, cudaStream_t stream) {
+    check_generic_limits(s);
+    const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
+    const uint64_t total = checked_mul(s.batch, slen, "signature output");
+    if (total == 0) return;
+    chen_left_adjoint_kernel<T><<<grid_1d(total, kGenericThreads), kGenericThreads, 0, stream>>>(
+        dS, ds_stride, A, a_stride, dX, dx_stride, total, slen, static_cast<int>(s.degree),
+        make_level_index(s.dim, s.degree));
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T>
 void launch_increment_to_point_grad(const T* incr_grad, T* out, uint64_t batch, uint64_t L, uint64_t d,
                                     cudaStream_t stream) {
     const uint64_t total = checked_mul(batch, checked_mul(L, d, "path gradient"), "path gradient");
@@ -502,6 +587,8 @@ void launch_nonfinite_scan(const T* data, uint64_t n, int* flag, cudaStream_t st
                                              unsigned, cudaStream_t);                                    \
     template void launch_increment_to_point_grad<T>(const T*, T*, uint64_t, uint64_t, uint64_t, cudaStream_t); \
     template void launch_chen_combine<T>(T*, const T*, T*, const SigShape&, int, cudaStream_t);                   \
+    template void launch_chen_product<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t); \
+    template void launch_chen_left_adjoint<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t); \
     template void launch_fill<T>(T*, uint64_t, T, cudaStream_t);                                         \
     template void launch_nonfinite_scan<T>(const T*, uint64_t, int*, cudaStream_t);
 INSTANTIATE(float)

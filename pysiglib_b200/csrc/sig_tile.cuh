@@ -213,6 +213,19 @@ tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out
     }
 }
 
+// Time segmentation of the reverse sweep (small batches): each path is cut into nseg segments
+// that are swept by independent warps.  Segment k starts from the signature of the path up to
+// its end (seg_sig for k = 0, state for 0 < k < nseg-1, the caller's sig for the last) and
+// from the loss adjoint of that signature (adjoint; the caller's sig_derivs for the last).
+// All three arrays are (batch, nseg, S) without scalar terms.
+template <typename T>
+struct BackwardSegments {
+    int nseg = 1;
+    const T* seg_sig = nullptr;
+    const T* state = nullptr;
+    const T* adjoint = nullptr;
+};
+
 constexpr int next_pow2(int v) { return v <= 1 ? 1 : 2 * next_pow2((v + 1) / 2); }
 constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v / 2); }
 
@@ -255,7 +268,7 @@ __device__ __forceinline__ int reduced_first_letter(int lane) {
 template <typename T, typename Sh, bool FLAGS, int WPB>
 __global__ void __launch_bounds__(WPB * 32)
 tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restrict__ derivs,
-                     T* __restrict__ incr_grad, uint64_t batch, uint32_t stride, bool scalar) {
+                     T* __restrict__ incr_grad, uint64_t batch, uint32_t stride, bool scalar, BackwardSegments<T> segs) {
     constexpr int D = Sh::D, G = Sh::G, P = Sh::P;
     constexpr int DP = RowPad<T, D>::DP;
     constexpr int DP2 = next_pow2(D);
@@ -265,10 +278,15 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * (DP + D);
     T* gbuf = zs + kTileChunk * DP;
 
+    const int nseg = segs.nseg;
     const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
-    if (gw >= batch * WPP) return;
-    const uint64_t b = gw / WPP;
-    const int u = int(gw - b * WPP) * 32 + lane;
+    if (gw >= batch * uint64_t(nseg) * WPP) return;
+    const uint64_t vp = gw / WPP;               // virtual path = b * nseg + segment
+    const uint64_t b = vp / uint64_t(nseg);
+    const int seg = int(vp - b * uint64_t(nseg));
+    const int j_begin = int(int64_t(pv.steps) * seg / nseg);
+    const int j_end = int(int64_t(pv.steps) * (seg + 1) / nseg);
+    const int u = int(gw - vp * WPP) * 32 + lane;
     const bool active = u < Sh::UNITS;
     const UnitIndex<Sh> ix = decode_unit<Sh>(active ? u : 0);
     const int grp = ix.c0 / G;
@@ -277,7 +295,18 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
 
     TileState<T, Sh> st;
     TileAdjoint<T, Sh> ad;
-    tile_load<T, Sh>(st, ad, ix, sig + b * stride - (scalar ? 0 : 1), derivs + b * stride - (scalar ? 0 : 1));
+    {
+        // Signature and adjoint at the END of this time segment: the caller's arrays for the last
+        // segment, else the prefix states / pulled-back adjoints prepared by the host (scalar-free).
+        const uint32_t slen = stride - (scalar ? 1 : 0);
+        const T* s_end = sig + b * stride - (scalar ? 0 : 1);
+        const T* a_end = derivs + b * stride - (scalar ? 0 : 1);
+        if (seg != nseg - 1) {
+            s_end = (seg == 0 ? segs.seg_sig : segs.state) + vp * slen - 1;
+            a_end = segs.adjoint + vp * slen - 1;
+        }
+        tile_load<T, Sh>(st, ad, ix, s_end, a_end);
+    }
     if (!active) {
         // idle lanes carry a zero adjoint so that they add nothing to the warp sums
 #pragma unroll
@@ -330,8 +359,8 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     // both were measured on B200 and cost a resident CTA per SM, 233 -> 293 ms on the C5 shape.)
     StepOperands<T, Sh> op;
     ChunkRegs<T, Sh> pre;
-    for (int j1 = pv.steps; j1 > 0;) {
-        const int j0 = max(0, j1 - kTileChunk);
+    for (int j1 = j_end; j1 > j_begin;) {
+        const int j0 = max(j_begin, j1 - kTileChunk);
         const int cnt = j1 - j0;
         __syncwarp();
         commit_increments<T, Sh, FLAGS, false>(zs, pre, pv, x, j0, cnt, lane);

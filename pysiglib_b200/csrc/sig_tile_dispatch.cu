@@ -39,6 +39,7 @@ const std::vector<TileEntry>& tile_table() {
 struct Plan {
     const TileEntry* entry = nullptr;
     int nseg = 1;
+    const TileEntry* forward_for_segments = nullptr;
 };
 
 // Resident CTAs per SM of a variant on a device, queried once and cached.
@@ -92,6 +93,10 @@ Plan choose(bool is_double, bool backward, const SigShape& s, int sm_count, bool
     double best = 0;
     const TileEntry* first = nullptr;
     const TileEntry* last = nullptr;
+    const TileEntry* fwd_big = nullptr;  // biggest forward tile: sweeps the segments of a segmented backward
+    for (const TileEntry& e : tile_table())
+        if (e.is_double == is_double && !e.backward && e.D == int(s.dim) && e.N == int(s.degree)) { fwd_big = &e; break; }
+    const double join_cost = double(s.full_len) * s.degree / 32.0 * s.batch / (4.0 * sms) * 6.0 + 4000.0;
     for (const TileEntry& e : tile_table()) {
         if (e.is_double != is_double || e.backward != backward || e.D != int(s.dim) || e.N != int(s.degree)) continue;
         if (!first) first = &e;
@@ -100,14 +105,23 @@ Plan choose(bool is_double, bool backward, const SigShape& s, int sm_count, bool
         const int occ = occupancy_of(e, flags, device);
         const uint64_t wpp = uint64_t((e.units + 31) / 32);
         for (int nseg : kSegments) {
-            if (nseg > 1 && (backward || pref == 3 || steps / nseg < 64 || seg_bytes * 2 * nseg > (1ull << 30))) break;
+            // segment scratch: forward nseg + joins (about 2 nseg signatures), backward 3 nseg
+            if (nseg > 1 && (pref == 3 || steps / nseg < 64 || seg_bytes * 3 * nseg > (1ull << 30))) break;
+            if (nseg > 1 && backward && !fwd_big) break;
             const uint64_t blocks = (s.batch * nseg * wpp + kTileWarpsPerBlock - 1) / kTileWarpsPerBlock;
             // time segmentation only pays while one sweep leaves SMs idle
             if (nseg > 1 && (s.batch * (nseg - 1) * wpp + kTileWarpsPerBlock - 1) / kTileWarpsPerBlock >=
                                 uint64_t(occ) * sms) break;
-            double t = modelled_time(blocks, occ, sms, double((steps + nseg - 1) / nseg), e);
-            // joining the segments: about nseg - 1 products over the whole signature
-            if (nseg > 1) t += (nseg - 1) * (double(s.full_len) * s.degree / 32.0 * s.batch / (4.0 * sms) * 6.0 + 4000.0);
+            const double seg_steps = double((steps + nseg - 1) / nseg);
+            double t = modelled_time(blocks, occ, sms, seg_steps, e);
+            if (nseg > 1 && !backward) t += (nseg - 1) * join_cost;  // joining the segments
+            if (nseg > 1 && backward) {
+                // segment signatures (one forward sweep), prefix states and pulled-back adjoints
+                const uint64_t fwpp = uint64_t((fwd_big->units + 31) / 32);
+                const uint64_t fblocks = (s.batch * nseg * fwpp + kTileWarpsPerBlock - 1) / kTileWarpsPerBlock;
+                t += modelled_time(fblocks, occupancy_of(*fwd_big, flags, device), sms, seg_steps, *fwd_big);
+                t += 2.0 * (nseg - 1) * join_cost;
+            }
             if (!plan.entry || t < best) {
                 best = t;
                 plan.entry = &e;
@@ -115,9 +129,10 @@ Plan choose(bool is_double, bool backward, const SigShape& s, int sm_count, bool
             }
         }
     }
+    plan.forward_for_segments = fwd_big;
     if (pref == 1 || pref == 4 || (device < 0 && first)) plan.entry = first, plan.nseg = 1;
     if (pref == 2) plan.entry = last, plan.nseg = 1;
-    if (pref == 4 && !backward && plan.entry) plan.nseg = int(std::min<uint64_t>(3, steps));
+    if (pref == 4 && plan.entry && (!backward || fwd_big)) plan.nseg = int(std::min<uint64_t>(3, steps));
     return plan;
 }
 
@@ -159,14 +174,46 @@ template <typename T>
 bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
                           T end_time, T* incr_grad, cudaStream_t stream) {
     const int device = current_device();
-    const TileEntry* e = choose(sizeof(T) == 8, true, s, device_context(device).sm_count, s.time_aug || s.lead_lag,
-                                device).entry;
+    const bool flags = s.time_aug || s.lead_lag;
+    const Plan plan = choose(sizeof(T) == 8, true, s, device_context(device).sm_count, flags, device);
+    const TileEntry* e = plan.entry;
     if (!e) return false;
     const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
     const uint64_t g_elems = s.batch * (s.data_len - 1) * s.data_dim;
+    const uint32_t stride = static_cast<uint32_t>(s.stride);
     SIG_CUDA_CHECK(cudaMemsetAsync(incr_grad, 0, g_elems * sizeof(T), stream));
-    e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term,
-              s.time_aug || s.lead_lag, 1, nullptr, stream);
+    if (plan.nseg > 1) {
+        // Small batch, long path: cut time into K segments swept by independent warps.  Needed per
+        // segment k: the signature E_k of the path up to the segment's end and its loss adjoint
+        // dE_k.  With A_k the signature of segment k alone (one forward sweep),
+        //   E_0 = A_0, E_k = E_{k-1} (x) A_k, E_{K-1} = sig (given);
+        //   dE_{K-1} = sig_derivs (given), dE_{k-1} = left adjoint of the product E_{k-1} (x) A_k.
+        const int K = plan.nseg;
+        const uint64_t slen = s.full_len - 1, row = uint64_t(K) * slen, per = s.batch * row;
+        Scratch buf(3 * per * sizeof(T), stream);
+        T* segA = buf.as<T>();
+        T* E = segA + per;
+        T* dE = E + per;
+        plan.forward_for_segments->launch(&pv, nullptr, nullptr, nullptr, s.batch, stride, s.scalar_term, flags, K,
+                                          segA, stream);
+        for (int k = 1; k <= K - 2; ++k)
+            launch_chen_product<T>(k == 1 ? segA : E + uint64_t(k - 1) * slen, row, segA + uint64_t(k) * slen, row,
+                                   E + uint64_t(k) * slen, row, s, stream);
+        for (int k = K - 1; k >= 1; --k) {
+            const bool top = k == K - 1;
+            launch_chen_left_adjoint<T>(top ? sig_derivs + (s.scalar_term ? 1 : 0) : dE + uint64_t(k) * slen,
+                                        top ? s.stride : row, segA + uint64_t(k) * slen, row,
+                                        dE + uint64_t(k - 1) * slen, row, s, stream);
+        }
+        BackwardSegments<T> segs;
+        segs.nseg = K;
+        segs.seg_sig = segA;
+        segs.state = E;
+        segs.adjoint = dE;
+        e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, stride, s.scalar_term, flags, K, &segs, stream);
+    } else {
+        e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, stride, s.scalar_term, flags, 1, nullptr, stream);
+    }
     launch_increment_to_point_grad<T>(incr_grad, out, s.batch, s.data_len, s.data_dim, stream);
     return true;
 }
@@ -178,7 +225,10 @@ bool launch_tile_backward_prealloc(const T* path, T* out, const T* sig_derivs, c
                                    T end_time, T* incr_grad, int sm_count, cudaStream_t stream) {
     int device = 0;
     SIG_CUDA_CHECK(cudaGetDevice(&device));
-    const TileEntry* e = choose(sizeof(T) == 8, true, s, sm_count, s.time_aug || s.lead_lag, device).entry;
+    // no extra scratch here: the choice is made among unsegmented sweeps only
+    SigShape one = s;
+    one.len = std::min<uint64_t>(s.len, 64);  // too short to be segmented, same variants otherwise
+    const TileEntry* e = choose(sizeof(T) == 8, true, one, sm_count, s.time_aug || s.lead_lag, device).entry;
     if (!e) return false;
     const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
     const uint64_t g_elems = s.batch * (s.data_len - 1) * s.data_dim;

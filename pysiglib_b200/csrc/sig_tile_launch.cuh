@@ -59,20 +59,24 @@ void tile_forward_launch(const void* pv_, void* out, const void*, const void*, u
 
 template <typename T, int D, int N, int P, int G>
 void tile_backward_launch(const void* pv_, void* incr_grad, const void* sig, const void* derivs, uint64_t batch,
-                          uint32_t stride, bool scalar, bool flags, int, void*, cudaStream_t stream) {
+                          uint32_t stride, bool scalar, bool flags, int nseg, void* segments, cudaStream_t stream) {
     using Sh = TileShape<D, N, P, G>;
     constexpr int W = kTileWarpsPerBlock;
     const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
     const size_t smem = size_t(W) * kTileChunk * (RowPad<T, D>::DP + D) * sizeof(T);
-    const unsigned grid = tile_grid(batch, Sh::UNITS);
+    BackwardSegments<T> segs;
+    if (nseg > 1 && segments) segs = *static_cast<const BackwardSegments<T>*>(segments);
+    const unsigned grid = tile_grid(batch * uint64_t(segs.nseg), Sh::UNITS);
     if (flags) {
         tile_set_smem(tile_backward_kernel<T, Sh, true, W>, smem);
         tile_backward_kernel<T, Sh, true, W><<<grid, W * 32, smem, stream>>>(
-            pv, static_cast<const T*>(sig), static_cast<const T*>(derivs), static_cast<T*>(incr_grad), batch, stride, scalar);
+            pv, static_cast<const T*>(sig), static_cast<const T*>(derivs), static_cast<T*>(incr_grad), batch, stride,
+            scalar, segs);
     } else {
         tile_set_smem(tile_backward_kernel<T, Sh, false, W>, smem);
         tile_backward_kernel<T, Sh, false, W><<<grid, W * 32, smem, stream>>>(
-            pv, static_cast<const T*>(sig), static_cast<const T*>(derivs), static_cast<T*>(incr_grad), batch, stride, scalar);
+            pv, static_cast<const T*>(sig), static_cast<const T*>(derivs), static_cast<T*>(incr_grad), batch, stride,
+            scalar, segs);
     }
     SIG_CUDA_CHECK(cudaGetLastError());
     count_launch();
