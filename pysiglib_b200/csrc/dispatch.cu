@@ -61,8 +61,11 @@ void run_host_pipeline(uint64_t batch, const std::vector<HostOperand>& inputs, v
     uint64_t per_path = out_bytes_per_path;
     for (const auto& in : inputs) per_path += in.bytes_per_path;
     per_path = std::max<uint64_t>(per_path, 1);
-    // ~8 chunks, each at most 2 GiB of staged operands, at least one path.
-    uint64_t chunk = (batch + 7) / 8;
+    // Up to 8 chunks so copies overlap compute, but no chunk below ~32 MiB of staged operands
+    // (small calls go as one piece: chunking them only shrinks the kernels), none above 2 GiB.
+    const uint64_t total_bytes = per_path * batch;
+    const uint64_t n_target = std::min<uint64_t>(8, std::max<uint64_t>(1, total_bytes / (32ull << 20)));
+    uint64_t chunk = (batch + n_target - 1) / n_target;
     chunk = std::min<uint64_t>(chunk, std::max<uint64_t>(1, (2ull << 30) / per_path));
     chunk = std::max<uint64_t>(chunk, 1);
     const uint64_t n_chunks = (batch + chunk - 1) / chunk;

@@ -1,0 +1,99 @@
+"""Host-side logic of the Python operators (argument contract of the reference's sig /
+sig_backprop, pysiglib/sig.py:265-279, pysiglib/sig_backprop.py:210-234), checked without a GPU:
+every case here fails or returns before any native compute call."""
+import inspect
+
+import numpy as np
+import pytest
+import torch
+
+import pysiglib_b200 as psl
+from pysiglib_b200 import torch_api
+from pysiglib_b200.sharded import shard_bounds
+
+
+def test_signatures_match_the_reference_surface():
+    p = inspect.signature(psl.sig).parameters
+    assert list(p) == ["path", "degree", "time_aug", "lead_lag", "end_time", "horner", "scalar_term", "correction",
+                       "n_jobs"]
+    assert all(p[k].kind is inspect.Parameter.KEYWORD_ONLY for k in list(p)[2:])
+    assert (p["time_aug"].default, p["lead_lag"].default, p["end_time"].default, p["horner"].default,
+            p["scalar_term"].default, p["correction"].default, p["n_jobs"].default) == (False, False, 1., True, False,
+                                                                                       None, 1)
+    q = inspect.signature(psl.sig_backprop).parameters
+    assert list(q) == ["path", "sig", "sig_derivs", "degree", "time_aug", "lead_lag", "end_time", "correction", "n_jobs"]
+    assert psl.signature is psl.sig
+    # torch_api mirrors the base API (reference tests/test_apis_match.py) and exposes no *_backprop
+    assert inspect.signature(torch_api.sig) == inspect.signature(psl.sig)
+    assert torch_api.sig.__doc__ == psl.sig.__doc__
+    assert not hasattr(torch_api, "sig_backprop")
+
+
+def test_sig_length():
+    assert psl.sig_length(3, 4, scalar_term=True) == 121
+    assert psl.sig_length(3, 4) == 120
+    assert psl.sig_length(3, 4, time_aug=True, lead_lag=True, scalar_term=True) == 2801
+    assert psl.sig_length(1, 5) == 5
+    assert psl.sig_length(0, 5, scalar_term=True) == 1
+    with pytest.raises(ValueError):
+        psl.sig_length(2, 64)
+    with pytest.raises(TypeError):
+        psl.sig_length(2.0, 3)
+
+
+def test_argument_type_checks():
+    x = np.zeros((2, 5, 3))
+    with pytest.raises(TypeError):
+        psl.sig(x, 2.0)
+    with pytest.raises(ValueError):
+        psl.sig(x, -1)
+    with pytest.raises(TypeError):
+        psl.sig(x, 2, end_time=1)          # an int is not accepted (reference sig.py:270)
+    with pytest.raises(TypeError):
+        psl.sig(x, 2, time_aug=1)
+    with pytest.raises(ValueError):
+        psl.sig(x, 2, n_jobs=0)
+    with pytest.raises(TypeError):
+        psl.sig([[0.0, 1.0]], 2)
+    with pytest.raises(TypeError):
+        psl.sig(x.astype(np.float16), 2)
+    with pytest.raises(ValueError):
+        psl.sig(np.zeros(5), 2)
+    with pytest.raises(ValueError):
+        psl.sig(np.zeros((2, 5, 0)), 2)
+    with pytest.raises(NotImplementedError):
+        psl.sig(x, 2, correction=np.ones(9))
+
+
+def test_empty_batch_returns_without_native_call():
+    out = psl.sig(np.zeros((0, 5, 3), dtype=np.float32), 3)
+    assert out.shape == (0, 39) and out.dtype == np.float32
+    out = psl.sig(torch.zeros((0, 4, 5, 2), dtype=torch.float64), 2, scalar_term=True)
+    assert tuple(out.shape) == (0, 4, 7)
+    g = psl.sig_backprop(np.zeros((0, 5, 3)), np.zeros((0, 39)), np.zeros((0, 39)), 3)
+    assert g.shape == (0, 5, 3)
+
+
+def test_backprop_argument_consistency():
+    x = np.zeros((2, 5, 3))
+    s = np.zeros((2, 39))
+    with pytest.raises(ValueError):
+        psl.sig_backprop(x, np.zeros((2, 38)), np.zeros((2, 38)), 3)       # neither layout
+    with pytest.raises(ValueError):
+        psl.sig_backprop(x, s, np.zeros((2, 41)), 3)                       # derivs of another length
+    with pytest.raises(ValueError):
+        psl.sig_backprop(x, s, s.astype(np.float32), 3)                    # dtypes differ
+    with pytest.raises(ValueError):
+        psl.sig_backprop(x, torch.zeros((2, 39), dtype=torch.float64), torch.zeros((2, 39), dtype=torch.float64), 3)
+    with pytest.raises(ValueError):
+        psl.sig_backprop(x, np.zeros((3, 39)), np.zeros((3, 39)), 3)       # batch shapes differ
+
+
+def test_shard_bounds_cover_the_batch():
+    for batch in (0, 1, 7, 8, 4096, 4099):
+        for n in (1, 2, 3, 4, 8):
+            b = shard_bounds(batch, n)
+            assert b[0][0] == 0 and b[-1][1] == batch
+            assert all(x[1] == y[0] for x, y in zip(b, b[1:]))
+            sizes = [e - s for s, e in b]
+            assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
