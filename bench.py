@@ -120,19 +120,27 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-def cpu_baseline(cfg, cores, paths_per_core=2):
-    """Times the CPU oracle (threaded, static contiguous chunks) on a bounded sample."""
+def cpu_baseline(cfg, cores, paths_per_core=None, target_seconds=10.0):
+    """Times the CPU oracle (threaded, static contiguous chunks) on a bounded sample: one path
+    per thread is timed first, then as many paths per thread as fit about `target_seconds`."""
     import torch
     from oracle import oracle
+
+    def run(sample):
+        path = make_paths(cfg, sample, 99, torch).numpy()
+        t0 = time.perf_counter()
+        sig = oracle.sig(path, cfg["N"], n_threads=cores)
+        if cfg["mode"] == "fwdbwd":
+            rng = np.random.default_rng(5)
+            seeds = rng.normal(size=sig.shape).astype(path.dtype)
+            oracle.sig_backprop(path, sig, seeds, cfg["N"], n_threads=cores)
+        return time.perf_counter() - t0
+
+    if paths_per_core is None:
+        probe = max(run(cores), 1e-4)
+        paths_per_core = int(max(1, min(512, target_seconds / probe)))
     sample = max(1, cores * paths_per_core)
-    path = make_paths(cfg, sample, 99, torch).numpy()
-    t0 = time.perf_counter()
-    sig = oracle.sig(path, cfg["N"], n_threads=cores)
-    if cfg["mode"] == "fwdbwd":
-        rng = np.random.default_rng(5)
-        seeds = rng.normal(size=sig.shape).astype(path.dtype)
-        oracle.sig_backprop(path, sig, seeds, cfg["N"], n_threads=cores)
-    dt = time.perf_counter() - t0
+    dt = run(sample)
     return sample / dt, sample, dt
 
 
@@ -142,15 +150,18 @@ def run_reference_arm(args, cfg, rank):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
+    # size one step to about 4 s of wall time on this box, then time exactly `steps` of them
+    probe = max(cpu_baseline(cfg, cores, 1)[2], 1e-4)
+    per_core = int(max(1, min(512, 4.0 / probe)))
     for _ in range(min(args.warmup, 1)):
-        cpu_baseline(cfg, cores, 1)
+        cpu_baseline(cfg, cores, per_core)
     total_paths, total_t = 0, 0.0
     for _ in range(args.steps):
-        _, n, dt = cpu_baseline(cfg, cores, 2)
+        _, n, dt = cpu_baseline(cfg, cores, per_core)
         total_paths += n
         total_t += dt
     value = total_paths / total_t
-    sample = "%d paths of %s per step (%s), %d host threads" % (2 * cores, args.config, cfg["mode"], cores)
+    sample = "%d paths of %s per step (%s), %d host threads" % (per_core * cores, args.config, cfg["mode"], cores)
     print(json.dumps({
         "impl": "reference", "metric": "paths_per_second_" + cfg["mode"], "value": value, "unit": "paths/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_t / args.steps,
