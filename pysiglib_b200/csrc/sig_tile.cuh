@@ -32,6 +32,12 @@ namespace sigb200 {
 
 constexpr int kTileChunk = 32;  // steps staged per warp and chunk
 
+constexpr int next_pow2_c(int v) {
+    int r = 1;
+    while (r < v) r *= 2;
+    return r;
+}
+
 template <typename T> struct VecOf;
 template <> struct VecOf<float> { using type = float4; static constexpr int n = 4; };
 template <> struct VecOf<double> { using type = double2; static constexpr int n = 2; };
@@ -265,8 +271,32 @@ __device__ __forceinline__ int reduced_first_letter(int lane) {
     else return lane >> (5 - ilog2(DP2));
 }
 
+// Shared-memory layout of one warp of the backward kernel (elements of T):
+//   zs   [kTileChunk][DP]   increments of the chunk
+//   gbuf [kTileChunk][D]    warp totals of the increment gradients, flushed once per chunk
+//   tbuf [RS][32 rows][ROWP] (+16 between steps)  per-lane gradient vectors of RS steps,
+//        written with vector stores and summed column-wise: the cross-lane reduction goes
+//        through shared memory with independent loads instead of a chain of shuffles.
+template <typename T, int D>
+struct BackwardSmem {
+    static constexpr int DP = RowPad<T, D>::DP;
+    static constexpr int DP2 = next_pow2_c(D);
+    static constexpr int RS = DP2 >= 32 ? 1 : 32 / DP2;      // steps per reduction group
+    static constexpr int ROWP = DP2 + (DP2 >= 4 ? 4 : 1);    // padded row: conflict-free stores
+    static constexpr int SLAB = 32 * ROWP + 16;              // one step; +16 words de-phases the banks
+    static constexpr int PER_WARP = kTileChunk * (DP + D) + RS * SLAB;
+};
+
+// Resident CTAs per SM the backward kernel is compiled for: shallow float tiles of up to 68 values fit
+// state + adjoint in 128 registers, which keeps four CTAs (16 warps) per SM; the reduction's
+// shuffle / shared-atomic latencies need those warps more than they need spare registers.
+template <typename T, typename Sh>
+constexpr int backward_min_ctas() {
+    return (sizeof(T) == 4 && Sh::TS <= 68 && Sh::Q <= 2) ? 4 : 1;
+}
+
 template <typename T, typename Sh, bool FLAGS, int WPB>
-__global__ void __launch_bounds__(WPB * 32)
+__global__ void __launch_bounds__(WPB * 32, backward_min_ctas<T, Sh>())
 tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restrict__ derivs,
                      T* __restrict__ incr_grad, uint64_t batch, uint32_t stride, bool scalar, BackwardSegments<T> segs) {
     constexpr int D = Sh::D, G = Sh::G, P = Sh::P;
@@ -275,8 +305,11 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     constexpr int WPP = (Sh::UNITS + 31) / 32;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * (DP + D);
+    using Lay = BackwardSmem<T, D>;
+    constexpr int RS = Lay::RS, ROWP = Lay::ROWP, SLAB = Lay::SLAB;
+    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * Lay::PER_WARP;
     T* gbuf = zs + kTileChunk * DP;
+    T* tbuf = gbuf + kTileChunk * D;
 
     const int nseg = segs.nseg;
     const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
@@ -321,18 +354,64 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     for (int m = 0; m < Sh::NG; ++m) gmask[m] = grp == m ? T(1) : T(0);
 
     // Warp-wide sum of one step's per-unit gradients into gbuf[step][letter] (zeroed at the
-    // start of the chunk; every contribution is a shared-memory atomic add).
-    auto reduce_step = [&](T (&v)[DP2], const T* gc, int step) {
-        // (1) letters with static indices (the unit's own children were folded in by the caller)
-        warp_halving_reduce<T, DP2>(v, lane);
-        constexpr int REP = DP2 >= 32 ? 1 : 32 / DP2;   // lanes holding the same letter
-        constexpr int PER = DP2 >= 32 ? DP2 / 32 : 1;   // letters per lane
+    // start of the chunk).
+    auto reduce_step = [&](T (&v)[DP2], const T* gc, int step, int cnt) {
+        // (1) letters with static indices (the unit's own children were folded in by the caller):
+        // every lane parks its vector in its own row of tbuf; once the RS steps of a group are
+        // there, each lane sums one column (one letter of one step) over the 32 rows.
         T* grow = gbuf + step * D;
-        if ((lane & (REP - 1)) == 0) {
-            const int first = reduced_first_letter<DP2>(lane);
+        {
+            T* row = tbuf + (step % RS) * SLAB + lane * ROWP;
+            if constexpr (DP2 >= 4) {
+                using V = typename VecOf<T>::type;
+                constexpr int W = VecOf<T>::n;
 #pragma unroll
-            for (int i = 0; i < PER; ++i)
-                if (first + i < D) atomicAdd(grow + first + i, v[i]);
+                for (int i = 0; i < DP2 / W; ++i) {
+                    V pack;
+                    T* e = reinterpret_cast<T*>(&pack);
+#pragma unroll
+                    for (int k = 0; k < W; ++k) e[k] = v[i * W + k];
+                    reinterpret_cast<V*>(row)[i] = pack;
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < DP2; ++c) row[c] = v[c];
+            }
+        }
+        if (step % RS == 0) {
+            const int in_group = min(RS, cnt - step);
+            __syncwarp();
+            if constexpr (DP2 < 32) {
+                const int sl = lane / DP2, c = lane % DP2;
+                if (sl < in_group && c < D) {
+                    const T* col = tbuf + sl * SLAB + c;
+                    T a0 = T(0), a1 = T(0), a2 = T(0), a3 = T(0);
+#pragma unroll
+                    for (int r = 0; r < 32; r += 4) {
+                        a0 += col[(r + 0) * ROWP];
+                        a1 += col[(r + 1) * ROWP];
+                        a2 += col[(r + 2) * ROWP];
+                        a3 += col[(r + 3) * ROWP];
+                    }
+                    atomicAdd(gbuf + (step + sl) * D + c, (a0 + a1) + (a2 + a3));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < DP2 / 32; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < D) {
+                        const T* col = tbuf + c;
+                        T a0 = T(0), a1 = T(0);
+#pragma unroll
+                        for (int r = 0; r < 32; r += 2) {
+                            a0 += col[(r + 0) * ROWP];
+                            a1 += col[(r + 1) * ROWP];
+                        }
+                        atomicAdd(gbuf + step * D + c, a0 + a1);
+                    }
+                }
+            }
+            __syncwarp();
         }
         // (2) chain letters: units sharing letter p[k] are STRIDE consecutive units, so a
         // partial butterfly sums them before one lane per group adds the total
@@ -397,7 +476,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
                 else if constexpr (Sh::NG == 1) v[c] = g.gz[c] + g.gg[c];
                 else v[c] = sig_fma(gmask[c / G], g.gg[c % G], g.gz[c]);
             }
-            reduce_step(v, g.gc, step);
+            reduce_step(v, g.gc, step, cnt);
         }
         __syncwarp();
         // flush the chunk: one atomic per (step, channel)

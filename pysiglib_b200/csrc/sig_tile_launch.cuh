@@ -63,7 +63,7 @@ void tile_backward_launch(const void* pv_, void* incr_grad, const void* sig, con
     using Sh = TileShape<D, N, P, G>;
     constexpr int W = kTileWarpsPerBlock;
     const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
-    const size_t smem = size_t(W) * kTileChunk * (RowPad<T, D>::DP + D) * sizeof(T);
+    const size_t smem = size_t(W) * BackwardSmem<T, D>::PER_WARP * sizeof(T);
     BackwardSegments<T> segs;
     if (nseg > 1 && segments) segs = *static_cast<const BackwardSegments<T>*>(segments);
     const unsigned grid = tile_grid(batch * uint64_t(segs.nseg), Sh::UNITS);
@@ -101,7 +101,7 @@ int tile_forward_occupancy(bool flags) {
 template <typename T, int D, int N, int P, int G>
 int tile_backward_occupancy(bool flags) {
     using Sh = TileShape<D, N, P, G>;
-    const size_t smem = size_t(kTileWarpsPerBlock) * kTileChunk * (RowPad<T, D>::DP + D) * sizeof(T);
+    const size_t smem = size_t(kTileWarpsPerBlock) * BackwardSmem<T, D>::PER_WARP * sizeof(T);
     return flags ? tile_occupancy_of(tile_backward_kernel<T, Sh, true, kTileWarpsPerBlock>, smem)
                  : tile_occupancy_of(tile_backward_kernel<T, Sh, false, kTileWarpsPerBlock>, smem);
 }

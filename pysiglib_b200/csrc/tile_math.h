@@ -53,6 +53,111 @@ template <> SIG_HD float sig_fma<float>(float a, float b, float c) { return ::fm
 template <> SIG_HD double sig_fma<double>(double a, double b, double c) { return ::fma(a, b, c); }
 #endif
 
+// Row primitives over the D children of one node.  In device code for float they use the
+// packed two-wide FP32 instructions of sm_100 (fma/mul.rn.f32x2 through __ffma2_rn / __fmul2_rn):
+// one issue slot performs two operations, which relieves the issue pressure of these
+// FMA-bound kernels; every element still gets one correctly rounded FMA, so results are
+// identical to the scalar form.  Host builds and double use the scalar loops.
+#if defined(__CUDA_ARCH__)
+#define SIG_PACKED_F32 1
+#else
+#define SIG_PACKED_F32 0
+#endif
+
+template <typename T> struct is_f32 { static constexpr bool value = false; };
+template <> struct is_f32<float> { static constexpr bool value = true; };
+
+// s[c] = fma(z[c], v, s[c])
+template <typename T, int n>
+SIG_HD void row_axpy(T* s, const T* z, T v) {
+#if SIG_PACKED_F32
+    if constexpr (is_f32<T>::value) {
+        const float2 vv = make_float2(v, v);
+#pragma unroll
+        for (int c = 0; c + 1 < n; c += 2) {
+            const float2 r = __ffma2_rn(make_float2(z[c], z[c + 1]), vv, make_float2(s[c], s[c + 1]));
+            s[c] = r.x;
+            s[c + 1] = r.y;
+        }
+        if (n % 2) s[n - 1] = sig_fma(z[n - 1], v, s[n - 1]);
+        return;
+    }
+#endif
+#pragma unroll
+    for (int c = 0; c < n; ++c) s[c] = sig_fma(z[c], v, s[c]);
+}
+
+// w[c] = z[c] * v
+template <typename T, int n>
+SIG_HD void row_scale(T* w, const T* z, T v) {
+#if SIG_PACKED_F32
+    if constexpr (is_f32<T>::value) {
+        const float2 vv = make_float2(v, v);
+#pragma unroll
+        for (int c = 0; c + 1 < n; c += 2) {
+            const float2 r = __fmul2_rn(make_float2(z[c], z[c + 1]), vv);
+            w[c] = r.x;
+            w[c + 1] = r.y;
+        }
+        if (n % 2) w[n - 1] = z[n - 1] * v;
+        return;
+    }
+#endif
+#pragma unroll
+    for (int c = 0; c < n; ++c) w[c] = z[c] * v;
+}
+
+// g[c] = fma(a[c], v, g[c]);  returns sum_c a[c] * z[c]
+template <typename T, int n>
+SIG_HD T row_pull(T* g, const T* a, const T* z, T v) {
+#if SIG_PACKED_F32
+    if constexpr (is_f32<T>::value) {
+        const float2 vv = make_float2(v, v);
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c + 1 < n; c += 2) {
+            const float2 aa = make_float2(a[c], a[c + 1]);
+            const float2 r = __ffma2_rn(aa, vv, make_float2(g[c], g[c + 1]));
+            g[c] = r.x;
+            g[c + 1] = r.y;
+            acc = __ffma2_rn(aa, make_float2(z[c], z[c + 1]), acc);
+        }
+        float total = acc.x + acc.y;
+        if (n % 2) {
+            g[n - 1] = sig_fma(a[n - 1], v, g[n - 1]);
+            total = sig_fma(a[n - 1], z[n - 1], total);
+        }
+        return total;
+    }
+#endif
+    T acc = T(0);
+#pragma unroll
+    for (int c = 0; c < n; ++c) {
+        g[c] = sig_fma(a[c], v, g[c]);
+        acc = sig_fma(a[c], z[c], acc);
+    }
+    return acc;
+}
+
+// a[c] += x[c]
+template <typename T, int n>
+SIG_HD void row_add(T* a, const T* x) {
+#if SIG_PACKED_F32
+    if constexpr (is_f32<T>::value) {
+#pragma unroll
+        for (int c = 0; c + 1 < n; c += 2) {
+            const float2 r = __fadd2_rn(make_float2(a[c], a[c + 1]), make_float2(x[c], x[c + 1]));
+            a[c] = r.x;
+            a[c + 1] = r.y;
+        }
+        if (n % 2) a[n - 1] += x[n - 1];
+        return;
+    }
+#endif
+#pragma unroll
+    for (int c = 0; c < n; ++c) a[c] += x[c];
+}
+
 template <int D_, int N_, int P_, int G_>
 struct TileShape {
     static constexpr int D = D_;   // augmented path dimension
@@ -94,8 +199,7 @@ SIG_HD void tile_init_first(TileState<T, Sh>& st, const T (&z)[Sh::D], const T (
 #pragma unroll
         for (int j = 0; j < Sh::nodes(q - 1); ++j) {
             const T v = st.s[Sh::off(q - 1) + j] * rcp_of<T>(Sh::P + q);
-#pragma unroll
-            for (int c = 0; c < Sh::D; ++c) st.s[Sh::off(q) + j * Sh::D + c] = z[c] * v;
+            row_scale<T, Sh::D>(&st.s[Sh::off(q) + j * Sh::D], z, v);
         }
     }
 }
@@ -135,8 +239,7 @@ SIG_HD void tile_update(TileState<T, Sh>& st, const T (&z)[Sh::D], const T (&zg)
 #pragma unroll
                     for (int j = 0; j < Sh::nodes(q - 1); ++j) {
                         const T v = (w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j]) * rcp_of<T>(t - q + 1);
-#pragma unroll
-                        for (int c = 0; c < D; ++c) w[Sh::off(q) + j * D + c] = z[c] * v;
+                        row_scale<T, D>(&w[Sh::off(q) + j * D], z, v);
                     }
                 }
             }
@@ -146,9 +249,7 @@ SIG_HD void tile_update(TileState<T, Sh>& st, const T (&z)[Sh::D], const T (&zg)
 #pragma unroll
                     for (int j = 0; j < Sh::nodes(q - 1); ++j) {
                         const T v = w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j];
-#pragma unroll
-                        for (int c = 0; c < D; ++c)
-                            st.s[Sh::off(q) + j * D + c] = sig_fma(z[c], v, st.s[Sh::off(q) + j * D + c]);
+                        row_axpy<T, D>(&st.s[Sh::off(q) + j * D], z, v);
                     }
                 }
             }
@@ -307,8 +408,7 @@ SIG_HD void tile_pullback(const TileState<T, Sh>& st, TileAdjoint<T, Sh>& ad, Ti
 #pragma unroll
                     for (int j = 0; j < Sh::nodes(q - 1); ++j) {
                         const T v = (w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j]) * rcp_of<T>(t - q + 1);
-#pragma unroll
-                        for (int c = 0; c < D; ++c) w[Sh::off(q) + j * D + c] = z[c] * v;
+                        row_scale<T, D>(&w[Sh::off(q) + j * D], z, v);
                     }
                 }
             }
@@ -319,14 +419,7 @@ SIG_HD void tile_pullback(const TileState<T, Sh>& st, TileAdjoint<T, Sh>& ad, Ti
 #pragma unroll
                     for (int j = 0; j < Sh::nodes(q - 1); ++j) {
                         const T v = w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j];
-                        T acc = T(0);
-#pragma unroll
-                        for (int c = 0; c < D; ++c) {
-                            const T a = ad.a[Sh::off(q) + j * D + c];
-                            g.gz[c] = sig_fma(a, v, g.gz[c]);
-                            acc = sig_fma(a, z[c], acc);
-                        }
-                        wa[Sh::off(q - 1) + j] = acc;
+                        wa[Sh::off(q - 1) + j] = row_pull<T, D>(g.gz, &ad.a[Sh::off(q) + j * D], z, v);
                     }
                 }
             }
@@ -338,15 +431,8 @@ SIG_HD void tile_pullback(const TileState<T, Sh>& st, TileAdjoint<T, Sh>& ad, Ti
 #pragma unroll
                     for (int j = 0; j < Sh::nodes(q - 1); ++j) {
                         const T v = (w[Sh::off(q - 1) + j] + st.s[Sh::off(q - 1) + j]) * r;
-                        T acc = T(0);
-#pragma unroll
-                        for (int c = 0; c < D; ++c) {
-                            const T x = wa[Sh::off(q) + j * D + c];
-                            ad.a[Sh::off(q) + j * D + c] += x;
-                            g.gz[c] = sig_fma(x, v, g.gz[c]);
-                            acc = sig_fma(x, z[c], acc);
-                        }
-                        wa[Sh::off(q - 1) + j] = acc * r;
+                        row_add<T, D>(&ad.a[Sh::off(q) + j * D], &wa[Sh::off(q) + j * D]);
+                        wa[Sh::off(q - 1) + j] = row_pull<T, D>(g.gz, &wa[Sh::off(q) + j * D], z, v) * r;
                     }
                 }
             }
