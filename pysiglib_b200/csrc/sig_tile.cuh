@@ -322,7 +322,6 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     const int u = int(gw - vp * WPP) * 32 + lane;
     const bool active = u < Sh::UNITS;
     const UnitIndex<Sh> ix = decode_unit<Sh>(active ? u : 0);
-    const int grp = ix.c0 / G;
     const T* x = pv.base + b * pv.path_stride;
     T* gout = incr_grad + b * uint64_t(pv.L - 1) * pv.d;
 
@@ -348,18 +347,12 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
         for (int i = 0; i < Sh::TS; ++i) ad.a[i] = T(0);
     }
 
-    // 1 for the unit's own child group, 0 for the others (folds gg into the static letters)
-    T gmask[Sh::NG];
-#pragma unroll
-    for (int m = 0; m < Sh::NG; ++m) gmask[m] = grp == m ? T(1) : T(0);
-
     // Warp-wide sum of one step's per-unit gradients into gbuf[step][letter] (zeroed at the
     // start of the chunk).
-    auto reduce_step = [&](T (&v)[DP2], const T* gc, int step, int cnt) {
-        // (1) letters with static indices (the unit's own children were folded in by the caller):
+    auto reduce_step = [&](T (&v)[DP2], const T* gg, const T* gc, int step, int cnt) {
+        // (1) letters with static indices:
         // every lane parks its vector in its own row of tbuf; once the RS steps of a group are
         // there, each lane sums one column (one letter of one step) over the 32 rows.
-        T* grow = gbuf + step * D;
         {
             T* row = tbuf + (step % RS) * SLAB + lane * ROWP;
             if constexpr (DP2 >= 4) {
@@ -377,6 +370,28 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
 #pragma unroll
                 for (int c = 0; c < DP2; ++c) row[c] = v[c];
             }
+        }
+        // The letters that depend on the unit (its own children c0 + j, its chain letters p[k])
+        // are added to the lane's private row in place: plain read-modify-write, no atomics.
+        {
+            T* row = tbuf + (step % RS) * SLAB + lane * ROWP;
+            if constexpr (G % VecOf<T>::n == 0 && DP2 >= 4) {
+                using V = typename VecOf<T>::type;
+                constexpr int W = VecOf<T>::n;
+#pragma unroll
+                for (int i = 0; i < G / W; ++i) {
+                    V pack = reinterpret_cast<V*>(row + ix.c0)[i];
+                    T* e = reinterpret_cast<T*>(&pack);
+#pragma unroll
+                    for (int k = 0; k < W; ++k) e[k] += gg[i * W + k];
+                    reinterpret_cast<V*>(row + ix.c0)[i] = pack;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < G; ++j) row[ix.c0 + j] += gg[j];
+            }
+#pragma unroll
+            for (int k = 0; k < P; ++k) row[ix.p[k]] += gc[k];
         }
         if (step % RS == 0) {
             const int in_group = min(RS, cnt - step);
@@ -412,25 +427,6 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
                 }
             }
             __syncwarp();
-        }
-        // (2) chain letters: units sharing letter p[k] are STRIDE consecutive units, so a
-        // partial butterfly sums them before one lane per group adds the total
-#pragma unroll
-        for (int k = 0; k < P; ++k) {
-            const int stride = cpow(D, P - 1 - k) * Sh::NG;
-            T xk = gc[k];
-            if (stride % 32 == 0) {
-#pragma unroll
-                for (int m = 16; m >= 1; m >>= 1) xk += __shfl_xor_sync(0xffffffffu, xk, m);
-                if (lane == 0) atomicAdd(grow + ix.p[k], xk);
-            } else if (32 % stride == 0) {
-#pragma unroll
-                for (int m = 1; m < 32; m <<= 1)
-                    if (m < stride) xk += __shfl_xor_sync(0xffffffffu, xk, m);
-                if ((lane & (stride - 1)) == 0) atomicAdd(grow + ix.p[k], xk);
-            } else {
-                atomicAdd(grow + ix.p[k], xk);
-            }
         }
     };
 
@@ -468,15 +464,10 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
             for (int k = 0; k < (P > 0 ? P : 1); ++k) g.gc[k] = T(0);
             tile_pullback<T, Sh>(st, ad, g, op.z, op.zg, op.zc);
 
-            // fold the unit's own children (letters c0 + j) into the static letters with a 0/1 mask
             T v[DP2];
 #pragma unroll
-            for (int c = 0; c < DP2; ++c) {
-                if (c >= D) v[c] = T(0);
-                else if constexpr (Sh::NG == 1) v[c] = g.gz[c] + g.gg[c];
-                else v[c] = sig_fma(gmask[c / G], g.gg[c % G], g.gz[c]);
-            }
-            reduce_step(v, g.gc, step, cnt);
+            for (int c = 0; c < DP2; ++c) v[c] = c < D ? g.gz[c] : T(0);
+            reduce_step(v, g.gg, g.gc, step, cnt);
         }
         __syncwarp();
         // flush the chunk: one atomic per (step, channel)
