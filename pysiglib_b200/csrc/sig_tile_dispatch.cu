@@ -1,6 +1,8 @@
 // Run-time choice among the compiled register-tile variants (tile_table.h).
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <string>
@@ -55,27 +57,21 @@ int occupancy_of(const TileEntry& e, bool flags, int device) {
     return occ;
 }
 
-// Issue-slot utilisation reached with w resident warps per SM sub-partition.  Calibrated on
-// B200 with these kernels: a warp with a big register tile has many independent FMAs in flight
-// and needs few neighbours to hide its latencies (136 values: 0.87 at w = 2), a small tile is
-// dominated by its dependent chain (36 values: 0.67 at w = 2).  FP64 FMAs occupy their pipe
-// for two issue cycles, so utilisation above one half cannot be used.
-double issue_utilisation(int w, int tile_values, bool is_double) {
-    const double k = std::min(1.1, 0.35 + 0.005 * tile_values);
-    const double u = std::min(0.92, 1.0 - std::exp(-k * w));
-    return is_double ? std::min(u, 0.5) : u;
-}
+// Relative time of one wave in which every SM runs r CTAs of the same sweep, in units of
+// the time a lone CTA needs.  Calibrated on B200 by forcing plans one by one (C4 shape,
+// float32): a single CTA per SM already keeps the FMA pipe about half busy (a step is a long
+// run of independent packed FMAs after a short dependent prologue), so co-resident CTAs
+// mostly take turns: each extra CTA costs about 0.8 of a lone one.  Splitting a sweep into
+// more CTAs therefore pays while SMs are idle and hardly at all afterwards.
+double wave_cost(int r) { return 1.0 + 0.8 * (r - 1); }
 
-// Modelled sweep time (arbitrary units) of `blocks` CTAs of 4 warps, each running `steps`
-// steps of `instr` issue slots, on `sms` SMs holding at most `occ` CTAs each.
+// Modelled sweep time (issue slots of the busiest SM) of `blocks` CTAs of 4 warps, each
+// running `steps` steps of e.est_instr slots, on `sms` SMs holding at most `occ` CTAs each.
 double modelled_time(uint64_t blocks, int occ, int sms, double steps, const TileEntry& e) {
     const uint64_t capacity = uint64_t(occ) * sms;
     const uint64_t full = blocks / capacity, rem = blocks % capacity;
-    double t = double(full) * occ / issue_utilisation(occ, e.tile_values, e.is_double);
-    if (rem) {
-        const int r = int((rem + sms - 1) / sms);
-        t += r / issue_utilisation(r, e.tile_values, e.is_double);
-    }
+    double t = double(full) * wave_cost(occ);
+    if (rem) t += wave_cost(int((rem + sms - 1) / sms));
     return t * steps * e.est_instr;
 }
 
@@ -96,7 +92,8 @@ Plan choose(bool is_double, bool backward, const SigShape& s, int sm_count, bool
     const TileEntry* fwd_big = nullptr;  // biggest forward tile: sweeps the segments of a segmented backward
     for (const TileEntry& e : tile_table())
         if (e.is_double == is_double && !e.backward && e.D == int(s.dim) && e.N == int(s.degree)) { fwd_big = &e; break; }
-    const double join_cost = double(s.full_len) * s.degree / 32.0 * s.batch / (4.0 * sms) * 6.0 + 4000.0;
+    // one pairwise Chen product / left adjoint over the batch: about 25 issue slots per term, plus launch
+    const double join_cost = double(s.full_len) * s.degree / 32.0 * s.batch / (4.0 * sms) * 25.0 + 10000.0;
     for (const TileEntry& e : tile_table()) {
         if (e.is_double != is_double || e.backward != backward || e.D != int(s.dim) || e.N != int(s.degree)) continue;
         if (!first) first = &e;
@@ -104,6 +101,12 @@ Plan choose(bool is_double, bool backward, const SigShape& s, int sm_count, bool
         if (pref == 1 || pref == 2 || pref == 4 || device < 0) continue;
         const int occ = occupancy_of(e, flags, device);
         const uint64_t wpp = uint64_t((e.units + 31) / 32);
+        if (&e == first && (s.batch * wpp + kTileWarpsPerBlock - 1) / kTileWarpsPerBlock >= uint64_t(occ) * sms) {
+            // the biggest tile already fills every SM to its occupancy: nothing to trade
+            plan.entry = &e;
+            plan.nseg = 1;
+            break;
+        }
         for (int nseg : kSegments) {
             // segment scratch: forward nseg + joins (about 2 nseg signatures), backward 3 nseg
             if (nseg > 1 && (pref == 3 || steps / nseg < 64 || seg_bytes * 3 * nseg > (1ull << 30))) break;
@@ -130,6 +133,21 @@ Plan choose(bool is_double, bool backward, const SigShape& s, int sm_count, bool
         }
     }
     plan.forward_for_segments = fwd_big;
+    // Tuning aid: SIGB200_FORCE_PLAN="P,G,segments" (forward) / SIGB200_FORCE_PLAN_BWD pins the
+    // variant and segment count when such a variant is compiled for the shape.
+    if (const char* forced = std::getenv(backward ? "SIGB200_FORCE_PLAN_BWD" : "SIGB200_FORCE_PLAN")) {
+        int fp = -1, fg = -1, fs = 1;
+        if (std::sscanf(forced, "%d,%d,%d", &fp, &fg, &fs) >= 2) {
+            for (const TileEntry& e : tile_table())
+                if (e.is_double == is_double && e.backward == backward && e.D == int(s.dim) && e.N == int(s.degree) &&
+                    e.P == fp && e.G == fg) {
+                    plan.entry = &e;
+                    plan.nseg = int(std::max<uint64_t>(1, std::min<uint64_t>(uint64_t(fs), steps)));
+                    if (backward && !fwd_big) plan.nseg = 1;
+                    return plan;
+                }
+        }
+    }
     if (pref == 1 || pref == 4 || (device < 0 && first)) plan.entry = first, plan.nseg = 1;
     if (pref == 2) plan.entry = last, plan.nseg = 1;
     if (pref == 4 && plan.entry && (!backward || fwd_big)) plan.nseg = int(std::min<uint64_t>(3, steps));
