@@ -80,11 +80,12 @@ SIG_HD void row_axpy(T* s, const T* z, T v) {
             s[c + 1] = r.y;
         }
         if (n % 2) s[n - 1] = sig_fma(z[n - 1], v, s[n - 1]);
-        return;
-    }
+    } else
 #endif
+    {
 #pragma unroll
-    for (int c = 0; c < n; ++c) s[c] = sig_fma(z[c], v, s[c]);
+        for (int c = 0; c < n; ++c) s[c] = sig_fma(z[c], v, s[c]);
+    }
 }
 
 // w[c] = z[c] * v
@@ -100,11 +101,12 @@ SIG_HD void row_scale(T* w, const T* z, T v) {
             w[c + 1] = r.y;
         }
         if (n % 2) w[n - 1] = z[n - 1] * v;
-        return;
-    }
+    } else
 #endif
+    {
 #pragma unroll
-    for (int c = 0; c < n; ++c) w[c] = z[c] * v;
+        for (int c = 0; c < n; ++c) w[c] = z[c] * v;
+    }
 }
 
 // g[c] = fma(a[c], v, g[c]);  returns sum_c a[c] * z[c]
@@ -128,15 +130,17 @@ SIG_HD T row_pull(T* g, const T* a, const T* z, T v) {
             total = sig_fma(a[n - 1], z[n - 1], total);
         }
         return total;
-    }
+    } else
 #endif
-    T acc = T(0);
+    {
+        T acc = T(0);
 #pragma unroll
-    for (int c = 0; c < n; ++c) {
-        g[c] = sig_fma(a[c], v, g[c]);
-        acc = sig_fma(a[c], z[c], acc);
+        for (int c = 0; c < n; ++c) {
+            g[c] = sig_fma(a[c], v, g[c]);
+            acc = sig_fma(a[c], z[c], acc);
+        }
+        return acc;
     }
-    return acc;
 }
 
 // a[c] += x[c]
@@ -151,11 +155,12 @@ SIG_HD void row_add(T* a, const T* x) {
             a[c + 1] = r.y;
         }
         if (n % 2) a[n - 1] += x[n - 1];
-        return;
-    }
+    } else
 #endif
+    {
 #pragma unroll
-    for (int c = 0; c < n; ++c) a[c] += x[c];
+        for (int c = 0; c < n; ++c) a[c] += x[c];
+    }
 }
 
 template <int D_, int N_, int P_, int G_>
