@@ -42,7 +42,8 @@ def _units():
 
 
 def _stamp(dev=False):
-    h = hashlib.sha256((" ".join(NVCC_FLAGS) + (" dev" if dev else "")).encode())
+    h = hashlib.sha256((" ".join(NVCC_FLAGS) + (" dev" if dev else "") +
+                        os.environ.get("SIGB200_NO_PACKED_F32", "0")).encode())
     for name in sorted(os.listdir(CSRC)):
         if name.endswith((".h", ".cuh", ".cu")):
             with open(os.path.join(CSRC, name), "rb") as f:
@@ -73,6 +74,8 @@ def build(force=False, jobs=None, verbose=False, dev=None):
     if dev is None:
         dev = os.environ.get("SIGB200_TILE_DEV", "0") == "1"
     _EXTRA[:] = ["-DSIG_TILE_DEV"] if dev else []
+    if os.environ.get("SIGB200_NO_PACKED_F32", "0") == "1":  # experiment switch: scalar FP32 rows
+        _EXTRA.append("-DSIG_NO_PACKED_F32")
     os.makedirs(OBJ, exist_ok=True)
     os.makedirs(LIB_DIR, exist_ok=True)
     stamp, stamp_file = _stamp(dev), os.path.join(LIB_DIR, "stamp.txt")
