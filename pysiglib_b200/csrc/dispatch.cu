@@ -173,6 +173,10 @@ void backward_on_device(const T* path, T* out, const T* sig_derivs, const T* sig
         launch_fill<T>(out, out_elems, T(0), stream);
         return;
     }
+    if (s.degree == 1) {
+        launch_degree_one_backward<T>(path, out, sig_derivs, s, end_time, stream);
+        return;
+    }
     if (s.degree > kMaxDegree)
         throw std::invalid_argument("sig_backprop on CUDA requires degree <= 64. Reduce the truncation level.");
     if (kernel_policy() == 0 && tile_backward_available<T>(s)) {

@@ -24,6 +24,11 @@ LevelIndex make_level_index(uint64_t dim, uint64_t degree);
 template <typename T>
 void launch_trivial_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream);
 
+// Degree-1 backward (closed form: only the end points of a path get a gradient).
+template <typename T>
+void launch_degree_one_backward(const T* path, T* out, const T* sig_derivs, const SigShape& s, T end_time,
+                                cudaStream_t stream);
+
 // ---- generic (any dimension / degree) level-synchronous kernels, one CTA per path ----
 // scratch: generic_forward_scratch_elems(s) elements per CTA, `ctas` CTAs.
 uint64_t generic_forward_scratch_elems(const SigShape& s);

@@ -65,6 +65,27 @@ __global__ void trivial_forward_kernel(PathView<T> pv, T* out, uint64_t total, u
     out[idx] = v;
 }
 
+// Degree-1 backward in closed form: S_1 is the total increment, so only the end points get a
+// gradient (+-dS_1; with lead-lag the lag and lead halves add up, the time channel has none).
+template <typename T>
+__global__ void degree_one_backward_kernel(PathView<T> pv, T* out, const T* derivs, uint64_t total, uint32_t stride,
+                                           bool scalar) {
+    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const uint64_t row = idx / uint32_t(pv.d);  // b * L + t
+    const int c = int(idx - row * uint32_t(pv.d));
+    const uint64_t b = row / uint32_t(pv.L);
+    const int t = int(row - b * uint32_t(pv.L));
+    T v = T(0);
+    if (t == 0 || t == pv.L - 1) {
+        const T* ds = derivs + b * stride + (scalar ? 1 : 0);
+        T g = ds[c];
+        if (pv.lead_lag) g += ds[pv.d + c];
+        v = t == 0 ? -g : g;
+    }
+    out[idx] = v;
+}
+
 // ---- block-cooperative Horner step on a scalar-term layout signature --------
 
 template <typename T>
@@ -462,9 +483,30 @@ void launch_trivial_forward(const T* path, T* out, const SigShape& s, T end_time
 }
 
 template <typename T>
+void launch_degree_one_backward(const T* path, T* out, const T* sig_derivs, const SigShape& s, T end_time,
+                                cudaStream_t stream) {
+    const uint64_t total = checked_mul(s.batch, checked_mul(s.data_len, s.data_dim, "path gradient"), "path gradient");
+    if (total == 0) return;
+    if (s.data_dim >= (1ull << 31) || s.data_len >= (1ull << 31) || s.stride >= (1ull << 32))
+        throw std::invalid_argument("path too large for the CUDA kernels");
+    const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
+    degree_one_backward_kernel<T><<<grid_1d(total, 256), 256, 0, stream>>>(
+        pv, out, sig_derivs, total, static_cast<uint32_t>(s.stride), s.scalar_term);
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+void check_generic_smem(size_t bytes) {
+    if (bytes > 200 * 1024)
+        throw std::invalid_argument("path dimension too large for the CUDA kernels at this degree (the increment "
+                                    "vector of one step must fit in shared memory)");
+}
+
+template <typename T>
 void launch_generic_forward(const T* path, T* out, const SigShape& s, T end_time, T* scratch, unsigned ctas,
                             cudaStream_t stream) {
     check_generic_limits(s);
+    check_generic_smem((s.dim + s.degree + 1) * sizeof(T));
     const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
     const size_t smem = (s.dim + s.degree + 1) * sizeof(T);
     if (smem > 48 * 1024)
@@ -481,6 +523,7 @@ template <typename T>
 void launch_generic_backward(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
                              T end_time, T* scratch, unsigned ctas, cudaStream_t stream) {
     check_generic_limits(s);
+    check_generic_smem((3 * s.dim + s.degree + 1) * sizeof(T));
     const PathView<T> pv = make_path_view(path, s.data_dim, s.data_len, s.time_aug, s.lead_lag, end_time);
     const size_t smem = (3 * s.dim + s.degree + 1) * sizeof(T);
     if (smem > 48 * 1024)
@@ -589,6 +632,7 @@ void launch_nonfinite_scan(const T* data, uint64_t n, int* flag, cudaStream_t st
     template void launch_chen_combine<T>(T*, const T*, T*, const SigShape&, int, cudaStream_t);                   \
     template void launch_chen_product<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t); \
     template void launch_chen_left_adjoint<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t); \
+    template void launch_degree_one_backward<T>(const T*, T*, const T*, const SigShape&, T, cudaStream_t); \
     template void launch_fill<T>(T*, uint64_t, T, cudaStream_t);                                         \
     template void launch_nonfinite_scan<T>(const T*, uint64_t, int*, cudaStream_t);
 INSTANTIATE(float)

@@ -239,6 +239,76 @@ def test_large_batch_crosses_grid_and_chunk_boundaries():
     np.testing.assert_allclose(got, oracle.sig(path, 2, n_threads=8), rtol=1e-5, atol=1e-6)
 
 
+def test_wide_paths_like_the_reference_resource_limit_tests():
+    """Shapes of the reference's tests/test_signature_cuda_shared_memory.py and
+    tests/test_cuda_memory_fallbacks.py: very wide paths at low degree."""
+    rng = np.random.default_rng(29)
+    for dtype, tol in ((np.float32, 1e-5), (np.float64, 1e-10)):
+        p = rng.normal(size=(16, 127, 98)).astype(dtype)
+        np.testing.assert_allclose(run_forward(p, 1), oracle.sig(p, 1), rtol=tol, atol=tol)
+        p = rng.normal(size=(1, 2, 350)).astype(dtype)
+        s = run_forward(p, 2)
+        assert_sig_close(s, oracle.sig(p, 2), 350, 2, tol)
+        g = run_backward(p, s, np.ones_like(s), 2)
+        np.testing.assert_allclose(g, oracle.sig_backprop(p, oracle.sig(p, 2), np.ones_like(s), 2), rtol=2e-4, atol=2e-4)
+        p = rng.normal(size=(1, 127, 1000)).astype(dtype)
+        s = run_forward(p, 1)
+        np.testing.assert_allclose(s, p[:, -1] - p[:, 0], rtol=tol, atol=tol)
+        g = run_backward(p, s, np.ones_like(s), 1)
+        assert not g[:, 1:-1].any() and np.all(g[:, 0] == -1) and np.all(g[:, -1] == 1)
+        # d = 100000, degree 1, weighted seeds; then lead-lag with d = 50000
+        p = rng.normal(size=(1, 3, 100000)).astype(dtype)
+        for scalar_term in (False, True):
+            s = run_forward(p, 1, scalar_term=scalar_term)
+            w = np.linspace(-0.25, 0.5, s.size).astype(dtype).reshape(s.shape)
+            g = run_backward(p, s, w, 1, scalar_term=scalar_term)
+            np.testing.assert_array_equal(g[0, 0], -w[0, -100000:])
+            np.testing.assert_array_equal(g[0, 1], 0)
+            np.testing.assert_array_equal(g[0, 2], w[0, -100000:])
+        p = rng.normal(size=(1, 3, 50000)).astype(dtype)
+        s = run_forward(p, 1, lead_lag=True)
+        np.testing.assert_allclose(s, oracle.sig(p, 1, lead_lag=True), rtol=tol, atol=tol)
+        g = run_backward(p, s, np.ones_like(s), 1, lead_lag=True)
+        np.testing.assert_allclose(g, oracle.sig_backprop(p, oracle.sig(p, 1, lead_lag=True), np.ones_like(s), 1,
+                                                          lead_lag=True), rtol=tol, atol=tol)
+
+
+def test_concurrent_calls_from_two_host_threads():
+    """The C ABI is callable from any host thread; device-pointer calls on different streams do not
+    share scratch memory (stream-ordered pool), host-pointer calls serialise on the staging streams."""
+    import threading
+    import pysiglib_b200
+    paths = [brownian_paths(40 + i, 64, 200, 8, np.float32) for i in range(2)]
+    expect = [oracle.sig(p, 4, n_threads=4) for p in paths]
+    results = [None, None, None, None]
+
+    def device_worker(i):
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            t = torch.tensor(paths[i], device="cuda")
+            for _ in range(5):
+                s = pysiglib_b200.sig(t, 4)
+                g = pysiglib_b200.sig_backprop(t, s, torch.ones_like(s), 4)
+            st.synchronize()
+        results[i] = (s.cpu().numpy(), g.cpu().numpy())
+
+    def host_worker(i):
+        for _ in range(3):
+            results[2 + i] = pysiglib_b200.sig(paths[i], 4)
+
+    threads = [threading.Thread(target=device_worker, args=(i,)) for i in range(2)] + \
+              [threading.Thread(target=host_worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for i in range(2):
+        assert_sig_close(results[i][0], expect[i], 8, 4, 1e-5)
+        assert_sig_close(results[2 + i], expect[i], 8, 4, 1e-5)
+        want = oracle.sig_backprop(paths[i], expect[i], np.ones_like(expect[i]), 4, n_threads=4)
+        np.testing.assert_allclose(results[i][1], want, rtol=1e-3, atol=1e-4 * np.abs(want).max())
+
+
 # ---- device pointers, streams, autograd ----
 
 def test_device_pointers_and_python_api():
