@@ -4,9 +4,9 @@
 # Only two translation units are needed for signature_cuda_* / sig_backprop_cuda_*:
 # siglib/cusig/cu_signature.cu and siglib/cusig/cu_path_transforms.cu (no Highway, oneTBB
 # or preparation library).  The reference's build system is not used.
-#   usage: oracle/build_ref_cuda.sh [/path/to/reference]     (takes 30-40 min of compiler time)
+#   usage: oracle/build_ref_cuda.sh /path/to/reference     (takes 15-40 min of compiler time)
 set -e
-REF="${1:-/root/reference}"
+REF="${1:?usage: build_ref_cuda.sh /path/to/reference}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 mkdir -p "$OUT"

@@ -166,6 +166,16 @@ def test_tile_variants_and_time_segmentation(pref, shape, dtype):
         p64 = path.astype(np.float64)
         truth = oracle.sig_backprop(p64, oracle.sig(p64, N), seeds.astype(np.float64), N)
         assert_grad_parity(run_backward(path, expect, seeds, N), want, truth, RTOL[dtype])
+        if d <= 5:  # flags through the same variants (lead-lag doubles the dimension)
+            kw = dict(time_aug=True, lead_lag=(d <= 3), end_time=0.8)
+            D = cabi.aug_dim(d, kw["time_aug"], kw["lead_lag"])
+            n_small = min(N, 4)
+            e2 = oracle.sig(path, n_small, **kw)
+            assert_sig_close(run_forward(path, n_small, **kw), e2, D, n_small, RTOL[dtype])
+            sd = np.ascontiguousarray(np.random.default_rng(L).normal(size=e2.shape).astype(dtype))
+            w2 = oracle.sig_backprop(path, e2, sd, n_small, **kw)
+            t2 = oracle.sig_backprop(p64, oracle.sig(p64, n_small, **kw), sd.astype(np.float64), n_small, **kw)
+            assert_grad_parity(run_backward(path, e2, sd, n_small, **kw), w2, t2, RTOL[dtype])
     finally:
         load_cusig.set_tile_preference(0)
 
@@ -365,6 +375,18 @@ def test_nonfinite_warning():
     big[0, 1] = -1e200
     with pytest.warns(RuntimeWarning, match="NaN or Inf"):
         pysiglib_b200.sig(torch.tensor(big, device="cuda"), 4)
+
+
+def test_sharded_call_reports_a_failing_shard_without_hanging():
+    """Host-side failure injection: a device ordinal that does not exist makes the whole call fail
+    with 'invalid argument' and a message; nothing is launched and later calls work."""
+    import pysiglib_b200
+    path = brownian_paths(8, 10, 20, 3, np.float32)
+    with pytest.raises(Exception, match="not available"):
+        pysiglib_b200.sig_sharded(path, 3, devices=[0, 99])
+    with pytest.raises(Exception, match="positive"):
+        pysiglib_b200.sig_sharded(path, 3, devices=[])
+    assert pysiglib_b200.sig_sharded(path, 3, devices=[0]).shape == (10, 39)
 
 
 def test_sharded_single_device_matches_plain():
