@@ -339,7 +339,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     const T* x = pv.base + b * pv.path_stride;
     T* gout = incr_grad + b * uint64_t(pv.L - 1) * pv.d;
 
-    TileState<T, Sh> st;
+    TileState<T, Sh, false> st;  // the reverse sweep keeps no level-N state (see TileState)
     TileAdjoint<T, Sh> ad;
     {
         // Signature and adjoint at the END of this time segment: the caller's arrays for the last
@@ -351,7 +351,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
             s_end = (seg == 0 ? segs.seg_sig : segs.state) + vp * slen - 1;
             a_end = segs.adjoint + vp * slen - 1;
         }
-        tile_load<T, Sh>(st, ad, ix, s_end, a_end);
+        tile_load<T, Sh, false>(st, ad, ix, s_end, a_end);
     }
     if (!active) {
         // idle lanes carry a zero adjoint so that they add nothing to the warp sums
@@ -467,7 +467,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
                 for (int j = 0; j < G; ++j) neg.zg[j] = -op.zg[j];
 #pragma unroll
                 for (int k = 0; k < P; ++k) neg.zc[k] = -op.zc[k];
-                tile_update<T, Sh>(st, neg.z, neg.zg, neg.zc);
+                tile_update<T, Sh, false>(st, neg.z, neg.zg, neg.zc);
             }
             TileGrad<T, Sh> g;
 #pragma unroll
@@ -476,7 +476,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
             for (int j = 0; j < G; ++j) g.gg[j] = T(0);
 #pragma unroll
             for (int k = 0; k < (P > 0 ? P : 1); ++k) g.gc[k] = T(0);
-            tile_pullback<T, Sh>(st, ad, g, op.z, op.zg, op.zc);
+            tile_pullback<T, Sh, false>(st, ad, g, op.z, op.zg, op.zc);
 
             T v[DP2];
 #pragma unroll

@@ -184,10 +184,15 @@ struct TileShape {
 template <typename T> SIG_HD T rcp_of(int k) { return T(1) / T(k); }
 
 // Per-unit state: chain coefficients ch[0..P] (ch[0] = 1) and the tile s[0..TS).
-template <typename T, typename Sh>
+// TOP = false drops the deepest tile level (the level-N coefficients).  The reverse sweep
+// never reads them: the pull-back of a step only needs the rewound levels below N, and
+// rewinding those does not involve level N either.  Leaving them out removes most of the
+// state registers, most of the signature reads and the largest FMA block of the rewind.
+template <typename T, typename Sh, bool TOP = true>
 struct TileState {
+    static constexpr int SIZE = TOP ? Sh::TS : (Sh::off(Sh::Q) > 0 ? Sh::off(Sh::Q) : 1);
     T ch[Sh::P + 1];
-    T s[Sh::TS];
+    T s[SIZE];
 };
 
 // First segment: S_k = S_{k-1} (x) z / k   (siglib/cpsig/cp_signature.h:365-389)
@@ -223,12 +228,12 @@ SIG_HD T tile_chain(const T* ch, const T* zc, int target, T* hist) {
 }
 
 // One Horner step with increment z (zg = z at the unit's children, zc = z at its chain letters).
-template <typename T, typename Sh>
-SIG_HD void tile_update(TileState<T, Sh>& st, const T (&z)[Sh::D], const T (&zg)[Sh::G], const T* zc) {
+template <typename T, typename Sh, bool TOP = true>
+SIG_HD void tile_update(TileState<T, Sh, TOP>& st, const T (&z)[Sh::D], const T (&zg)[Sh::G], const T* zc) {
     constexpr int P = Sh::P, Q = Sh::Q, D = Sh::D, G = Sh::G;
     T w[Sh::WS];
 #pragma unroll
-    for (int t = Q; t >= 1; --t) {
+    for (int t = (TOP ? Q : Q - 1); t >= 1; --t) {
         const int target = P + t;
         const T base = tile_chain<T, Sh, P>(st.ch, zc, target, nullptr) + st.ch[P];
         if (t == 1) {
@@ -323,8 +328,8 @@ struct TileAdjoint {
 
 // Loads the final signature and the seeds (dLoss/dSignature) of a unit; chain adjoints
 // are taken by the owning unit only, so that their sum over units is the true adjoint.
-template <typename T, typename Sh>
-SIG_HD void tile_load(TileState<T, Sh>& st, TileAdjoint<T, Sh>& ad, const UnitIndex<Sh>& ix, const T* S,
+template <typename T, typename Sh, bool TOP>
+SIG_HD void tile_load(TileState<T, Sh, TOP>& st, TileAdjoint<T, Sh>& ad, const UnitIndex<Sh>& ix, const T* S,
                       const T* dS) {
     st.ch[0] = T(1);
     ad.ac[0] = T(0);
@@ -339,7 +344,7 @@ SIG_HD void tile_load(TileState<T, Sh>& st, TileAdjoint<T, Sh>& ad, const UnitIn
         const int base = cgeom(Sh::D, Sh::P + q) + (ix.pw * Sh::D + ix.c0) * cpow(Sh::D, q - 1);
 #pragma unroll
         for (int j = 0; j < Sh::nodes(q); ++j) {
-            st.s[Sh::off(q) + j] = S[base + j];
+            if (TOP || q < Sh::Q) st.s[Sh::off(q) + j] = S[base + j];
             ad.a[Sh::off(q) + j] = dS[base + j];
         }
     }
@@ -358,8 +363,8 @@ struct TileGrad {
 
 // Pull the adjoint back through one Horner step taken with increment z from the
 // (already rewound) state st.  Accumulates into ad and into g (which the caller zeroes).
-template <typename T, typename Sh>
-SIG_HD void tile_pullback(const TileState<T, Sh>& st, TileAdjoint<T, Sh>& ad, TileGrad<T, Sh>& g,
+template <typename T, typename Sh, bool TOP>
+SIG_HD void tile_pullback(const TileState<T, Sh, TOP>& st, TileAdjoint<T, Sh>& ad, TileGrad<T, Sh>& g,
                           const T (&z)[Sh::D], const T (&zg)[Sh::G], const T* zc) {
     constexpr int P = Sh::P, Q = Sh::Q, D = Sh::D, G = Sh::G;
     T hist[P > 0 ? P : 1];

@@ -42,20 +42,20 @@ static void backward_path(const T* path, int L, const T* sig, const T* seeds, T*
     std::vector<T> incr(size_t(L - 1) * D, T(0));
     for (int u = 0; u < Sh::UNITS; ++u) {
         const UnitIndex<Sh> ix = decode_unit<Sh>(u);
-        TileState<T, Sh> st;
+        TileState<T, Sh, false> st;  // the reverse sweep keeps no level-N state
         TileAdjoint<T, Sh> ad;
-        tile_load<T, Sh>(st, ad, ix, sig - 1, seeds - 1);
+        tile_load<T, Sh, false>(st, ad, ix, sig - 1, seeds - 1);
         T zf[D], z[D], zg[Sh::G], zc[Sh::P + 1];
         for (int step = L - 2; step >= 0; --step) {
             for (int c = 0; c < D; ++c) zf[c] = path[(step + 1) * D + c] - path[step * D + c];
             gather_z<T, Sh>(zf, ix, z, zg, zc, T(-1));
-            tile_update<T, Sh>(st, z, zg, zc);
+            tile_update<T, Sh, false>(st, z, zg, zc);
             gather_z<T, Sh>(zf, ix, z, zg, zc, T(1));
             TileGrad<T, Sh> g;
             for (int c = 0; c < D; ++c) g.gz[c] = T(0);
             for (int j = 0; j < Sh::G; ++j) g.gg[j] = T(0);
             for (int k = 0; k < (Sh::P > 0 ? Sh::P : 1); ++k) g.gc[k] = T(0);
-            tile_pullback<T, Sh>(st, ad, g, z, zg, zc);
+            tile_pullback<T, Sh, false>(st, ad, g, z, zg, zc);
             T* row = incr.data() + size_t(step) * D;
             for (int c = 0; c < D; ++c) row[c] += g.gz[c];
             for (int j = 0; j < Sh::G; ++j) row[ix.c0 + j] += g.gg[j];
