@@ -57,6 +57,15 @@ int sig_backprop_cuda_d(const double* path, double* out, const double* sig_deriv
                         const double* correction, uint64_t correction_len,
                         uint64_t correction_batch_stride, uint64_t correction_segment_stride);
 
+/* Chen product of two batches of signatures: out = sig1 (x) sig2, the signature of the
+ * concatenated paths.  All three arrays are (batch, S) in the layout above.
+ * Replaces: siglib/cusig/cusig.h:363-365 (siglib/cusig/cu_sig_combine.cu); bound by
+ *           pysiglib/load_siglib.py:450-453.  Synchronous; device or host pointers. */
+int sig_combine_cuda_f(const float* sig1, const float* sig2, float* out, uint64_t batch_size,
+                       uint64_t dimension, uint64_t degree, bool scalar_term);
+int sig_combine_cuda_d(const double* sig1, const double* sig2, double* out, uint64_t batch_size,
+                       uint64_t dimension, uint64_t degree, bool scalar_term);
+
 /* Thread-local text of the last error; valid until the next call on this thread.
  * Replaces: siglib/cusig/cusig.h:43; bound by pysiglib/load_siglib.py:108-110. */
 const char* cusig_last_error_message(void);

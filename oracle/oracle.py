@@ -41,6 +41,9 @@ def _lib():
             bwd.restype = ctypes.c_int
             bwd.argtypes = [ptr, ptr, ptr, ptr, u64, u64, u64, u64, ctypes.c_int, ctypes.c_int,
                             real, ctypes.c_int, ctypes.c_int]
+            cmb = getattr(lib, "oracle_sig_combine_" + suf)
+            cmb.restype = ctypes.c_int
+            cmb.argtypes = [ptr, ptr, ptr, u64, u64, u64, ctypes.c_int]
         lib.oracle_sig_length.restype = u64
         lib.oracle_sig_length.argtypes = [u64, u64]
         _LIB = lib
@@ -106,3 +109,24 @@ def sig_backprop(path, sig_, sig_derivs, degree, *, time_aug=False, lead_lag=Fal
     if rc:
         raise RuntimeError("oracle_sig_backprop failed with code %d" % rc)
     return out[0] if single else out
+
+
+def sig_combine(sig1, sig2, dim, degree):
+    """Oracle Chen product of two (batches of) signatures of a ``dim``-channel path; the
+    scalar-term layout is inferred from the length."""
+    a = np.ascontiguousarray(sig1)
+    single = a.ndim == 1
+    a2 = a[None] if single else a.reshape(-1, a.shape[-1])
+    b2 = np.ascontiguousarray(sig2, dtype=a.dtype).reshape(a2.shape)
+    suf, real = _suffix(a2)
+    full = sig_length(dim, degree, True)
+    if a2.shape[1] not in (full, full - 1):
+        raise ValueError("signatures have the wrong length")
+    out = np.empty_like(a2)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_sig_combine_" + suf)(a2.ctypes.data_as(ptr), b2.ctypes.data_as(ptr),
+                                                      out.ctypes.data_as(ptr), a2.shape[0], dim, degree,
+                                                      int(a2.shape[1] == full))
+    if rc:
+        raise RuntimeError("oracle_sig_combine failed with code %d" % rc)
+    return out[0] if single else out.reshape(a.shape)

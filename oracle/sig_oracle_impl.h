@@ -527,6 +527,29 @@ int FN(oracle_sig_backprop_)(const REAL* path, REAL* out, const REAL* sig_derivs
     return FN(run_batch_)(&j, batch, n_threads);
 }
 
+/* out = sig1 (x) sig2 per batch entry (cp_sig_combine.h:34-66 on scalar-padded copies) */
+int FN(oracle_sig_combine_)(const REAL* sig1, const REAL* sig2, REAL* out, uint64_t batch, uint64_t dim,
+                            uint64_t degree, int scalar_term) {
+    if (dim == 0) return 2;
+    const uint64_t full = oracle_sig_length(dim, degree);
+    const uint64_t stride = scalar_term ? full : full - 1;
+    uint64_t* li = (uint64_t*)malloc((degree + 2) * sizeof(uint64_t));
+    REAL* a = (REAL*)malloc(2 * full * sizeof(REAL));
+    if (!li || !a) { free(li); free(a); return 1; }
+    REAL* b = a + full;
+    populate_level_index(li, dim, degree + 2);
+    for (uint64_t i = 0; i < batch; ++i) {
+        a[0] = b[0] = (REAL)1;
+        memcpy(a + 1, sig1 + i * stride + (scalar_term ? 1 : 0), (full - 1) * sizeof(REAL));
+        memcpy(b + 1, sig2 + i * stride + (scalar_term ? 1 : 0), (full - 1) * sizeof(REAL));
+        FN(sig_combine_inplace_)(a, b, degree, li);
+        memcpy(out + i * stride, a + (scalar_term ? 0 : 1), stride * sizeof(REAL));
+    }
+    free(li);
+    free(a);
+    return 0;
+}
+
 #undef FN
 #undef CAT
 #undef CAT_

@@ -149,6 +149,16 @@ SIG_API int sig_backprop_cuda_d(const double* path, double* out, const double* s
                                              sync_options()));
 }
 
+SIG_API int sig_combine_cuda_f(const float* sig1, const float* sig2, float* out, uint64_t batch_size,
+                               uint64_t dimension, uint64_t degree, bool scalar_term) {
+    SIG_SAFE_CALL(sig_combine_entry<float>(sig1, sig2, out, batch_size, dimension, degree, scalar_term, sync_options()));
+}
+
+SIG_API int sig_combine_cuda_d(const double* sig1, const double* sig2, double* out, uint64_t batch_size,
+                               uint64_t dimension, uint64_t degree, bool scalar_term) {
+    SIG_SAFE_CALL(sig_combine_entry<double>(sig1, sig2, out, batch_size, dimension, degree, scalar_term, sync_options()));
+}
+
 SIG_API const char* cusig_last_error_message(void) { return last_error(); }
 
 SIG_API void cusig_shutdown(void) { shutdown_runtime(); }
@@ -270,7 +280,7 @@ SIG_STUB_PAIR(log_sig_combine_cuda) SIG_STUB_PAIR(log_sig_combine_backprop_cuda)
 SIG_STUB_PAIR(log_sig_from_path_cuda) SIG_STUB_PAIR(log_sig_from_path_backprop_cuda)
 SIG_STUB_PAIR(log_sig_join_cuda) SIG_STUB_PAIR(log_sig_join_backprop_cuda)
 SIG_STUB_PAIR(logsig_to_sig_cuda) SIG_STUB_PAIR(logsig_to_sig_backprop_cuda)
-SIG_STUB_PAIR(sig_combine_cuda) SIG_STUB_PAIR(sig_combine_backprop_cuda)
+SIG_STUB_PAIR(sig_combine_backprop_cuda)
 SIG_STUB_PAIR(sig_join_cuda) SIG_STUB_PAIR(sig_join_backprop_cuda)
 SIG_STUB_PAIR(sig_coef_cuda) SIG_STUB_PAIR(sig_coef_backprop_cuda)
 SIG_STUB_PAIR(sig_to_log_sig_cuda) SIG_STUB_PAIR(sig_to_log_sig_backprop_cuda)

@@ -278,7 +278,43 @@ void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig
         });
 }
 
+// Chen product of two batches of signatures.  Replaces siglib/cusig/cu_sig_combine.cu
+// (sig_combine_cuda_): same buffers and layout; one thread per output coefficient.
+template <typename T>
+void sig_combine_entry(const T* sig1, const T* sig2, T* out, uint64_t batch, uint64_t dimension, uint64_t degree,
+                       bool scalar_term, const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("sig_combine_cuda received dimension 0");
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, dimension, 2, degree, false, false, scalar_term);
+    if (s.stride == 0) return;
+    if (sig1 == nullptr || sig2 == nullptr || out == nullptr)
+        throw std::invalid_argument("sig_combine_cuda received a null pointer");
+    const uint64_t shift = scalar_term ? 1 : 0;
+    auto run = [&](const T* a, const T* b, T* c, uint64_t count, cudaStream_t stream) {
+        SigShape cs = s;
+        cs.batch = count;
+        if (degree == 0) launch_fill<T>(c, count * s.stride, T(1), stream);  // only the scalar term
+        else launch_chen_product<T>(a + shift, s.stride, b + shift, s.stride, c + shift, s.stride, cs, stream, scalar_term);
+    };
+    const PointerInfo pout = classify_pointer(out);
+    if (pout.on_device) {
+        if (!classify_pointer(sig1).on_device || !classify_pointer(sig2).on_device)
+            throw std::invalid_argument("sig_combine_cuda: all buffers must be device pointers or all host pointers");
+        DeviceGuard guard(pout.device);
+        run(sig1, sig2, out, batch, opt.stream);
+        if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        return;
+    }
+    DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
+    std::vector<HostOperand> ins{{sig1, s.stride * sizeof(T)}, {sig2, s.stride * sizeof(T)}};
+    run_host_pipeline(batch, ins, out, s.stride * sizeof(T),
+        [&](const std::vector<void*>& din, void* dout, uint64_t count, cudaStream_t stream) {
+            run(static_cast<const T*>(din[0]), static_cast<const T*>(din[1]), static_cast<T*>(dout), count, stream);
+        });
+}
+
 #define INSTANTIATE(T)                                                                                    \
+    template void sig_combine_entry<T>(const T*, const T*, T*, uint64_t, uint64_t, uint64_t, bool, const CallOptions&); \
     template void forward_on_device<T>(const T*, T*, const SigShape&, T, cudaStream_t);                   \
     template void backward_on_device<T>(const T*, T*, const T*, const T*, const SigShape&, T, cudaStream_t); \
     template void signature_entry<T>(const T*, T*, uint64_t, uint64_t, uint64_t, uint64_t, bool, bool, T, bool, \

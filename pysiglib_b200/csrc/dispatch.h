@@ -34,4 +34,9 @@ void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig
                         T end_time, bool scalar_term, const T* correction, uint64_t correction_len,
                         const CallOptions& opt);
 
+// out = sig1 (x) sig2 (Chen's identity) for batches of signatures of a `dimension`-channel path.
+template <typename T>
+void sig_combine_entry(const T* sig1, const T* sig2, T* out, uint64_t batch, uint64_t dimension, uint64_t degree,
+                       bool scalar_term, const CallOptions& opt);
+
 }  // namespace sigb200

@@ -70,7 +70,7 @@ void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int ns
 // has its own batch stride (in elements).
 template <typename T>
 void launch_chen_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_stride, T* C, uint64_t c_stride,
-                         const SigShape& s, cudaStream_t stream);
+                         const SigShape& s, cudaStream_t stream, bool write_scalar = false);
 template <typename T>
 void launch_chen_left_adjoint(const T* dS, uint64_t ds_stride, const T* A, uint64_t a_stride, T* dX,
                               uint64_t dx_stride, const SigShape& s, cudaStream_t stream);

@@ -345,7 +345,8 @@ chen_pair_kernel(const T* __restrict__ in, int n, T* __restrict__ out, uint64_t 
 template <typename T>
 __global__ void __launch_bounds__(kGenericThreads)
 chen_product_kernel(const T* __restrict__ A, uint64_t a_stride, const T* __restrict__ B, uint64_t b_stride,
-                    T* __restrict__ C, uint64_t c_stride, uint64_t total, uint32_t slen, int N, LevelIndex lev) {
+                    T* __restrict__ C, uint64_t c_stride, bool c_scalar, uint64_t total, uint32_t slen, int N,
+                    LevelIndex lev) {
     __shared__ uint32_t li[kMaxDegree + 2];
     for (unsigned i = threadIdx.x; i < unsigned(N + 2); i += blockDim.x) li[i] = lev.li[i];
     __syncthreads();
@@ -365,6 +366,7 @@ chen_product_kernel(const T* __restrict__ A, uint64_t a_stride, const T* __restr
         acc = fma_t(a[li[i] + left], bb[li[m - i] + (idx - left * pw)], acc);
     }
     (C + b * c_stride - 1)[pos] = acc + bb[pos];
+    if (c_scalar && pos == 1) (C + b * c_stride - 1)[0] = T(1);  // the slot before level 1 is the scalar term
 }
 
 // Adjoint of the left factor of a Chen product: for S = X (x) A and a loss adjoint dS,
@@ -568,13 +570,13 @@ void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int ns
 
 template <typename T>
 void launch_chen_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_stride, T* C, uint64_t c_stride,
-                         const SigShape& s, cudaStream_t stream) {
+                         const SigShape& s, cudaStream_t stream, bool write_scalar) {
     check_generic_limits(s);
     const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
     const uint64_t total = checked_mul(s.batch, slen, "signature output");
     if (total == 0) return;
     chen_product_kernel<T><<<grid_1d(total, kGenericThreads), kGenericThreads, 0, stream>>>(
-        A, a_stride, B, b_stride, C, c_stride, total, slen, static_cast<int>(s.degree),
+        A, a_stride, B, b_stride, C, c_stride, write_scalar, total, slen, static_cast<int>(s.degree),
         make_level_index(s.dim, s.degree));
     SIG_CUDA_CHECK(cudaGetLastError());
     count_launch();
@@ -630,7 +632,7 @@ void launch_nonfinite_scan(const T* data, uint64_t n, int* flag, cudaStream_t st
                                              unsigned, cudaStream_t);                                    \
     template void launch_increment_to_point_grad<T>(const T*, T*, uint64_t, uint64_t, uint64_t, cudaStream_t); \
     template void launch_chen_combine<T>(T*, const T*, T*, const SigShape&, int, cudaStream_t);                   \
-    template void launch_chen_product<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t); \
+    template void launch_chen_product<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t, bool); \
     template void launch_chen_left_adjoint<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t); \
     template void launch_degree_one_backward<T>(const T*, T*, const T*, const SigShape&, T, cudaStream_t); \
     template void launch_fill<T>(T*, uint64_t, T, cudaStream_t);                                         \

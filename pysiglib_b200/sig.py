@@ -10,10 +10,10 @@ import numpy as np
 import torch
 
 from . import load_cusig
-from .data_handlers import Output, PathInput, check_correction_unsupported
+from .data_handlers import Output, PathInput, SigInput, check_correction_unsupported, check_same
 from .error_codes import err_msg
 from .param_checks import check_n_jobs, check_non_neg, check_type
-from .sig_length import sig_length
+from .sig_length import infer_scalar_term, sig_length
 
 NONFINITE_WARNING = ("sig produced NaN or Inf values. This is typically caused by paths with large "
                      "increments, leading to numerical overflow. Consider normalizing your paths.")
@@ -94,3 +94,67 @@ def sig(
 
 
 signature = sig
+
+
+def sig_combine(
+        sig1: Union[np.ndarray, torch.Tensor],
+        sig2: Union[np.ndarray, torch.Tensor],
+        dimension: int,
+        degree: int,
+        *,
+        time_aug: bool = False,
+        lead_lag: bool = False,
+        n_jobs: int = 1
+) -> Union[np.ndarray, torch.Tensor]:
+    """Signature of a concatenated path from the signatures of its two parts (Chen's identity).
+
+    If ``sig1 = sig(x1)`` and ``sig2 = sig(x2)`` where ``x2`` starts where ``x1`` ends, the
+    result is ``sig(x1 * x2) = sig1 (x) sig2`` truncated at ``degree``.  Same parameters as the
+    reference's ``pysiglib.sig_combine`` (``pysiglib/sig.py:28-126``).
+
+    :param sig1, sig2: arrays ``(..., S)`` of the same kind, dtype, device and batch shape, both
+        with or both without the scalar term (the result uses the same layout).
+    :param dimension: dimension of the underlying path (before ``time_aug`` / ``lead_lag``).
+    :param degree: truncation level of both signatures.
+    :param time_aug, lead_lag: the flags the signatures were computed with (they only change the
+        effective dimension).
+    :param n_jobs: accepted for compatibility.
+    """
+    check_type(dimension, "dimension", int)
+    check_type(degree, "degree", int)
+    check_non_neg(dimension, "dimension")
+    check_non_neg(degree, "degree")
+    check_type(time_aug, "time_aug", bool)
+    check_type(lead_lag, "lead_lag", bool)
+    check_n_jobs(n_jobs)
+    from .data_handlers import _describe, _pointer
+    from .param_checks import check_dtype, own_contiguous
+    from .sig_length import aug_dim
+
+    class _Sig:  # a signature-shaped input kept in the caller's layout (scalar term not stripped)
+        def __init__(self, arr, name):
+            check_type(arr, name, (np.ndarray, torch.Tensor))
+            self.array = own_contiguous(arr)
+            check_dtype(self.array, name)
+            if self.array.ndim < 1:
+                raise ValueError("%s must have at least rank 1, got rank 0." % name)
+            self.batch_shape = tuple(self.array.shape[:-1])
+            self.kind, self.dtype, self.device = _describe(self.array)
+            self.pointer = _pointer(self.array, self.dtype)
+
+    a, b = _Sig(sig1, "sig1"), _Sig(sig2, "sig2")
+    scalar_term = infer_scalar_term(a.array, dimension, degree, time_aug=time_aug, lead_lag=lead_lag)
+    if b.array.shape[-1] != a.array.shape[-1]:
+        raise ValueError("sig2 is of incorrect length. Expected %d, got %d" % (a.array.shape[-1], b.array.shape[-1]))
+    check_same([a, b], ["sig1", "sig2"])
+    result = Output(a, (a.array.shape[-1],))
+    batch = 1
+    for extent in a.batch_shape:
+        batch *= extent
+    if batch == 0 or a.array.shape[-1] == 0:
+        return result.array
+    code = load_cusig.fn("sig_combine_cuda", a.dtype)(
+        a.pointer, b.pointer, result.pointer, batch, aug_dim(dimension, time_aug, lead_lag), degree, scalar_term)
+    if code:
+        raise Exception("Error in pysiglib.sig_combine: " + err_msg(code))
+    return result.array

@@ -238,7 +238,7 @@ def test_error_codes_and_messages():
     assert lib.signature_cuda_d(dptr, optr, 1, 2, 4, 2, False, False, 1.0, True, False, optr, 4, 0, 0) == 2
     assert lib.sig_backprop_cuda_d(dptr, optr, optr, optr, 1, 0, 4, 2, False, False, 1.0, False, None, 0, 0, 0) == 2
     # symbols outside the served path exist and fail cleanly
-    assert lib.sig_combine_cuda_d() == 10
+    assert lib.sig_join_cuda_d() == 10
     assert "not part of this build" in load_cusig.last_error_message()
 
 
@@ -398,3 +398,25 @@ def test_sharded_single_device_matches_plain():
     g = pysiglib_b200.sig_backprop_sharded(path, a, np.ones_like(a), 3, devices=[0])
     np.testing.assert_allclose(g, oracle.sig_backprop(path, oracle.sig(path, 3), np.ones_like(a), 3), rtol=1e-4,
                                atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float64, 1e-10), (np.float32, 1e-5)])
+def test_sig_combine_matches_oracle_and_chen_identity(dtype, tol):
+    import pysiglib_b200
+    for (B, L, d, N) in ((5, 31, 3, 4), (3, 40, 8, 4), (2, 25, 2, 9), (4, 12, 1, 5)):
+        p = brownian_paths(B + d, B, L, d, dtype) * 2.0
+        m = L // 2
+        for scalar_term in (False, True):
+            a = pysiglib_b200.sig(p[:, :m + 1].copy(), N, scalar_term=scalar_term)
+            b = pysiglib_b200.sig(p[:, m:].copy(), N, scalar_term=scalar_term)
+            ab = pysiglib_b200.sig(p, N, scalar_term=scalar_term)
+            got = pysiglib_b200.sig_combine(a, b, d, N)
+            assert got.shape == ab.shape
+            assert_sig_close(got, oracle.sig_combine(a, b, d, N), d, N, tol, scalar_term)
+            assert_sig_close(got, ab, d, N, 20 * tol, scalar_term)
+        ta, tb = torch.tensor(a, device="cuda"), torch.tensor(b, device="cuda")
+        tg = pysiglib_b200.sig_combine(ta, tb, d, N)
+        assert tg.is_cuda
+        np.testing.assert_array_equal(tg.cpu().numpy(), got)
+    with pytest.raises(ValueError):
+        pysiglib_b200.sig_combine(np.zeros((2, 14)), np.zeros((2, 13)), 2, 3)

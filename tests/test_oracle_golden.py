@@ -229,3 +229,16 @@ def test_scalar_term_consistency_and_threads():  # reference tests/test_scalar_t
     b = oracle.sig(p, 4, scalar_term=False)
     assert np.all(a[:, 0] == 1.0)
     np.testing.assert_array_equal(a[:, 1:], b)
+
+
+def test_sig_combine_is_chen_identity():  # reference tests: sig(x1 * x2) == sig_combine(sig(x1), sig(x2))
+    p = brownian_paths(9, 4, 21, 3)
+    for scalar_term in (False, True):
+        a = oracle.sig(p[:, :11], 4, scalar_term=scalar_term)
+        b = oracle.sig(p[:, 10:], 4, scalar_term=scalar_term)
+        ab = oracle.sig(p, 4, scalar_term=scalar_term)
+        np.testing.assert_allclose(oracle.sig_combine(a, b, 3, 4), ab, rtol=1e-12, atol=1e-15)
+    # hand-computed: level 2 of the product is a2 + b2 + a1 (x) b1
+    s1 = np.array([1., 1., 1., .5, .5, .5, .5])
+    s2 = np.array([1., 0., 1., 0., 1., -1., .5])
+    np.testing.assert_allclose(oracle.sig_combine(s1, s2, 2, 2), [1., 1., 2., .5, 2.5, -.5, 2.], atol=1e-15)
