@@ -191,6 +191,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-refcuda", action="store_true", help="skip timing the reference's own CUDA kernels")
+    ap.add_argument("--gather", action="store_true",
+                    help="with N > 1 also time one NCCL all-gather of the signatures onto every rank (not part of value)")
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (profiling on a small case)")
     ap.add_argument("--length", type=int, default=None, help="override the path length (profiling on a small case)")
     args = ap.parse_args()
@@ -311,6 +313,24 @@ def main():
     total_ms_max = float(t.item())
     value = cfg["B"] * args.steps / (total_ms_max * 1e-3)
 
+    # ---- optional: the one collective the path can have, a gather of the per-rank results ----
+    gather_ms = None
+    if args.gather and world > 1 and cfg["B"] % world == 0:
+        full = torch.empty((cfg["B"], S), dtype=sig.dtype, device=dev)
+        dist.all_gather_into_tensor(full, sig)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(3):
+            dist.all_gather_into_tensor(full, sig)
+        g1.record(stream)
+        g1.synchronize()
+        gt = torch.tensor([g0.elapsed_time(g1) / 3], dtype=torch.float64, device=dev)
+        dist.all_reduce(gt, op=dist.ReduceOp.MAX)
+        gather_ms = float(gt.item())
+        assert torch.equal(full[rank * b_local:(rank + 1) * b_local], sig)
+        del full
+
     # ---- end to end through the reference-named C-ABI symbols with pinned host buffers ----
     e2e = None
     if not args.no_e2e:
@@ -426,6 +446,9 @@ def main():
         out["e2e"] = e2e
     if ref_cuda is not None:
         out["reference_cuda"] = ref_cuda
+    if gather_ms is not None:
+        out["all_gather"] = {"ms": gather_ms, "bytes_per_rank": b_local * S * esize,
+                             "what": "NCCL all_gather_into_tensor of the signatures onto every rank, max over ranks"}
     if not args.no_cpu and world == 1:
         cores = os.cpu_count() or 1
         v, n, dt = cpu_baseline(cfg, cores)
