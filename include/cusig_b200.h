@@ -66,6 +66,17 @@ int sig_combine_cuda_f(const float* sig1, const float* sig2, float* out, uint64_
 int sig_combine_cuda_d(const double* sig1, const double* sig2, double* out, uint64_t batch_size,
                        uint64_t dimension, uint64_t degree, bool scalar_term);
 
+/* Backward of sig_combine: given dLoss/d(sig1 (x) sig2), writes dLoss/d sig1 and dLoss/d sig2
+ * (same layout; the scalar slots get 0).
+ * Replaces: siglib/cusig/cusig.h:386-388 (siglib/cusig/cu_sig_combine.cu); bound by
+ *           pysiglib/load_siglib.py:466-470.  Synchronous; device or host pointers. */
+int sig_combine_backprop_cuda_f(const float* sig_combined_deriv, float* sig1_deriv, float* sig2_deriv,
+                                const float* sig1, const float* sig2, uint64_t batch_size, uint64_t dimension,
+                                uint64_t degree, bool scalar_term);
+int sig_combine_backprop_cuda_d(const double* sig_combined_deriv, double* sig1_deriv, double* sig2_deriv,
+                                const double* sig1, const double* sig2, uint64_t batch_size, uint64_t dimension,
+                                uint64_t degree, bool scalar_term);
+
 /* Thread-local text of the last error; valid until the next call on this thread.
  * Replaces: siglib/cusig/cusig.h:43; bound by pysiglib/load_siglib.py:108-110. */
 const char* cusig_last_error_message(void);

@@ -44,6 +44,9 @@ def _lib():
             cmb = getattr(lib, "oracle_sig_combine_" + suf)
             cmb.restype = ctypes.c_int
             cmb.argtypes = [ptr, ptr, ptr, u64, u64, u64, ctypes.c_int]
+            cbp = getattr(lib, "oracle_sig_combine_backprop_" + suf)
+            cbp.restype = ctypes.c_int
+            cbp.argtypes = [ptr, ptr, ptr, ptr, ptr, u64, u64, u64, ctypes.c_int]
         lib.oracle_sig_length.restype = u64
         lib.oracle_sig_length.argtypes = [u64, u64]
         _LIB = lib
@@ -130,3 +133,23 @@ def sig_combine(sig1, sig2, dim, degree):
     if rc:
         raise RuntimeError("oracle_sig_combine failed with code %d" % rc)
     return out[0] if single else out.reshape(a.shape)
+
+
+def sig_combine_backprop(deriv, sig1, sig2, dim, degree):
+    """Oracle adjoints (d sig1, d sig2) of sig_combine; scalar-term layout inferred from the length."""
+    a = np.ascontiguousarray(sig1)
+    a2 = a.reshape(-1, a.shape[-1])
+    b2 = np.ascontiguousarray(sig2, dtype=a.dtype).reshape(a2.shape)
+    d2 = np.ascontiguousarray(deriv, dtype=a.dtype).reshape(a2.shape)
+    suf, real = _suffix(a2)
+    full = sig_length(dim, degree, True)
+    if a2.shape[1] not in (full, full - 1):
+        raise ValueError("signatures have the wrong length")
+    o1, o2 = np.empty_like(a2), np.empty_like(a2)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_sig_combine_backprop_" + suf)(
+        d2.ctypes.data_as(ptr), o1.ctypes.data_as(ptr), o2.ctypes.data_as(ptr), a2.ctypes.data_as(ptr),
+        b2.ctypes.data_as(ptr), a2.shape[0], dim, degree, int(a2.shape[1] == full))
+    if rc:
+        raise RuntimeError("oracle_sig_combine_backprop failed with code %d" % rc)
+    return o1.reshape(a.shape), o2.reshape(a.shape)

@@ -550,6 +550,48 @@ int FN(oracle_sig_combine_)(const REAL* sig1, const REAL* sig2, REAL* out, uint6
     return 0;
 }
 
+/* Adjoints of both factors of a (x) b: d1[u] = sum_v deriv[uv] b[v], d2[v] = sum_u deriv[uv] a[u]
+ * (what siglib/cpsig/cp_sig_combine.h sig_combine_backprop_ computes; scalar slots get 0).
+ * Written from the definition, level pair by level pair. */
+int FN(oracle_sig_combine_backprop_)(const REAL* deriv, REAL* d1, REAL* d2, const REAL* sig1, const REAL* sig2,
+                                     uint64_t batch, uint64_t dim, uint64_t degree, int scalar_term) {
+    if (dim == 0) return 2;
+    const uint64_t full = oracle_sig_length(dim, degree);
+    const uint64_t stride = scalar_term ? full : full - 1;
+    uint64_t* li = (uint64_t*)malloc((degree + 2) * sizeof(uint64_t));
+    REAL* buf = (REAL*)malloc(5 * full * sizeof(REAL));
+    if (!li || !buf) { free(li); free(buf); return 1; }
+    populate_level_index(li, dim, degree + 2);
+    REAL *ds = buf, *a = buf + full, *b = buf + 2 * full, *o1 = buf + 3 * full, *o2 = buf + 4 * full;
+    const uint64_t off = scalar_term ? 1 : 0;
+    for (uint64_t i = 0; i < batch; ++i) {
+        ds[0] = (REAL)0; a[0] = b[0] = (REAL)1;
+        memcpy(ds + 1, deriv + i * stride + off, (full - 1) * sizeof(REAL));
+        memcpy(a + 1, sig1 + i * stride + off, (full - 1) * sizeof(REAL));
+        memcpy(b + 1, sig2 + i * stride + off, (full - 1) * sizeof(REAL));
+        for (uint64_t k = 0; k < full; ++k) o1[k] = o2[k] = (REAL)0;
+        for (uint64_t n = 0; n <= degree; ++n) {            /* level of the left word u */
+            const uint64_t cn = li[n + 1] - li[n];
+            for (uint64_t m = 0; n + m <= degree; ++m) {    /* level of the right word v */
+                if (n + m == 0) continue;
+                const uint64_t cm = li[m + 1] - li[m];
+                for (uint64_t u = 0; u < cn; ++u)
+                    for (uint64_t v = 0; v < cm; ++v) {
+                        const REAL g = ds[li[n + m] + u * cm + v];
+                        o1[li[n] + u] = FMA(g, b[li[m] + v], o1[li[n] + u]);
+                        o2[li[m] + v] = FMA(g, a[li[n] + u], o2[li[m] + v]);
+                    }
+            }
+        }
+        o1[0] = o2[0] = (REAL)0;
+        memcpy(d1 + i * stride, o1 + (scalar_term ? 0 : 1), stride * sizeof(REAL));
+        memcpy(d2 + i * stride, o2 + (scalar_term ? 0 : 1), stride * sizeof(REAL));
+    }
+    free(li);
+    free(buf);
+    return 0;
+}
+
 #undef FN
 #undef CAT
 #undef CAT_

@@ -3,11 +3,11 @@
 Drop-in for that path only: the functions below keep the reference's names, parameters
 and result layout, and the shared library keeps the reference's C entry points.  All
 computation runs in hand-written CUDA kernels; there is no CPU implementation."""
-from .sig import sig, sig_combine, signature
+from .sig import sig, sig_combine, sig_combine_backprop, signature
 from .sig_backprop import sig_backprop
 from .sig_length import sig_length
 from .sharded import sig_backprop_sharded, sig_sharded
 from . import torch_api
 
 __version__ = "0.1.0"
-__all__ = ["sig", "signature", "sig_combine", "sig_backprop", "sig_length", "sig_sharded", "sig_backprop_sharded", "torch_api"]
+__all__ = ["sig", "signature", "sig_combine", "sig_combine_backprop", "sig_backprop", "sig_length", "sig_sharded", "sig_backprop_sharded", "torch_api"]

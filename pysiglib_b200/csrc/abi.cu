@@ -159,6 +159,20 @@ SIG_API int sig_combine_cuda_d(const double* sig1, const double* sig2, double* o
     SIG_SAFE_CALL(sig_combine_entry<double>(sig1, sig2, out, batch_size, dimension, degree, scalar_term, sync_options()));
 }
 
+SIG_API int sig_combine_backprop_cuda_f(const float* sig_combined_deriv, float* sig1_deriv, float* sig2_deriv,
+                                        const float* sig1, const float* sig2, uint64_t batch_size,
+                                        uint64_t dimension, uint64_t degree, bool scalar_term) {
+    SIG_SAFE_CALL(sig_combine_backprop_entry<float>(sig_combined_deriv, sig1_deriv, sig2_deriv, sig1, sig2, batch_size,
+                                                    dimension, degree, scalar_term, sync_options()));
+}
+
+SIG_API int sig_combine_backprop_cuda_d(const double* sig_combined_deriv, double* sig1_deriv, double* sig2_deriv,
+                                        const double* sig1, const double* sig2, uint64_t batch_size,
+                                        uint64_t dimension, uint64_t degree, bool scalar_term) {
+    SIG_SAFE_CALL(sig_combine_backprop_entry<double>(sig_combined_deriv, sig1_deriv, sig2_deriv, sig1, sig2, batch_size,
+                                                     dimension, degree, scalar_term, sync_options()));
+}
+
 SIG_API const char* cusig_last_error_message(void) { return last_error(); }
 
 SIG_API void cusig_shutdown(void) { shutdown_runtime(); }
@@ -280,7 +294,6 @@ SIG_STUB_PAIR(log_sig_combine_cuda) SIG_STUB_PAIR(log_sig_combine_backprop_cuda)
 SIG_STUB_PAIR(log_sig_from_path_cuda) SIG_STUB_PAIR(log_sig_from_path_backprop_cuda)
 SIG_STUB_PAIR(log_sig_join_cuda) SIG_STUB_PAIR(log_sig_join_backprop_cuda)
 SIG_STUB_PAIR(logsig_to_sig_cuda) SIG_STUB_PAIR(logsig_to_sig_backprop_cuda)
-SIG_STUB_PAIR(sig_combine_backprop_cuda)
 SIG_STUB_PAIR(sig_join_cuda) SIG_STUB_PAIR(sig_join_backprop_cuda)
 SIG_STUB_PAIR(sig_coef_cuda) SIG_STUB_PAIR(sig_coef_backprop_cuda)
 SIG_STUB_PAIR(sig_to_log_sig_cuda) SIG_STUB_PAIR(sig_to_log_sig_backprop_cuda)

@@ -313,7 +313,58 @@ void sig_combine_entry(const T* sig1, const T* sig2, T* out, uint64_t batch, uin
         });
 }
 
+// Backward of the Chen product.  Replaces siglib/cusig/cu_sig_combine.cu (sig_combine_backprop_cuda_):
+// d sig1[u] = sum_v deriv[u v] sig2[v],  d sig2[v] = sum_u deriv[u v] sig1[u]; scalar slots get 0.
+template <typename T>
+void sig_combine_backprop_entry(const T* deriv, T* sig1_deriv, T* sig2_deriv, const T* sig1, const T* sig2,
+                                uint64_t batch, uint64_t dimension, uint64_t degree, bool scalar_term,
+                                const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("sig_combine_backprop_cuda received dimension 0");
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, dimension, 2, degree, false, false, scalar_term);
+    if (s.stride == 0) return;
+    if (!deriv || !sig1_deriv || !sig2_deriv || !sig1 || !sig2)
+        throw std::invalid_argument("sig_combine_backprop_cuda received a null pointer");
+    const uint64_t shift = scalar_term ? 1 : 0;
+    const uint64_t n = batch * s.stride;
+    auto run = [&](const T* dS, T* d1, T* d2, const T* a, const T* b, cudaStream_t stream) {
+        if (scalar_term) {  // also clears the scalar slots; the kernels overwrite everything else
+            SIG_CUDA_CHECK(cudaMemsetAsync(d1, 0, n * sizeof(T), stream));
+            SIG_CUDA_CHECK(cudaMemsetAsync(d2, 0, n * sizeof(T), stream));
+        }
+        if (degree == 0) return;
+        launch_chen_left_adjoint<T>(dS + shift, s.stride, b + shift, s.stride, d1 + shift, s.stride, s, stream);
+        launch_chen_right_adjoint<T>(dS + shift, s.stride, a + shift, s.stride, d2 + shift, s.stride, s, stream);
+    };
+    const PointerInfo pout = classify_pointer(sig1_deriv);
+    if (pout.on_device) {
+        if (!classify_pointer(deriv).on_device || !classify_pointer(sig2_deriv).on_device ||
+            !classify_pointer(sig1).on_device || !classify_pointer(sig2).on_device)
+            throw std::invalid_argument("sig_combine_backprop_cuda: all buffers must be device pointers or all host pointers");
+        DeviceGuard guard(pout.device);
+        run(deriv, sig1_deriv, sig2_deriv, sig1, sig2, opt.stream);
+        if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        return;
+    }
+    // host buffers: these arrays are small next to a path batch, so one staged round trip
+    DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
+    DeviceContext& ctx = device_context(current_device());
+    std::lock_guard<std::mutex> lock(ctx.mu);
+    cudaStream_t st = ctx.compute;
+    Scratch buf(5 * n * sizeof(T), st);
+    T* d = buf.as<T>();
+    SIG_CUDA_CHECK(cudaMemcpyAsync(d, deriv, n * sizeof(T), cudaMemcpyHostToDevice, st));
+    SIG_CUDA_CHECK(cudaMemcpyAsync(d + n, sig1, n * sizeof(T), cudaMemcpyHostToDevice, st));
+    SIG_CUDA_CHECK(cudaMemcpyAsync(d + 2 * n, sig2, n * sizeof(T), cudaMemcpyHostToDevice, st));
+    run(d, d + 3 * n, d + 4 * n, d + n, d + 2 * n, st);
+    SIG_CUDA_CHECK(cudaMemcpyAsync(sig1_deriv, d + 3 * n, n * sizeof(T), cudaMemcpyDeviceToHost, st));
+    SIG_CUDA_CHECK(cudaMemcpyAsync(sig2_deriv, d + 4 * n, n * sizeof(T), cudaMemcpyDeviceToHost, st));
+    SIG_CUDA_CHECK(cudaStreamSynchronize(st));
+}
+
 #define INSTANTIATE(T)                                                                                    \
+    template void sig_combine_backprop_entry<T>(const T*, T*, T*, const T*, const T*, uint64_t, uint64_t, uint64_t, \
+                                                bool, const CallOptions&);                                \
     template void sig_combine_entry<T>(const T*, const T*, T*, uint64_t, uint64_t, uint64_t, bool, const CallOptions&); \
     template void forward_on_device<T>(const T*, T*, const SigShape&, T, cudaStream_t);                   \
     template void backward_on_device<T>(const T*, T*, const T*, const T*, const SigShape&, T, cudaStream_t); \

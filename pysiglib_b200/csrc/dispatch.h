@@ -39,4 +39,10 @@ template <typename T>
 void sig_combine_entry(const T* sig1, const T* sig2, T* out, uint64_t batch, uint64_t dimension, uint64_t degree,
                        bool scalar_term, const CallOptions& opt);
 
+// Adjoints of both factors of out = sig1 (x) sig2 given dLoss/d out.
+template <typename T>
+void sig_combine_backprop_entry(const T* deriv, T* sig1_deriv, T* sig2_deriv, const T* sig1, const T* sig2,
+                                uint64_t batch, uint64_t dimension, uint64_t degree, bool scalar_term,
+                                const CallOptions& opt);
+
 }  // namespace sigb200

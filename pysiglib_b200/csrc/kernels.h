@@ -74,6 +74,10 @@ void launch_chen_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_s
 template <typename T>
 void launch_chen_left_adjoint(const T* dS, uint64_t ds_stride, const T* A, uint64_t a_stride, T* dX,
                               uint64_t dx_stride, const SigShape& s, cudaStream_t stream);
+// dY[v] = sum_u dS[u v] A[u]: adjoint of the right factor of A (x) Y
+template <typename T>
+void launch_chen_right_adjoint(const T* dS, uint64_t ds_stride, const T* A, uint64_t a_stride, T* dY,
+                               uint64_t dy_stride, const SigShape& s, cudaStream_t stream);
 
 // out[t] = g[t-1] - g[t] over the raw path (g = increment gradients, (batch, L-1, d))
 template <typename T>

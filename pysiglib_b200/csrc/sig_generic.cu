@@ -399,6 +399,37 @@ chen_left_adjoint_kernel(const T* __restrict__ dS, uint64_t ds_stride, const T* 
     (dX + b * dx_stride - 1)[pos] = acc;
 }
 
+// Adjoint of the right factor of a Chen product: for S = A (x) Y and a loss adjoint dS,
+//   dY[v] = dS[v] + sum_{n >= 1, n + |v| <= N} sum_{|u| = n} dS[u v] * A[u].
+// One thread per coefficient of dY.
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads)
+chen_right_adjoint_kernel(const T* __restrict__ dS, uint64_t ds_stride, const T* __restrict__ A, uint64_t a_stride,
+                          T* __restrict__ dY, uint64_t dy_stride, uint64_t total, uint32_t slen, int N,
+                          LevelIndex lev) {
+    __shared__ uint32_t li[kMaxDegree + 2];
+    for (unsigned i = threadIdx.x; i < unsigned(N + 2); i += blockDim.x) li[i] = lev.li[i];
+    __syncthreads();
+    const uint64_t gid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= total) return;
+    const uint64_t b = gid / slen;
+    const uint32_t pos = uint32_t(gid - b * slen) + 1;
+    const T* ds = dS + b * ds_stride - 1;
+    const T* a = A + b * a_stride - 1;
+    int m = 1;
+    while (m < N && pos >= li[m + 1]) ++m;
+    const uint32_t idx = pos - li[m];
+    const uint32_t pw = li[m + 1] - li[m];  // d^m
+    T acc = ds[pos];
+    for (int n = 1; n + m <= N; ++n) {
+        const uint32_t count = li[n + 1] - li[n];  // d^n
+        const T* col = ds + li[n + m] + idx;
+        const T* av = a + li[n];
+        for (uint32_t u = 0; u < count; ++u) acc = fma_t(col[uint64_t(u) * pw], av[u], acc);
+    }
+    (dY + b * dy_stride - 1)[pos] = acc;
+}
+
 template <typename T>
 __global__ void increment_to_point_grad_kernel(const T* __restrict__ g, T* __restrict__ out, uint64_t total,
                                                uint32_t L, uint32_t d) {
@@ -597,6 +628,20 @@ void launch_chen_left_adjoint(const T* dS, uint64_t ds_stride, const T* A, uint6
 }
 
 template <typename T>
+void launch_chen_right_adjoint(const T* dS, uint64_t ds_stride, const T* A, uint64_t a_stride, T* dY,
+                               uint64_t dy_stride, const SigShape& s, cudaStream_t stream) {
+    check_generic_limits(s);
+    const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
+    const uint64_t total = checked_mul(s.batch, slen, "signature output");
+    if (total == 0) return;
+    chen_right_adjoint_kernel<T><<<grid_1d(total, kGenericThreads), kGenericThreads, 0, stream>>>(
+        dS, ds_stride, A, a_stride, dY, dy_stride, total, slen, static_cast<int>(s.degree),
+        make_level_index(s.dim, s.degree));
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+template <typename T>
 void launch_increment_to_point_grad(const T* incr_grad, T* out, uint64_t batch, uint64_t L, uint64_t d,
                                     cudaStream_t stream) {
     const uint64_t total = checked_mul(batch, checked_mul(L, d, "path gradient"), "path gradient");
@@ -635,6 +680,7 @@ void launch_nonfinite_scan(const T* data, uint64_t n, int* flag, cudaStream_t st
     template void launch_chen_product<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t, bool); \
     template void launch_chen_left_adjoint<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t); \
     template void launch_degree_one_backward<T>(const T*, T*, const T*, const SigShape&, T, cudaStream_t); \
+    template void launch_chen_right_adjoint<T>(const T*, uint64_t, const T*, uint64_t, T*, uint64_t, const SigShape&, cudaStream_t); \
     template void launch_fill<T>(T*, uint64_t, T, cudaStream_t);                                         \
     template void launch_nonfinite_scan<T>(const T*, uint64_t, int*, cudaStream_t);
 INSTANTIATE(float)

@@ -69,6 +69,9 @@ def _bind(lib):
         f = getattr(lib, "sig_combine_cuda_" + suffix)
         f.argtypes = (ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_bool)
         f.restype = c_int
+        f = getattr(lib, "sig_combine_backprop_cuda_" + suffix)
+        f.argtypes = (ptr, ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_bool)
+        f.restype = c_int
         f = getattr(lib, "sig_backprop_cuda_" + suffix)
         f.argtypes = (ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real, c_bool,
                       ptr, c_uint64, c_uint64, c_uint64)

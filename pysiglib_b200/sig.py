@@ -96,6 +96,29 @@ def sig(
 signature = sig
 
 
+class _Sig:
+    """A signature-shaped input kept in the caller's layout (a scalar term is not stripped)."""
+
+    def __init__(self, arr, name):
+        from .data_handlers import _describe, _pointer
+        from .param_checks import check_dtype, own_contiguous
+        check_type(arr, name, (np.ndarray, torch.Tensor))
+        self.array = own_contiguous(arr)
+        check_dtype(self.array, name)
+        if self.array.ndim < 1:
+            raise ValueError("%s must have at least rank 1, got rank 0." % name)
+        self.batch_shape = tuple(self.array.shape[:-1])
+        self.kind, self.dtype, self.device = _describe(self.array)
+        self.pointer = _pointer(self.array, self.dtype)
+
+    @property
+    def batch_size(self):
+        n = 1
+        for extent in self.batch_shape:
+            n *= extent
+        return n
+
+
 def sig_combine(
         sig1: Union[np.ndarray, torch.Tensor],
         sig2: Union[np.ndarray, torch.Tensor],
@@ -127,34 +150,61 @@ def sig_combine(
     check_type(time_aug, "time_aug", bool)
     check_type(lead_lag, "lead_lag", bool)
     check_n_jobs(n_jobs)
-    from .data_handlers import _describe, _pointer
-    from .param_checks import check_dtype, own_contiguous
-    from .sig_length import aug_dim
-
-    class _Sig:  # a signature-shaped input kept in the caller's layout (scalar term not stripped)
-        def __init__(self, arr, name):
-            check_type(arr, name, (np.ndarray, torch.Tensor))
-            self.array = own_contiguous(arr)
-            check_dtype(self.array, name)
-            if self.array.ndim < 1:
-                raise ValueError("%s must have at least rank 1, got rank 0." % name)
-            self.batch_shape = tuple(self.array.shape[:-1])
-            self.kind, self.dtype, self.device = _describe(self.array)
-            self.pointer = _pointer(self.array, self.dtype)
-
     a, b = _Sig(sig1, "sig1"), _Sig(sig2, "sig2")
     scalar_term = infer_scalar_term(a.array, dimension, degree, time_aug=time_aug, lead_lag=lead_lag)
     if b.array.shape[-1] != a.array.shape[-1]:
         raise ValueError("sig2 is of incorrect length. Expected %d, got %d" % (a.array.shape[-1], b.array.shape[-1]))
     check_same([a, b], ["sig1", "sig2"])
     result = Output(a, (a.array.shape[-1],))
-    batch = 1
-    for extent in a.batch_shape:
-        batch *= extent
+    batch = a.batch_size
     if batch == 0 or a.array.shape[-1] == 0:
         return result.array
+    from .sig_length import aug_dim
     code = load_cusig.fn("sig_combine_cuda", a.dtype)(
         a.pointer, b.pointer, result.pointer, batch, aug_dim(dimension, time_aug, lead_lag), degree, scalar_term)
     if code:
         raise Exception("Error in pysiglib.sig_combine: " + err_msg(code))
     return result.array
+
+
+def sig_combine_backprop(
+        deriv: Union[np.ndarray, torch.Tensor],
+        sig1: Union[np.ndarray, torch.Tensor],
+        sig2: Union[np.ndarray, torch.Tensor],
+        dimension: int,
+        degree: int,
+        *,
+        time_aug: bool = False,
+        lead_lag: bool = False,
+        n_jobs: int = 1
+):
+    """Backward pass of ``sig_combine``: from ``dF/d sig_combine(sig1, sig2)`` to
+    ``(dF/d sig1, dF/d sig2)``.  Same parameters as the reference's
+    ``pysiglib.sig_combine_backprop`` (``pysiglib/sig_backprop.py:27-126``); all three inputs
+    share one layout (with or without the scalar term) and the results use it too, with zeros
+    in the scalar slots.
+    """
+    check_type(dimension, "dimension", int)
+    check_type(degree, "degree", int)
+    check_non_neg(dimension, "dimension")
+    check_non_neg(degree, "degree")
+    check_type(time_aug, "time_aug", bool)
+    check_type(lead_lag, "lead_lag", bool)
+    check_n_jobs(n_jobs)
+    d, a, b = _Sig(deriv, "deriv"), _Sig(sig1, "sig1"), _Sig(sig2, "sig2")
+    scalar_term = infer_scalar_term(a.array, dimension, degree, time_aug=time_aug, lead_lag=lead_lag)
+    for other, name in ((b, "sig2"), (d, "deriv")):
+        if other.array.shape[-1] != a.array.shape[-1]:
+            raise ValueError("%s is of incorrect length. Expected %d, got %d"
+                             % (name, a.array.shape[-1], other.array.shape[-1]))
+    check_same([d, a, b], ["deriv", "sig1", "sig2"])
+    out1, out2 = Output(a, (a.array.shape[-1],)), Output(a, (a.array.shape[-1],))
+    if a.batch_size == 0 or a.array.shape[-1] == 0:
+        return out1.array, out2.array
+    from .sig_length import aug_dim
+    code = load_cusig.fn("sig_combine_backprop_cuda", a.dtype)(
+        d.pointer, out1.pointer, out2.pointer, a.pointer, b.pointer, a.batch_size,
+        aug_dim(dimension, time_aug, lead_lag), degree, scalar_term)
+    if code:
+        raise Exception("Error in pysiglib.sig_combine_backprop: " + err_msg(code))
+    return out1.array, out2.array

@@ -3,8 +3,8 @@
 Source: the reference's ``tests/fixtures/reference_data.npz`` (generated there by
 iisignature, see the reference's ``tests/fixtures/generate_fixtures_iisig.py:47-82``
 and consumed by its ``tests/test_signature.py:32-110`` and
-``tests/test_sig_backprop.py:69-98``).  Only the keys that pin ``sig`` and
-``sig_backprop`` are kept; the file written here is what the tests read, so the
+``tests/test_sig_backprop.py:69-98``, ``tests/test_sig_combine_backprop.py:28-67``).  Only the
+keys that pin ``sig``, ``sig_backprop`` and ``sig_combine_backprop`` are kept; the file written here is what the tests read, so the
 suite does not need the reference tree at run time.
 
 Usage (only where the reference tree is mounted):
@@ -16,7 +16,7 @@ import sys
 import numpy as np
 
 KEEP_PREFIXES = ("path", "sig__d", "sig_ta__d", "sig_ll__d", "sig_ta_ll__d",
-                 "sig_bp_derivs__d", "sig_bp_expected__d")
+                 "sig_bp_derivs__d", "sig_bp_expected__d", "sig_comb_bp_")
 
 
 def main(reference_root):

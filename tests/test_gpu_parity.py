@@ -420,3 +420,33 @@ def test_sig_combine_matches_oracle_and_chen_identity(dtype, tol):
         np.testing.assert_array_equal(tg.cpu().numpy(), got)
     with pytest.raises(ValueError):
         pysiglib_b200.sig_combine(np.zeros((2, 14)), np.zeros((2, 13)), 2, 3)
+
+
+@pytest.mark.parametrize("deg", range(1, 6))
+def test_golden_sig_combine_backprop(golden, deg):
+    """The reference's iisignature vectors for sig_combine_backprop (tests/test_sig_combine_backprop.py),
+    host arrays and device tensors, scalar-term layout."""
+    import pysiglib_b200
+    s1, s2 = golden["sig_comb_bp_sig1__d%d" % deg], golden["sig_comb_bp_sig2__d%d" % deg]
+    derivs = golden["sig_comb_bp_derivs__d%d" % deg]
+    d1, d2 = pysiglib_b200.sig_combine_backprop(derivs, s1, s2, 3, deg)
+    np.testing.assert_allclose(d1[:, 1:], golden["sig_comb_bp_d1__d%d" % deg], rtol=0, atol=1e-5)
+    np.testing.assert_allclose(d2[:, 1:], golden["sig_comb_bp_d2__d%d" % deg], rtol=0, atol=1e-5)
+    assert not d1[:, 0].any() and not d2[:, 0].any()
+    t1, t2 = pysiglib_b200.sig_combine_backprop(torch.tensor(derivs, device="cuda"), torch.tensor(s1, device="cuda"),
+                                                torch.tensor(s2, device="cuda"), 3, deg)
+    np.testing.assert_array_equal(t1.cpu().numpy(), d1)
+    np.testing.assert_array_equal(t2.cpu().numpy(), d2)
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float64, 1e-10), (np.float32, 1e-5)])
+def test_sig_combine_backprop_matches_oracle(dtype, tol):
+    import pysiglib_b200
+    rng = np.random.default_rng(12)
+    for (B, d, N) in ((4, 3, 4), (2, 8, 4), (3, 2, 8), (2, 16, 3)):
+        n = oracle.sig_length(d, N)
+        a, b, g = (np.ascontiguousarray(rng.normal(size=(B, n)).astype(dtype)) for _ in range(3))
+        d1, d2 = pysiglib_b200.sig_combine_backprop(g, a, b, d, N)
+        w1, w2 = oracle.sig_combine_backprop(g, a, b, d, N)
+        assert_sig_close(d1, w1, d, N, tol)
+        assert_sig_close(d2, w2, d, N, tol)

@@ -242,3 +242,31 @@ def test_sig_combine_is_chen_identity():  # reference tests: sig(x1 * x2) == sig
     s1 = np.array([1., 1., 1., .5, .5, .5, .5])
     s2 = np.array([1., 0., 1., 0., 1., -1., .5])
     np.testing.assert_allclose(oracle.sig_combine(s1, s2, 2, 2), [1., 1., 2., .5, 2.5, -.5, 2.], atol=1e-15)
+
+
+@pytest.mark.parametrize("deg", range(1, 6))
+def test_fixture_sig_combine_backprop(golden, deg):
+    # reference tests/test_sig_combine_backprop.py:28-67 (dimension 3, inputs carry the scalar slot)
+    s1, s2 = golden["sig_comb_bp_sig1__d%d" % deg], golden["sig_comb_bp_sig2__d%d" % deg]
+    derivs = golden["sig_comb_bp_derivs__d%d" % deg]
+    d1, d2 = oracle.sig_combine_backprop(derivs, s1, s2, 3, deg)
+    np.testing.assert_allclose(d1[:, 1:], golden["sig_comb_bp_d1__d%d" % deg], rtol=0, atol=1e-5)
+    np.testing.assert_allclose(d2[:, 1:], golden["sig_comb_bp_d2__d%d" % deg], rtol=0, atol=1e-5)
+    assert not d1[:, 0].any() and not d2[:, 0].any()
+
+
+def test_sig_combine_backprop_matches_autograd():
+    rng = np.random.default_rng(4)
+    d, N = 3, 3
+    n = oracle.sig_length(d, N)
+    a, b, g = rng.normal(size=n), rng.normal(size=n), rng.normal(size=n)
+    ta, tb = torch.tensor(a, requires_grad=True), torch.tensor(b, requires_grad=True)
+    off = [0, 3, 12, 39]
+    la = [torch.ones(1, dtype=torch.float64)] + [ta[off[k]:off[k + 1]] for k in range(N)]
+    lb = [torch.ones(1, dtype=torch.float64)] + [tb[off[k]:off[k + 1]] for k in range(N)]
+    prod = torch.cat([sum(torch.kron(la[i], lb[k - i]) for i in range(k + 1)) for k in range(1, N + 1)])
+    np.testing.assert_allclose(oracle.sig_combine(a, b, d, N), prod.detach().numpy(), rtol=1e-13)
+    (prod * torch.tensor(g)).sum().backward()
+    d1, d2 = oracle.sig_combine_backprop(g, a, b, d, N)
+    np.testing.assert_allclose(d1, ta.grad.numpy(), rtol=1e-12, atol=1e-14)
+    np.testing.assert_allclose(d2, tb.grad.numpy(), rtol=1e-12, atol=1e-14)
