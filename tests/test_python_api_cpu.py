@@ -97,3 +97,24 @@ def test_shard_bounds_cover_the_batch():
             assert all(x[1] == y[0] for x, y in zip(b, b[1:]))
             sizes = [e - s for s, e in b]
             assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+
+
+def test_sig_combine_argument_contract():
+    p = inspect.signature(psl.sig_combine).parameters
+    assert list(p) == ["sig1", "sig2", "dimension", "degree", "time_aug", "lead_lag", "n_jobs"]
+    q = inspect.signature(psl.sig_combine_backprop).parameters
+    assert list(q) == ["deriv", "sig1", "sig2", "dimension", "degree", "time_aug", "lead_lag", "n_jobs"]
+    a = np.zeros((2, 14))
+    with pytest.raises(ValueError):
+        psl.sig_combine(a, np.zeros((2, 15)), 2, 3)            # lengths differ
+    with pytest.raises(ValueError):
+        psl.sig_combine(np.zeros((2, 13)), np.zeros((2, 13)), 2, 3)   # neither layout of (d=2, N=3)
+    with pytest.raises(ValueError):
+        psl.sig_combine(a, a.astype(np.float32), 2, 3)          # dtypes differ
+    with pytest.raises(TypeError):
+        psl.sig_combine(a, a, 2.0, 3)
+    with pytest.raises(ValueError):
+        psl.sig_combine_backprop(np.zeros((3, 14)), a, a, 2, 3)  # batch shapes differ
+    assert psl.sig_combine(np.zeros((0, 14)), np.zeros((0, 14)), 2, 3).shape == (0, 14)
+    d1, d2 = psl.sig_combine_backprop(np.zeros((0, 15)), np.zeros((0, 15)), np.zeros((0, 15)), 2, 3)
+    assert d1.shape == d2.shape == (0, 15)
