@@ -1,4 +1,5 @@
-"""Builds libcusig.so (sm_100a) from pysiglib_b200/csrc with nvcc, in-tree and incrementally.
+"""Builds libcusig.so (sm_100a) from pysiglib_b200/csrc with nvcc, in-tree and incrementally
+(an object is recompiled only when a file its preprocessor run reads has changed).
 
     python -m pysiglib_b200._build [--force] [--jobs N]
 
@@ -53,17 +54,48 @@ def _stamp(dev=False):
     return h.hexdigest()
 
 
-def _compile(unit):
+def _unit_hash(unit):
+    """Hash of one translation unit: its flags and the contents of every file of this
+    repository that the preprocessor pulls in (nvcc -M), so that an edit recompiles only
+    the objects that can see it."""
     obj, src, extra = unit
-    extra = extra + _EXTRA
-    cmd = [_nvcc()] + NVCC_FLAGS + extra + ["-c", os.path.join(CSRC, src), "-o", os.path.join(OBJ, obj)]
+    cmd = [_nvcc()] + NVCC_FLAGS + extra + _EXTRA + ["-M", os.path.join(CSRC, src)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc -M failed for %s:\n%s\n%s" % (src, proc.stdout, proc.stderr))
+    root = os.path.realpath(os.path.join(HERE, ".."))
+    deps = set()
+    for tok in proc.stdout.split(":", 1)[-1].replace("\\\n", " ").split():
+        path = os.path.realpath(tok)
+        if path.startswith(root + os.sep):
+            deps.add(path)
+    h = hashlib.sha256((" ".join(NVCC_FLAGS + extra + _EXTRA)).encode())
+    for path in sorted(deps):
+        with open(path, "rb") as f:
+            h.update(os.path.relpath(path, root).encode() + f.read())
+    return h.hexdigest()
+
+
+def _compile(unit):
+    """Compiles one unit unless its object is already up to date; returns (object, rebuilt)."""
+    obj, src, extra = unit
+    digest = _unit_hash(unit)
+    obj_path, hash_path = os.path.join(OBJ, obj), os.path.join(OBJ, obj + ".hash")
+    if not _FORCE[0] and os.path.exists(obj_path) and os.path.exists(hash_path):
+        with open(hash_path) as f:
+            if f.read().strip() == digest:
+                return obj, False
+    cmd = [_nvcc()] + NVCC_FLAGS + extra + _EXTRA + ["-c", os.path.join(CSRC, src), "-o", obj_path]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, proc.stdout, proc.stderr))
-    return obj
+    with open(hash_path, "w") as f:
+        f.write(digest)
+    return obj, True
 
 
 _EXTRA = []
+_FORCE = [False]
 
 
 def build(force=False, jobs=None, verbose=False, dev=None):
@@ -76,6 +108,9 @@ def build(force=False, jobs=None, verbose=False, dev=None):
     _EXTRA[:] = ["-DSIG_TILE_DEV"] if dev else []
     if os.environ.get("SIGB200_NO_PACKED_F32", "0") == "1":  # experiment switch: scalar FP32 rows
         _EXTRA.append("-DSIG_NO_PACKED_F32")
+    _FORCE[0] = bool(force)
+    global OBJ
+    OBJ = os.path.join(CSRC, "_build_dev" if dev else "_build")  # two caches: switching tables recompiles nothing
     os.makedirs(OBJ, exist_ok=True)
     os.makedirs(LIB_DIR, exist_ok=True)
     stamp, stamp_file = _stamp(dev), os.path.join(LIB_DIR, "stamp.txt")
@@ -86,9 +121,9 @@ def build(force=False, jobs=None, verbose=False, dev=None):
     units = _units()
     jobs = jobs or min(len(units), os.cpu_count() or 4)
     with concurrent.futures.ThreadPoolExecutor(max_workers=jobs) as pool:
-        for obj in pool.map(_compile, units):
+        for obj, rebuilt in pool.map(_compile, units):
             if verbose:
-                print("compiled", obj, flush=True)
+                print("compiled" if rebuilt else "up to date", obj, flush=True)
     link = [_nvcc(), "-shared", "-o", LIB] + [os.path.join(OBJ, u[0]) for u in units] + \
            ["-gencode", "arch=compute_100a,code=sm_100a"]
     proc = subprocess.run(link, capture_output=True, text=True)
