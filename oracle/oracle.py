@@ -17,7 +17,7 @@ _LIB = None
 
 def build(force=False):
     """Compile the oracle with gcc (idempotent)."""
-    src = [os.path.join(_HERE, f) for f in ("sig_oracle.c", "sig_oracle_impl.h")]
+    src = [os.path.join(_HERE, f) for f in ("sig_oracle.c", "sig_oracle_impl.h", "sig_oracle_algebra.h")]
     if (not force and os.path.exists(_LIB_PATH)
             and all(os.path.getmtime(_LIB_PATH) >= os.path.getmtime(s) for s in src)):
         return _LIB_PATH
@@ -47,6 +47,19 @@ def _lib():
             cbp = getattr(lib, "oracle_sig_combine_backprop_" + suf)
             cbp.restype = ctypes.c_int
             cbp.argtypes = [ptr, ptr, ptr, ptr, ptr, u64, u64, u64, ctypes.c_int]
+            ci = ctypes.c_int
+            for name, args in (
+                    ("oracle_signature_correction_", [ptr, ptr, u64, u64, u64, u64, ci, real, ci, ptr, u64, u64, u64]),
+                    ("oracle_sig_backprop_correction_",
+                     [ptr, ptr, ptr, ptr, u64, u64, u64, u64, ci, real, ci, ptr, u64, u64, u64]),
+                    ("oracle_tensor_exp_", [ptr, ptr, u64, u64]),
+                    ("oracle_tensor_exp_backprop_", [ptr, ptr, ptr, u64, u64]),
+                    ("oracle_linear_sig_", [ptr, ptr, u64, u64, u64, ci]),
+                    ("oracle_sig_join_", [ptr, ptr, ptr, u64, u64, u64, ci, ci]),
+                    ("oracle_sig_join_backprop_", [ptr, ptr, ptr, ptr, ptr, u64, u64, u64, ci, ci])):
+                fn = getattr(lib, name + suf)
+                fn.restype = ctypes.c_int
+                fn.argtypes = args
         lib.oracle_sig_length.restype = u64
         lib.oracle_sig_length.argtypes = [u64, u64]
         _LIB = lib
@@ -70,9 +83,23 @@ def sig_length(dim, degree, scalar_term=False):
     return n - (0 if scalar_term else 1)
 
 
+def _correction_layout(correction, B, L, dtype):
+    """(array, length, batch stride, segment stride) for the three accepted shapes: (C,),
+    (L-1, C) and (B, L-1, C) (pysiglib/data_handlers.py:233-258)."""
+    c = np.ascontiguousarray(correction, dtype=dtype)
+    if c.ndim == 1:
+        return c, c.shape[0], 0, 0
+    if c.ndim == 2 and c.shape[0] == max(L - 1, 0):
+        return c, c.shape[1], 0, c.shape[1]
+    if c.shape[:-1] != (B, max(L - 1, 0)):
+        raise ValueError("correction shape")
+    return c, c.shape[-1], max(L - 1, 0) * c.shape[-1], c.shape[-1]
+
+
 def sig(path, degree, *, time_aug=False, lead_lag=False, end_time=1.0, horner=True,
-        scalar_term=False, n_threads=1):
-    """Oracle signature of ``path`` (B, L, d) or (L, d); numpy in, numpy out."""
+        scalar_term=False, n_threads=1, correction=None):
+    """Oracle signature of ``path`` (B, L, d) or (L, d); numpy in, numpy out.  ``correction``
+    adds per-segment higher-level terms: segment signature = exp(increment + correction)."""
     path = np.ascontiguousarray(path)
     single = path.ndim == 2
     p3 = path[None] if single else path
@@ -81,6 +108,16 @@ def sig(path, degree, *, time_aug=False, lead_lag=False, end_time=1.0, horner=Tr
     n = sig_length(aug_dim(d, time_aug, lead_lag), degree, scalar_term)
     out = np.empty((B, n), dtype=p3.dtype)
     ptr = ctypes.POINTER(real)
+    if correction is not None and np.size(correction):
+        if lead_lag:
+            raise ValueError("correction cannot be used with lead_lag")
+        c, clen, bs, ss = _correction_layout(correction, B, L, p3.dtype)
+        rc = getattr(_lib(), "oracle_signature_correction_" + suf)(
+            p3.ctypes.data_as(ptr), out.ctypes.data_as(ptr), B, d, L, degree, int(time_aug), real(end_time),
+            int(scalar_term), c.ctypes.data_as(ptr), clen, bs, ss)
+        if rc:
+            raise RuntimeError("oracle_signature_correction failed with code %d" % rc)
+        return out[0] if single else out
     rc = getattr(_lib(), "oracle_signature_" + suf)(
         p3.ctypes.data_as(ptr), out.ctypes.data_as(ptr), B, d, L, degree,
         int(time_aug), int(lead_lag), real(end_time), int(horner), int(scalar_term), int(n_threads))
@@ -90,7 +127,7 @@ def sig(path, degree, *, time_aug=False, lead_lag=False, end_time=1.0, horner=Tr
 
 
 def sig_backprop(path, sig_, sig_derivs, degree, *, time_aug=False, lead_lag=False,
-                 end_time=1.0, n_threads=1):
+                 end_time=1.0, n_threads=1, correction=None):
     """Oracle gradient of sum(sig * sig_derivs) w.r.t. ``path``; scalar-term format inferred."""
     path = np.ascontiguousarray(path)
     single = path.ndim == 2
@@ -105,6 +142,16 @@ def sig_backprop(path, sig_, sig_derivs, degree, *, time_aug=False, lead_lag=Fal
     scalar_term = s2.shape[1] == full
     out = np.empty_like(p3)
     ptr = ctypes.POINTER(real)
+    if correction is not None and np.size(correction):
+        if lead_lag:
+            raise ValueError("correction cannot be used with lead_lag")
+        c, clen, bs, ss = _correction_layout(correction, B, L, p3.dtype)
+        rc = getattr(_lib(), "oracle_sig_backprop_correction_" + suf)(
+            p3.ctypes.data_as(ptr), out.ctypes.data_as(ptr), g2.ctypes.data_as(ptr), s2.ctypes.data_as(ptr),
+            B, d, L, degree, int(time_aug), real(end_time), int(scalar_term), c.ctypes.data_as(ptr), clen, bs, ss)
+        if rc:
+            raise RuntimeError("oracle_sig_backprop_correction failed with code %d" % rc)
+        return out[0] if single else out
     rc = getattr(_lib(), "oracle_sig_backprop_" + suf)(
         p3.ctypes.data_as(ptr), out.ctypes.data_as(ptr), g2.ctypes.data_as(ptr),
         s2.ctypes.data_as(ptr), B, d, L, degree, int(time_aug), int(lead_lag), real(end_time),
@@ -153,3 +200,84 @@ def sig_combine_backprop(deriv, sig1, sig2, dim, degree):
     if rc:
         raise RuntimeError("oracle_sig_combine_backprop failed with code %d" % rc)
     return o1.reshape(a.shape), o2.reshape(a.shape)
+
+
+def tensor_exp(log_sig, dim, degree):
+    """Oracle truncated tensor exponential of one element given WITH its scalar slot (ignored)."""
+    x = np.ascontiguousarray(log_sig)
+    suf, real = _suffix(x)
+    out = np.empty_like(x)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_tensor_exp_" + suf)(x.ctypes.data_as(ptr), out.ctypes.data_as(ptr), dim, degree)
+    if rc:
+        raise RuntimeError("oracle_tensor_exp failed with code %d" % rc)
+    return out
+
+
+def tensor_exp_backprop(d_sig, log_sig, dim, degree):
+    """Oracle adjoint of tensor_exp (both arrays with their scalar slots)."""
+    x = np.ascontiguousarray(log_sig)
+    g = np.ascontiguousarray(d_sig, dtype=x.dtype)
+    suf, real = _suffix(x)
+    out = np.empty_like(x)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_tensor_exp_backprop_" + suf)(out.ctypes.data_as(ptr), g.ctypes.data_as(ptr),
+                                                              x.ctypes.data_as(ptr), dim, degree)
+    if rc:
+        raise RuntimeError("oracle_tensor_exp_backprop failed with code %d" % rc)
+    return out
+
+
+def linear_sig(displacement, degree, scalar_term=False):
+    """Oracle signature of the straight segment with the given displacement(s) (..., d)."""
+    v = np.ascontiguousarray(displacement)
+    v2 = v.reshape(-1, v.shape[-1])
+    suf, real = _suffix(v2)
+    dim = v2.shape[1]
+    out = np.empty((v2.shape[0], sig_length(dim, degree, scalar_term)), dtype=v2.dtype)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_linear_sig_" + suf)(v2.ctypes.data_as(ptr), out.ctypes.data_as(ptr), v2.shape[0],
+                                                     dim, degree, int(scalar_term))
+    if rc:
+        raise RuntimeError("oracle_linear_sig failed with code %d" % rc)
+    return out.reshape(v.shape[:-1] + (out.shape[1],))
+
+
+def sig_join(sig_, displacement, dim, degree, prepend=False):
+    """Oracle sig (x) linear_sig(displacement) (or the reverse product with prepend=True)."""
+    a = np.ascontiguousarray(sig_)
+    a2 = a.reshape(-1, a.shape[-1])
+    v2 = np.ascontiguousarray(displacement, dtype=a.dtype).reshape(a2.shape[0], dim)
+    suf, real = _suffix(a2)
+    full = sig_length(dim, degree, True)
+    if a2.shape[1] not in (full, full - 1):
+        raise ValueError("signature has the wrong length")
+    out = np.empty_like(a2)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_sig_join_" + suf)(a2.ctypes.data_as(ptr), v2.ctypes.data_as(ptr),
+                                                   out.ctypes.data_as(ptr), a2.shape[0], dim, degree, int(prepend),
+                                                   int(a2.shape[1] == full))
+    if rc:
+        raise RuntimeError("oracle_sig_join failed with code %d" % rc)
+    return out.reshape(a.shape)
+
+
+def sig_join_backprop(d_out, sig_, displacement, dim, degree, prepend=False):
+    """Oracle adjoints (d sig, d displacement) of sig_join."""
+    a = np.ascontiguousarray(sig_)
+    a2 = a.reshape(-1, a.shape[-1])
+    v = np.ascontiguousarray(displacement, dtype=a.dtype)
+    v2 = v.reshape(a2.shape[0], dim)
+    g2 = np.ascontiguousarray(d_out, dtype=a.dtype).reshape(a2.shape)
+    suf, real = _suffix(a2)
+    full = sig_length(dim, degree, True)
+    if a2.shape[1] not in (full, full - 1):
+        raise ValueError("signature has the wrong length")
+    d_sig, d_disp = np.empty_like(a2), np.empty_like(v2)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_sig_join_backprop_" + suf)(
+        g2.ctypes.data_as(ptr), d_sig.ctypes.data_as(ptr), d_disp.ctypes.data_as(ptr), a2.ctypes.data_as(ptr),
+        v2.ctypes.data_as(ptr), a2.shape[0], dim, degree, int(prepend), int(a2.shape[1] == full))
+    if rc:
+        raise RuntimeError("oracle_sig_join_backprop failed with code %d" % rc)
+    return d_sig.reshape(a.shape), d_disp.reshape(v.shape)

@@ -37,6 +37,7 @@ uint64_t oracle_sig_length(uint64_t dim, uint64_t degree) {
 #define SUF f
 #define FMA(a, b, c) fmaf((a), (b), (c))
 #include "sig_oracle_impl.h"
+#include "sig_oracle_algebra.h"
 #undef REAL
 #undef SUF
 #undef FMA
@@ -45,6 +46,7 @@ uint64_t oracle_sig_length(uint64_t dim, uint64_t degree) {
 #define SUF d
 #define FMA(a, b, c) fma((a), (b), (c))
 #include "sig_oracle_impl.h"
+#include "sig_oracle_algebra.h"
 #undef REAL
 #undef SUF
 #undef FMA
