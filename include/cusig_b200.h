@@ -32,7 +32,10 @@ extern "C" {
  *           siglib/cusig/cu_signature.cu:3497-3517 (definition); bound by
  *           pysiglib/load_siglib.py:484-488.
  * `horner` is accepted for compatibility; both settings run the Horner kernels.
- * A non-empty `correction` is rejected with code 2.  Synchronous. */
+ * A non-empty `correction` (correction_len values per segment, a prefix of tensor levels
+ * 2..degree of the data dimension; segment j of path b at correction + b * batch_stride +
+ * j * segment_stride) makes every segment's signature exp(increment + correction)
+ * (siglib/cusig/cu_signature.cu:2369-2427, 2503-2531); not allowed with lead_lag.  Synchronous. */
 int signature_cuda_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
                      uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, float end_time,
                      bool horner, bool scalar_term, const float* correction, uint64_t correction_len,
@@ -45,7 +48,9 @@ int signature_cuda_d(const double* path, double* out, uint64_t batch_size, uint6
 /* Gradient of a scalar loss with respect to the path, given dLoss/dSignature.
  * Replaces: siglib/cusig/cusig.h:342-344, siglib/cusig/cu_signature.cu:3524-3544; bound by
  *           pysiglib/load_siglib.py:490-494.  Note the order: sig_derivs before sig.
- * `out` has the shape of `path`.  Synchronous. */
+ * `out` has the shape of `path`.  With a non-empty `correction` the gradient is that of the
+ * corrected signature, still with respect to the path only (siglib/cusig/cu_signature.cu:2659-2763).
+ * Synchronous. */
 int sig_backprop_cuda_f(const float* path, float* out, const float* sig_derivs, const float* sig,
                         uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
                         bool time_aug, bool lead_lag, float end_time, bool scalar_term,
@@ -76,6 +81,48 @@ int sig_combine_backprop_cuda_f(const float* sig_combined_deriv, float* sig1_der
 int sig_combine_backprop_cuda_d(const double* sig_combined_deriv, double* sig1_deriv, double* sig2_deriv,
                                 const double* sig1, const double* sig2, uint64_t batch_size, uint64_t dimension,
                                 uint64_t degree, bool scalar_term);
+
+/* Signature of the straight segment with the given displacement: out[b] = exp(displacement[b]),
+ * level k = displacement^(x)k / k!.
+ * Replaces: siglib/cusig/cusig.h:942-944 (siglib/cusig/cu_sig_combine.cu); bound by
+ *           pysiglib/load_siglib.py:618-622.  Synchronous; device or host pointers. */
+int linear_sig_cuda_f(const float* displacement, float* out, uint64_t batch_size, uint64_t dimension,
+                      uint64_t degree, bool scalar_term);
+int linear_sig_cuda_d(const double* displacement, double* out, uint64_t batch_size, uint64_t dimension,
+                      uint64_t degree, bool scalar_term);
+
+/* Extends signatures by one straight segment: out = sig (x) exp(displacement), or
+ * exp(displacement) (x) sig with `prepend`.
+ * Replaces: siglib/cusig/cusig.h:962-964 (siglib/cusig/cu_sig_combine.cu:495-543); bound by
+ *           pysiglib/load_siglib.py:455-459.  Synchronous; device or host pointers. */
+int sig_join_cuda_f(const float* sig, const float* displacement, float* out, uint64_t batch_size,
+                    uint64_t dimension, uint64_t degree, bool prepend, bool scalar_term);
+int sig_join_cuda_d(const double* sig, const double* displacement, double* out, uint64_t batch_size,
+                    uint64_t dimension, uint64_t degree, bool prepend, bool scalar_term);
+
+/* Backward of sig_join: writes dLoss/d sig (scalar slots 0) and dLoss/d displacement.
+ * Replaces: siglib/cusig/cusig.h:984-986 (siglib/cusig/cu_sig_combine.cu:549-659); bound by
+ *           pysiglib/load_siglib.py:460-464.  Computed entirely on the device. */
+int sig_join_backprop_cuda_f(const float* d_out, float* d_sig, float* d_displacement, const float* sig,
+                             const float* displacement, uint64_t batch_size, uint64_t dimension,
+                             uint64_t degree, bool prepend, bool scalar_term);
+int sig_join_backprop_cuda_d(const double* d_out, double* d_sig, double* d_displacement, const double* sig,
+                             const double* displacement, uint64_t batch_size, uint64_t dimension,
+                             uint64_t degree, bool prepend, bool scalar_term);
+
+/* Materialises the lead-lag / time-augmented path: (B, L, d) -> (B, L', d') with L' = 2L-1 under
+ * lead_lag and d' = (lead_lag ? 2d : d) + (time_aug ? 1 : 0); and the adjoint of that map
+ * ((B, L', d') -> (B, L, d), the time channel dropped).
+ * Replaces: siglib/cusig/cusig.h:65-67, 90-92 (siglib/cusig/cu_path_transforms.cu:100-205); bound by
+ *           pysiglib/load_siglib.py:420-429.  Synchronous; device or host pointers. */
+int transform_path_cuda_f(const float* data_in, float* data_out, uint64_t batch_size, uint64_t dimension,
+                          uint64_t length, bool time_aug, bool lead_lag, float end_time);
+int transform_path_cuda_d(const double* data_in, double* data_out, uint64_t batch_size, uint64_t dimension,
+                          uint64_t length, bool time_aug, bool lead_lag, double end_time);
+int transform_path_backprop_cuda_f(const float* derivs, float* data_out, uint64_t batch_size, uint64_t dimension,
+                                   uint64_t length, bool time_aug, bool lead_lag, float end_time);
+int transform_path_backprop_cuda_d(const double* derivs, double* data_out, uint64_t batch_size, uint64_t dimension,
+                                   uint64_t length, bool time_aug, bool lead_lag, double end_time);
 
 /* Thread-local text of the last error; valid until the next call on this thread.
  * Replaces: siglib/cusig/cusig.h:43; bound by pysiglib/load_siglib.py:108-110. */

@@ -39,7 +39,20 @@ def _ptr(t):
     return ctypes.cast(t.data_ptr(), ctypes.POINTER(_real(t)))
 
 
-def sig(path, degree, *, time_aug=False, lead_lag=False, end_time=1.0, scalar_term=False, out=None):
+def _correction_args(correction, B, L):
+    """(pointer, length, batch stride, segment stride) for a contiguous CUDA tensor of shape (C,),
+    (L-1, C) or (B, L-1, C), or the empty correction."""
+    if correction is None or correction.numel() == 0:
+        return None, 0, 0, 0
+    c = correction.shape[-1]
+    if correction.dim() == 1:
+        return _ptr(correction), c, 0, 0
+    if correction.dim() == 2:
+        return _ptr(correction), c, 0, c
+    return _ptr(correction), c, (L - 1) * c, c
+
+
+def sig(path, degree, *, time_aug=False, lead_lag=False, end_time=1.0, scalar_term=False, out=None, correction=None):
     """Reference signature_cuda_* on a contiguous CUDA tensor (B, L, d)."""
     import torch
     B, L, d = path.shape
@@ -50,14 +63,15 @@ def sig(path, degree, *, time_aug=False, lead_lag=False, end_time=1.0, scalar_te
     real = _real(path)
     suf = "f" if real is ctypes.c_float else "d"
     rc = getattr(library(), "signature_cuda_" + suf)(_ptr(path), _ptr(out), B, d, L, degree, time_aug, lead_lag,
-                                                      real(end_time), True, scalar_term, None, 0, 0, 0)
+                                                      real(end_time), True, scalar_term,
+                                                      *_correction_args(correction, B, L))
     if rc:
         raise RuntimeError("reference signature_cuda failed with code %d" % rc)
     return out
 
 
 def sig_backprop(path, sig_, derivs, degree, *, time_aug=False, lead_lag=False, end_time=1.0, scalar_term=False,
-                 out=None):
+                 out=None, correction=None):
     import torch
     B, L, d = path.shape
     if out is None:
@@ -66,7 +80,7 @@ def sig_backprop(path, sig_, derivs, degree, *, time_aug=False, lead_lag=False, 
     suf = "f" if real is ctypes.c_float else "d"
     rc = getattr(library(), "sig_backprop_cuda_" + suf)(_ptr(path), _ptr(out), _ptr(derivs), _ptr(sig_), B, d, L,
                                                          degree, time_aug, lead_lag, real(end_time), scalar_term,
-                                                         None, 0, 0, 0)
+                                                         *_correction_args(correction, B, L))
     if rc:
         raise RuntimeError("reference sig_backprop_cuda failed with code %d" % rc)
     return out

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../include/cusig_b200.h"
+#include "algebra.h"
 #include "dispatch.h"
 #include "kernels.h"
 #include "runtime.h"
@@ -106,7 +107,7 @@ void sig_backprop_sharded(const T* path, T* out, const T* sig_derivs, const T* s
 int stub_not_built(const char* name) noexcept {
     clear_last_error();
     std::string msg = std::string(name) +
-        " is not part of this build of libcusig (only signature_cuda_* and sig_backprop_cuda_* are served)";
+        " is not part of this build of libcusig (it serves the signature, sig_backprop, sig_combine, sig_join, linear_sig and transform_path families)";
     set_last_error(msg.c_str());
     return 10;
 }
@@ -118,35 +119,39 @@ int stub_not_built(const char* name) noexcept {
 SIG_API int signature_cuda_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
                              uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, float end_time,
                              bool horner, bool scalar_term, const float* correction, uint64_t correction_len,
-                             uint64_t, uint64_t) {
+                             uint64_t correction_batch_stride, uint64_t correction_segment_stride) {
     SIG_SAFE_CALL(signature_entry<float>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag,
-                                         end_time, horner, scalar_term, correction, correction_len, sync_options()));
+                                         end_time, horner, scalar_term, correction, correction_len, sync_options(),
+                        correction_batch_stride, correction_segment_stride));
 }
 
 SIG_API int signature_cuda_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension,
                              uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, double end_time,
                              bool horner, bool scalar_term, const double* correction, uint64_t correction_len,
-                             uint64_t, uint64_t) {
+                             uint64_t correction_batch_stride, uint64_t correction_segment_stride) {
     SIG_SAFE_CALL(signature_entry<double>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag,
-                                          end_time, horner, scalar_term, correction, correction_len, sync_options()));
+                                          end_time, horner, scalar_term, correction, correction_len, sync_options(),
+                        correction_batch_stride, correction_segment_stride));
 }
 
 SIG_API int sig_backprop_cuda_f(const float* path, float* out, const float* sig_derivs, const float* sig,
                                 uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
                                 bool time_aug, bool lead_lag, float end_time, bool scalar_term,
-                                const float* correction, uint64_t correction_len, uint64_t, uint64_t) {
+                                const float* correction, uint64_t correction_len, uint64_t correction_batch_stride,
+                                uint64_t correction_segment_stride) {
     SIG_SAFE_CALL(sig_backprop_entry<float>(path, out, sig_derivs, sig, batch_size, dimension, length, degree,
                                             time_aug, lead_lag, end_time, scalar_term, correction, correction_len,
-                                            sync_options()));
+                                            sync_options(), correction_batch_stride, correction_segment_stride));
 }
 
 SIG_API int sig_backprop_cuda_d(const double* path, double* out, const double* sig_derivs, const double* sig,
                                 uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
                                 bool time_aug, bool lead_lag, double end_time, bool scalar_term,
-                                const double* correction, uint64_t correction_len, uint64_t, uint64_t) {
+                                const double* correction, uint64_t correction_len, uint64_t correction_batch_stride,
+                                uint64_t correction_segment_stride) {
     SIG_SAFE_CALL(sig_backprop_entry<double>(path, out, sig_derivs, sig, batch_size, dimension, length, degree,
                                              time_aug, lead_lag, end_time, scalar_term, correction, correction_len,
-                                             sync_options()));
+                                             sync_options(), correction_batch_stride, correction_segment_stride));
 }
 
 SIG_API int sig_combine_cuda_f(const float* sig1, const float* sig2, float* out, uint64_t batch_size,
@@ -172,6 +177,38 @@ SIG_API int sig_combine_backprop_cuda_d(const double* sig_combined_deriv, double
     SIG_SAFE_CALL(sig_combine_backprop_entry<double>(sig_combined_deriv, sig1_deriv, sig2_deriv, sig1, sig2, batch_size,
                                                      dimension, degree, scalar_term, sync_options()));
 }
+
+#define SIG_ALGEBRA_EXPORTS(SUF, T)                                                                                   \
+    SIG_API int linear_sig_cuda_##SUF(const T* displacement, T* out, uint64_t batch_size, uint64_t dimension,         \
+                                      uint64_t degree, bool scalar_term) {                                            \
+        SIG_SAFE_CALL(linear_sig_entry<T>(displacement, out, batch_size, dimension, degree, scalar_term,              \
+                                          sync_options()));                                                           \
+    }                                                                                                                 \
+    SIG_API int sig_join_cuda_##SUF(const T* sig, const T* displacement, T* out, uint64_t batch_size,                 \
+                                    uint64_t dimension, uint64_t degree, bool prepend, bool scalar_term) {            \
+        SIG_SAFE_CALL(sig_join_entry<T>(sig, displacement, out, batch_size, dimension, degree, prepend, scalar_term,  \
+                                        sync_options()));                                                             \
+    }                                                                                                                 \
+    SIG_API int sig_join_backprop_cuda_##SUF(const T* d_out, T* d_sig, T* d_displacement, const T* sig,               \
+                                             const T* displacement, uint64_t batch_size, uint64_t dimension,          \
+                                             uint64_t degree, bool prepend, bool scalar_term) {                       \
+        SIG_SAFE_CALL(sig_join_backprop_entry<T>(d_out, d_sig, d_displacement, sig, displacement, batch_size,         \
+                                                 dimension, degree, prepend, scalar_term, sync_options()));           \
+    }                                                                                                                 \
+    SIG_API int transform_path_cuda_##SUF(const T* data_in, T* data_out, uint64_t batch_size, uint64_t dimension,     \
+                                          uint64_t length, bool time_aug, bool lead_lag, T end_time) {                \
+        SIG_SAFE_CALL(transform_path_entry<T>(data_in, data_out, batch_size, dimension, length, time_aug, lead_lag,   \
+                                              end_time, sync_options()));                                             \
+    }                                                                                                                 \
+    SIG_API int transform_path_backprop_cuda_##SUF(const T* derivs, T* data_out, uint64_t batch_size,                 \
+                                                   uint64_t dimension, uint64_t length, bool time_aug,                \
+                                                   bool lead_lag, T end_time) {                                       \
+        SIG_SAFE_CALL(transform_path_backprop_entry<T>(derivs, data_out, batch_size, dimension, length, time_aug,     \
+                                                       lead_lag, end_time, sync_options()));                          \
+    }
+SIG_ALGEBRA_EXPORTS(f, float)
+SIG_ALGEBRA_EXPORTS(d, double)
+#undef SIG_ALGEBRA_EXPORTS
 
 SIG_API const char* cusig_last_error_message(void) { return last_error(); }
 
@@ -289,17 +326,14 @@ SIG_API uint64_t sigb200_launch_count(void) { return launch_count(); }
 #define SIG_STUB(name) SIG_API int name(...) { return stub_not_built(#name); }
 #define SIG_STUB_PAIR(name) SIG_STUB(name##_f) SIG_STUB(name##_d)
 
-SIG_STUB_PAIR(transform_path_cuda) SIG_STUB_PAIR(transform_path_backprop_cuda)
 SIG_STUB_PAIR(log_sig_combine_cuda) SIG_STUB_PAIR(log_sig_combine_backprop_cuda)
 SIG_STUB_PAIR(log_sig_from_path_cuda) SIG_STUB_PAIR(log_sig_from_path_backprop_cuda)
 SIG_STUB_PAIR(log_sig_join_cuda) SIG_STUB_PAIR(log_sig_join_backprop_cuda)
 SIG_STUB_PAIR(logsig_to_sig_cuda) SIG_STUB_PAIR(logsig_to_sig_backprop_cuda)
-SIG_STUB_PAIR(sig_join_cuda) SIG_STUB_PAIR(sig_join_backprop_cuda)
 SIG_STUB_PAIR(sig_coef_cuda) SIG_STUB_PAIR(sig_coef_backprop_cuda)
 SIG_STUB_PAIR(sig_to_log_sig_cuda) SIG_STUB_PAIR(sig_to_log_sig_backprop_cuda)
 SIG_STUB_PAIR(sig_kernel_cuda) SIG_STUB_PAIR(sig_kernel_backprop_cuda)
 SIG_STUB_PAIR(sig_kernel_poly_cuda) SIG_STUB_PAIR(sig_kernel_poly_backprop_cuda)
-SIG_STUB_PAIR(linear_sig_cuda)
 SIG_STUB_PAIR(branched_sig_cuda) SIG_STUB_PAIR(branched_sig_backprop_cuda)
 SIG_STUB_PAIR(branched_sig_coef_cuda) SIG_STUB_PAIR(branched_sig_coef_backprop_cuda)
 SIG_STUB_PAIR(branched_sig_combine_cuda) SIG_STUB_PAIR(branched_sig_combine_backprop_cuda)

@@ -1,0 +1,68 @@
+// Host entry points of the tensor-algebra operations around the signature kernels:
+// signatures with per-segment correction terms, linear signatures, sig_join and the
+// standalone path transforms.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "common.h"
+#include "dispatch.h"
+
+namespace sigb200 {
+
+// Per-segment correction terms as the C ABI passes them (siglib/cusig/cusig.h:312-314):
+// `len` values per segment covering tensor levels 2..k of the DATA dimension; the segment of
+// path b, step j starts at ptr + b * batch_stride + j * segment_stride (strides may be 0).
+template <typename T>
+struct CorrectionView {
+    const T* ptr = nullptr;
+    uint64_t len = 0, batch_stride = 0, segment_stride = 0;
+};
+
+// Throws std::invalid_argument unless the arguments are acceptable (same rules and wording
+// as siglib/cusig/cu_signature.cu:2028-2055).
+void validate_correction(const void* correction, uint64_t correction_len, uint64_t dimension, uint64_t degree,
+                         bool lead_lag);
+
+// Signature with segment signatures exp(increment + correction); device pointers, s.len >= 2,
+// s.degree >= 2, no lead-lag.
+template <typename T>
+void correction_forward_on_device(const T* path, T* out, const SigShape& s, T end_time, const CorrectionView<T>& c,
+                                  cudaStream_t stream);
+
+// Gradient of sum(sig_derivs * sig) w.r.t. the path for the corrected signature.
+template <typename T>
+void correction_backward_on_device(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
+                                   T end_time, const CorrectionView<T>& c, cudaStream_t stream);
+
+// Signature of straight segments: out[b] = exp(displacement[b]).  Replaces linear_sig_cuda_
+// (siglib/cusig/cu_sig_combine.cu).
+template <typename T>
+void linear_sig_entry(const T* displacement, T* out, uint64_t batch, uint64_t dimension, uint64_t degree,
+                      bool scalar_term, const CallOptions& opt);
+
+// out = sig (x) exp(displacement), or exp(displacement) (x) sig with prepend.  Replaces sig_join_cuda_
+// (siglib/cusig/cu_sig_combine.cu:495-543).
+template <typename T>
+void sig_join_entry(const T* sig, const T* displacement, T* out, uint64_t batch, uint64_t dimension,
+                    uint64_t degree, bool prepend, bool scalar_term, const CallOptions& opt);
+
+// Adjoints of sig_join w.r.t. the signature and the displacement.  Replaces sig_join_backprop_cuda_
+// (siglib/cusig/cu_sig_combine.cu:549-659), without its round trip through host memory.
+template <typename T>
+void sig_join_backprop_entry(const T* d_out, T* d_sig, T* d_displacement, const T* sig, const T* displacement,
+                             uint64_t batch, uint64_t dimension, uint64_t degree, bool prepend, bool scalar_term,
+                             const CallOptions& opt);
+
+// Materialises the time-augmented / lead-lag path, and the adjoint of that map.  Replace
+// transform_path_cuda_ and transform_path_backprop_cuda_ (siglib/cusig/cu_path_transforms.cu:100-205).
+template <typename T>
+void transform_path_entry(const T* data_in, T* data_out, uint64_t batch, uint64_t dimension, uint64_t length,
+                          bool time_aug, bool lead_lag, T end_time, const CallOptions& opt);
+template <typename T>
+void transform_path_backprop_entry(const T* derivs, T* data_out, uint64_t batch, uint64_t dimension, uint64_t length,
+                                   bool time_aug, bool lead_lag, T end_time, const CallOptions& opt);
+
+}  // namespace sigb200

@@ -12,8 +12,10 @@
 //   * host pointers are accepted: the batch is cut into chunks that are copied
 //     in, computed and copied out on three streams so the copies overlap compute.
 #include "dispatch.h"
+#include "algebra.h"
 
 #include <algorithm>
+#include <cmath>
 #include <vector>
 
 #include "kernels.h"
@@ -23,15 +25,10 @@ namespace sigb200 {
 
 namespace {
 
-void validate_correction(const void* correction, uint64_t correction_len, bool lead_lag, uint64_t degree) {
-    // siglib/cusig/cu_signature.cu (validate_signature_correction_args_cuda_): a non-empty
-    // correction needs a pointer, degree >= 2 and no lead-lag.
-    if (correction_len == 0) return;
-    if (correction == nullptr) throw std::invalid_argument("correction pointer is null but correction_len != 0");
-    if (lead_lag) throw std::invalid_argument("correction cannot be used with lead_lag");
-    if (degree < 2) throw std::invalid_argument("correction must be empty when degree < 2");
-    throw std::invalid_argument(
-        "per-segment corrections are not implemented in this build of libcusig (sm_100a signature path)");
+// Number of correction values reachable from the base pointer for `batch` paths of `segments` segments.
+template <typename T>
+uint64_t corrected_elems(const CorrectionView<T>& c, uint64_t batch, uint64_t segments) {
+    return (batch - 1) * c.batch_stride + (segments - 1) * c.segment_stride + c.len;
 }
 
 unsigned generic_ctas(const SigShape& s, int sm_count, uint64_t bytes_per_cta) {
@@ -193,15 +190,62 @@ void backward_on_device(const T* path, T* out, const T* sig_derivs, const T* sig
 template <typename T>
 void signature_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, uint64_t length,
                      uint64_t degree, bool time_aug, bool lead_lag, T end_time, bool /*horner*/,
-                     bool scalar_term, const T* correction, uint64_t correction_len, const CallOptions& opt) {
+                     bool scalar_term, const T* correction, uint64_t correction_len, const CallOptions& opt,
+                     uint64_t correction_batch_stride, uint64_t correction_segment_stride) {
     if (dimension == 0) throw std::invalid_argument("signature_cuda received path of dimension 0");
-    validate_correction(correction, correction_len, lead_lag, degree);
+    validate_correction(correction, correction_len, dimension, degree, lead_lag);
     if (opt.nonfinite) *opt.nonfinite = 0;
     if (batch == 0) return;
     const SigShape s = make_shape(batch, dimension, length, degree, time_aug, lead_lag, scalar_term);
     if (s.stride == 0) return;
     if (out == nullptr || (path == nullptr && length * dimension != 0))
         throw std::invalid_argument("signature_cuda received a null pointer");
+    if (correction_len != 0 && s.len > 1) {
+        // segment signatures exp(increment + correction): siglib/cusig/cu_signature.cu:2503-2531
+        const CorrectionView<T> cv{correction, correction_len, correction_batch_stride, correction_segment_stride};
+        const uint64_t corr_elems = corrected_elems(cv, batch, s.len - 1);
+        const PointerInfo po = classify_pointer(out);
+        if (po.on_device) {
+            if (!classify_pointer(path).on_device || !classify_pointer(correction).on_device)
+                throw std::invalid_argument("signature_cuda: path, correction and out must all be device pointers or all host pointers");
+            DeviceGuard guard(po.device);
+            correction_forward_on_device<T>(path, out, s, end_time, cv, opt.stream);
+            if (opt.nonfinite) {
+                Scratch flag(sizeof(int), opt.stream);
+                SIG_CUDA_CHECK(cudaMemsetAsync(flag.get(), 0, sizeof(int), opt.stream));
+                launch_nonfinite_scan<T>(out, s.batch * s.stride, flag.as<int>(), opt.stream);
+                SIG_CUDA_CHECK(cudaMemcpyAsync(opt.nonfinite, flag.get(), sizeof(int), cudaMemcpyDeviceToHost, opt.stream));
+                SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+            } else if (opt.synchronize) {
+                SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+            }
+            return;
+        }
+        if (classify_pointer(path).on_device || classify_pointer(correction).on_device)
+            throw std::invalid_argument("signature_cuda: path, correction and out must all be device pointers or all host pointers");
+        // host buffers: one staged round trip (corrected signatures are small next to the headline workloads)
+        DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
+        DeviceContext& ctx = device_context(current_device());
+        std::lock_guard<std::mutex> lock(ctx.mu);
+        cudaStream_t st = ctx.compute;
+        const uint64_t np = batch * length * dimension, no = batch * s.stride;
+        Scratch buf((np + no + corr_elems) * sizeof(T), st);
+        T* dp = buf.as<T>();
+        T* dout = dp + np;
+        T* dc = dout + no;
+        SIG_CUDA_CHECK(cudaMemcpyAsync(dp, path, np * sizeof(T), cudaMemcpyHostToDevice, st));
+        SIG_CUDA_CHECK(cudaMemcpyAsync(dc, correction, corr_elems * sizeof(T), cudaMemcpyHostToDevice, st));
+        CorrectionView<T> dcv = cv;
+        dcv.ptr = dc;
+        correction_forward_on_device<T>(dp, dout, s, end_time, dcv, st);
+        SIG_CUDA_CHECK(cudaMemcpyAsync(out, dout, no * sizeof(T), cudaMemcpyDeviceToHost, st));
+        SIG_CUDA_CHECK(cudaStreamSynchronize(st));
+        if (opt.nonfinite) {
+            for (uint64_t i = 0; i < no && !*opt.nonfinite; ++i)
+                if (!std::isfinite(out[i])) *opt.nonfinite = 1;
+        }
+        return;
+    }
 
     const PointerInfo pin = classify_pointer(path), pout = classify_pointer(out);
     const bool host_call = !pout.on_device;
@@ -244,9 +288,10 @@ template <typename T>
 void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig, uint64_t batch,
                         uint64_t dimension, uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
                         T end_time, bool scalar_term, const T* correction, uint64_t correction_len,
-                        const CallOptions& opt) {
+                        const CallOptions& opt, uint64_t correction_batch_stride,
+                        uint64_t correction_segment_stride) {
     if (dimension == 0) throw std::invalid_argument("sig_backprop_cuda received path of dimension 0");
-    validate_correction(correction, correction_len, lead_lag, degree);
+    validate_correction(correction, correction_len, dimension, degree, lead_lag);
     if (batch == 0) return;
     const SigShape s = make_shape(batch, dimension, length, degree, time_aug, lead_lag, scalar_term);
     if (length == 0) return;
@@ -254,6 +299,45 @@ void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig
     const bool needs_sig = !(s.len <= 1 || s.degree == 0) && s.stride != 0;
     if (needs_sig && (sig == nullptr || sig_derivs == nullptr))
         throw std::invalid_argument("sig_backprop_cuda received a null pointer");
+    if (correction_len != 0 && s.len > 1) {
+        // reverse sweep through exp(increment + correction): siglib/cusig/cu_signature.cu:2936-2966
+        const CorrectionView<T> cv{correction, correction_len, correction_batch_stride, correction_segment_stride};
+        const uint64_t corr_elems = corrected_elems(cv, batch, s.len - 1);
+        const PointerInfo po = classify_pointer(out);
+        const bool others_on_device = classify_pointer(path).on_device && classify_pointer(sig).on_device &&
+                                      classify_pointer(sig_derivs).on_device && classify_pointer(correction).on_device;
+        const bool others_on_host = !classify_pointer(path).on_device && !classify_pointer(sig).on_device &&
+                                    !classify_pointer(sig_derivs).on_device && !classify_pointer(correction).on_device;
+        if (po.on_device ? !others_on_device : !others_on_host)
+            throw std::invalid_argument("sig_backprop_cuda: all buffers must be device pointers or all host pointers");
+        if (po.on_device) {
+            DeviceGuard guard(po.device);
+            correction_backward_on_device<T>(path, out, sig_derivs, sig, s, end_time, cv, opt.stream);
+            if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+            return;
+        }
+        DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
+        DeviceContext& ctx = device_context(current_device());
+        std::lock_guard<std::mutex> lock(ctx.mu);
+        cudaStream_t st = ctx.compute;
+        const uint64_t np = batch * length * dimension, ns = batch * s.stride;
+        Scratch buf((2 * np + 2 * ns + corr_elems) * sizeof(T), st);
+        T* dp = buf.as<T>();
+        T* dout = dp + np;
+        T* dg = dout + np;
+        T* dsig = dg + ns;
+        T* dc = dsig + ns;
+        SIG_CUDA_CHECK(cudaMemcpyAsync(dp, path, np * sizeof(T), cudaMemcpyHostToDevice, st));
+        SIG_CUDA_CHECK(cudaMemcpyAsync(dg, sig_derivs, ns * sizeof(T), cudaMemcpyHostToDevice, st));
+        SIG_CUDA_CHECK(cudaMemcpyAsync(dsig, sig, ns * sizeof(T), cudaMemcpyHostToDevice, st));
+        SIG_CUDA_CHECK(cudaMemcpyAsync(dc, correction, corr_elems * sizeof(T), cudaMemcpyHostToDevice, st));
+        CorrectionView<T> dcv = cv;
+        dcv.ptr = dc;
+        correction_backward_on_device<T>(dp, dout, dg, dsig, s, end_time, dcv, st);
+        SIG_CUDA_CHECK(cudaMemcpyAsync(out, dout, np * sizeof(T), cudaMemcpyDeviceToHost, st));
+        SIG_CUDA_CHECK(cudaStreamSynchronize(st));
+        return;
+    }
 
     const PointerInfo pout = classify_pointer(out);
     if (pout.on_device) {
@@ -369,9 +453,10 @@ void sig_combine_backprop_entry(const T* deriv, T* sig1_deriv, T* sig2_deriv, co
     template void forward_on_device<T>(const T*, T*, const SigShape&, T, cudaStream_t);                   \
     template void backward_on_device<T>(const T*, T*, const T*, const T*, const SigShape&, T, cudaStream_t); \
     template void signature_entry<T>(const T*, T*, uint64_t, uint64_t, uint64_t, uint64_t, bool, bool, T, bool, \
-                                     bool, const T*, uint64_t, const CallOptions&);                       \
+                                     bool, const T*, uint64_t, const CallOptions&, uint64_t, uint64_t);   \
     template void sig_backprop_entry<T>(const T*, T*, const T*, const T*, uint64_t, uint64_t, uint64_t, uint64_t, \
-                                        bool, bool, T, bool, const T*, uint64_t, const CallOptions&);
+                                        bool, bool, T, bool, const T*, uint64_t, const CallOptions&, uint64_t,    \
+                                        uint64_t);
 INSTANTIATE(float)
 INSTANTIATE(double)
 #undef INSTANTIATE

@@ -26,13 +26,15 @@ void backward_on_device(const T* path, T* out, const T* sig_derivs, const T* sig
 template <typename T>
 void signature_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, uint64_t length,
                      uint64_t degree, bool time_aug, bool lead_lag, T end_time, bool horner,
-                     bool scalar_term, const T* correction, uint64_t correction_len, const CallOptions& opt);
+                     bool scalar_term, const T* correction, uint64_t correction_len, const CallOptions& opt,
+                     uint64_t correction_batch_stride = 0, uint64_t correction_segment_stride = 0);
 
 template <typename T>
 void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig, uint64_t batch,
                         uint64_t dimension, uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
                         T end_time, bool scalar_term, const T* correction, uint64_t correction_len,
-                        const CallOptions& opt);
+                        const CallOptions& opt, uint64_t correction_batch_stride = 0,
+                        uint64_t correction_segment_stride = 0);
 
 // out = sig1 (x) sig2 (Chen's identity) for batches of signatures of a `dimension`-channel path.
 template <typename T>

@@ -1,0 +1,636 @@
+// Tensor-algebra operations around the signature kernels, for sm_100a:
+//   * signatures whose segment signatures are exp(increment + correction)  (forward and backward),
+//   * linear signatures, sig_join and its adjoints,
+//   * the standalone time-augmentation / lead-lag path transform and its adjoint.
+//
+// These follow the per-coefficient formulation of algebra_math.h: every phase of an algorithm
+// assigns each output coefficient to exactly one thread, which reads only buffers finished in an
+// earlier phase, so the only synchronisation is a CTA barrier (or a kernel boundary) between phases.
+// The corrected signature runs one CTA per path, sequentially over the segments, with its working
+// set (a dozen signature-sized vectors per path) in a scratch buffer that stays in L2.
+#include <algorithm>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "algebra.h"
+#include "algebra_math.h"
+#include "increments.cuh"
+#include "kernels.h"
+#include "runtime.h"
+
+namespace sigb200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+unsigned grid_1d(uint64_t work, int threads) {
+    const uint64_t blocks = (work + threads - 1) / threads;
+    if (blocks == 0) return 1;
+    if (blocks > 0x7fffffffull) throw std::invalid_argument("problem too large for one kernel launch");
+    return static_cast<unsigned>(blocks);
+}
+
+Levels checked_levels(uint64_t dim, uint64_t degree, const char* who) {
+    if (degree > kAlgebraMaxDegree)
+        throw std::invalid_argument(std::string(who) + ": degree above 64 is not supported");
+    return make_levels(dim, degree);
+}
+
+void check_launch(const char* what) {
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
+}
+
+// ----- linear signature and its adjoint ------------------------------------------------------
+
+// out points at the level-1 coefficient of path 0; one thread per coefficient of the batch.
+template <typename T>
+__global__ void linear_sig_kernel(const T* __restrict__ disp, T* __restrict__ out, uint64_t out_stride, Levels lv,
+                                  uint64_t batch, bool write_scalar) {
+    const uint64_t S = lv.total();
+    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= batch * S) return;
+    const uint64_t b = idx / S, j = idx - b * S;
+    const uint32_t t = lv.level_of(j);
+    out[b * out_stride + j] = linear_sig_coeff(disp + b * lv.dim, lv, t, j - lv.off[t]);
+    if (write_scalar && j == 0) out[b * out_stride - 1] = T(1);
+}
+
+// d_disp[b][i] = sum over coefficients of dL[b] * d(linear signature)/d v_i.  One CTA per path;
+// partial sums meet in shared memory (acc, dim values) when it fits, else directly in d_disp,
+// which the caller has zeroed.
+template <typename T>
+__global__ void linear_sig_adjoint_kernel(const T* __restrict__ disp, const T* __restrict__ dL, uint64_t dl_stride,
+                                          T* __restrict__ d_disp, Levels lv, bool use_shared) {
+    extern __shared__ unsigned char smem_raw[];
+    T* acc = reinterpret_cast<T*>(smem_raw);
+    const uint64_t b = blockIdx.x;
+    const T* v = disp + b * lv.dim;
+    const T* g = dL + b * dl_stride;
+    T* target = use_shared ? acc : d_disp + b * lv.dim;
+    if (use_shared) {
+        for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) acc[i] = T(0);
+        __syncthreads();
+    }
+    const uint64_t S = lv.total();
+    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+        const uint32_t t = lv.level_of(j);
+        linear_sig_adjoint_terms(v, g[j], lv, t, j - lv.off[t],
+                                 [&](uint64_t letter, T value) { atomicAdd(&target[letter], value); });
+    }
+    if (use_shared) {
+        __syncthreads();
+        for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) d_disp[b * lv.dim + i] = acc[i];
+    }
+}
+
+template <typename T>
+void launch_linear_sig(const T* disp, T* out_level1, uint64_t out_stride, const Levels& lv, uint64_t batch,
+                       bool write_scalar, cudaStream_t stream) {
+    if (lv.degree == 0 || batch == 0) return;
+    linear_sig_kernel<T><<<grid_1d(batch * lv.total(), kThreads), kThreads, 0, stream>>>(disp, out_level1, out_stride,
+                                                                                        lv, batch, write_scalar);
+    check_launch("linear_sig kernel");
+}
+
+template <typename T>
+void launch_linear_sig_adjoint(const T* disp, const T* dL_level1, uint64_t dl_stride, T* d_disp, const Levels& lv,
+                               uint64_t batch, cudaStream_t stream) {
+    if (batch == 0) return;
+    if (batch > 0x7fffffffull) throw std::invalid_argument("batch too large for one kernel launch");
+    const size_t smem = lv.dim * sizeof(T);
+    const bool use_shared = smem <= 32 * 1024;
+    if (!use_shared) SIG_CUDA_CHECK(cudaMemsetAsync(d_disp, 0, batch * lv.dim * sizeof(T), stream));
+    linear_sig_adjoint_kernel<T><<<static_cast<unsigned>(batch), kThreads, use_shared ? smem : 0, stream>>>(
+        disp, dL_level1, dl_stride, d_disp, lv, use_shared);
+    check_launch("linear_sig adjoint kernel");
+}
+
+// ----- corrected signature: one CTA per path --------------------------------------------------
+
+template <typename T>
+struct CorrectionArgs {
+    const T* ptr;
+    uint64_t len, batch_stride, segment_stride;
+    uint64_t data_dim;
+};
+
+// X <- increment of augmented step `step` on level 1, the correction scattered from data-dimension
+// words to augmented words on levels >= 2, zero elsewhere.  Ends with a CTA barrier.
+template <typename T>
+__device__ void build_segment_log(T* X, const PathView<T>& pv, const T* x, int step, const CorrectionArgs<T>& c,
+                                  const T* corr_path, const Levels& lv) {
+    const uint64_t S = lv.total();
+    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x)
+        X[j] = j < lv.dim ? pv.increment(x, step, static_cast<int>(j)) : T(0);
+    __syncthreads();
+    const T* seg = corr_path + uint64_t(step) * c.segment_stride;
+    uint64_t offset = 0, level_size = c.data_dim;
+    for (uint32_t level = 2; level <= lv.degree; ++level) {
+        level_size *= c.data_dim;
+        if (offset + level_size > c.len) break;
+        for (uint64_t w = threadIdx.x; w < level_size; w += blockDim.x) {
+            const T value = seg[offset + w];
+            if (value == T(0)) continue;
+            uint64_t rest = w, aug = 0, pw = level_size / c.data_dim;
+            for (uint32_t pos = 0; pos < level; ++pos) {
+                const uint64_t label = rest / pw;
+                rest -= label * pw;
+                if (pos + 1 < level) pw /= c.data_dim;
+                aug = aug * lv.dim + label;
+            }
+            X[lv.off[level] + aug] = value;
+        }
+        offset += level_size;
+    }
+    __syncthreads();
+}
+
+// E <- exp(X) (and Einv <- exp(-X) when asked), keeping the powers P_2..P_N in `powers`
+// (N-1 vectors) when keep_powers, else ping-ponging inside the first two.  Ends with a barrier.
+template <typename T>
+__device__ void segment_exp(const T* X, T* E, T* Einv, T* powers, bool keep_powers, const Levels& lv) {
+    const uint64_t S = lv.total();
+    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+        E[j] = X[j];
+        if (Einv) Einv[j] = -X[j];
+    }
+    const T* prev = X;
+    for (uint32_t n = 2; n <= lv.degree; ++n) {
+        T* cur = powers + (keep_powers ? uint64_t(n - 2) : uint64_t(n & 1)) * S;
+        for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+            const uint32_t t = lv.level_of(j);
+            const T val = exp_power_coeff(X, prev, lv, n, t, j - lv.off[t]);
+            cur[j] = val;
+            E[j] += val;  // coefficient j belongs to this thread in every round
+            if (Einv) Einv[j] += (n & 1) ? -val : val;
+        }
+        __syncthreads();
+        prev = cur;
+    }
+    __syncthreads();
+}
+
+template <typename T>
+__global__ void correction_forward_kernel(PathView<T> pv, CorrectionArgs<T> c, T* __restrict__ out,
+                                          uint64_t out_stride, bool scalar_term, T* __restrict__ scratch, Levels lv,
+                                          uint64_t batch_offset) {
+    const uint64_t S = lv.total();
+    const uint64_t b = batch_offset + blockIdx.x;
+    const T* x = pv.base + b * pv.path_stride;
+    const T* corr_path = c.ptr + b * c.batch_stride;
+    T* ws = scratch + uint64_t(blockIdx.x) * 6 * S;
+    T *X = ws, *powers = ws + S, *E = ws + 3 * S, *cur = ws + 4 * S, *nxt = ws + 5 * S;
+
+    for (int step = 0; step < pv.steps; ++step) {
+        build_segment_log(X, pv, x, step, c, corr_path, lv);
+        segment_exp<T>(X, E, nullptr, powers, false, lv);
+        for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+            if (step == 0) {
+                nxt[j] = E[j];
+            } else {
+                const uint32_t t = lv.level_of(j);
+                nxt[j] = product_coeff(cur, E, lv, t, j - lv.off[t]);
+            }
+        }
+        __syncthreads();
+        T* tmp = cur; cur = nxt; nxt = tmp;
+    }
+    T* o = out + b * out_stride;
+    if (scalar_term) {
+        if (threadIdx.x == 0) o[0] = T(1);
+        ++o;
+    }
+    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) o[j] = cur[j];
+}
+
+// Buffers per path: X, P_2..P_N (at least 2), E, Einv, S x2, dS x2, dE, dP x2.
+__host__ __device__ inline uint64_t backward_vectors(uint32_t degree) {
+    return 10 + (degree > 3 ? degree - 1 : 2);
+}
+
+template <typename T>
+__global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, const T* __restrict__ sig,
+                                           const T* __restrict__ sig_derivs, uint64_t sig_stride, bool scalar_term,
+                                           T* __restrict__ out, T* __restrict__ scratch, Levels lv,
+                                           uint64_t batch_offset) {
+    extern __shared__ unsigned char smem_raw[];
+    T* g = reinterpret_cast<T*>(smem_raw);  // gradient w.r.t. this step's increment
+    T* g_next = g + lv.dim;                 // the same for the step after it
+    const uint64_t S = lv.total();
+    const uint32_t N = lv.degree;
+    const uint64_t b = batch_offset + blockIdx.x;
+    const T* x = pv.base + b * pv.path_stride;
+    const T* corr_path = c.ptr + b * c.batch_stride;
+    const uint64_t npow = N > 3 ? N - 1 : 2;
+    T* ws = scratch + uint64_t(blockIdx.x) * backward_vectors(N) * S;
+    T* X = ws;
+    T* powers = ws + S;                      // P_2 .. P_N
+    T* E = powers + npow * S;
+    T* Einv = E + S;
+    T* Scur = Einv + S;
+    T* Snxt = Scur + S;
+    T* dScur = Snxt + S;
+    T* dSnxt = dScur + S;
+    T* dE = dSnxt + S;
+    T* dPa = dE + S;
+    T* dPb = dPa + S;
+    T* o = out + b * pv.path_stride;
+    const uint64_t shift = scalar_term ? 1 : 0;
+
+    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+        Scur[j] = sig[b * sig_stride + shift + j];
+        dScur[j] = sig_derivs[b * sig_stride + shift + j];
+    }
+    for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) g_next[i] = T(0);
+    __syncthreads();
+
+    for (int step = pv.steps - 1; step >= 0; --step) {
+        for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) g[i] = T(0);
+        build_segment_log(X, pv, x, step, c, corr_path, lv);
+        segment_exp<T>(X, E, Einv, powers, true, lv);
+
+        // signature of the path up to the start of this segment
+        for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+            const uint32_t t = lv.level_of(j);
+            Snxt[j] = product_coeff(Scur, Einv, lv, t, j - lv.off[t]);
+        }
+        __syncthreads();
+        { T* tmp = Scur; Scur = Snxt; Snxt = tmp; }
+
+        // split the adjoint of (Scur (x) E) between its factors
+        for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+            const uint32_t t = lv.level_of(j);
+            const uint64_t w = j - lv.off[t];
+            dE[j] = right_adjoint_coeff(dScur, Scur, lv, t, w);
+            dSnxt[j] = left_adjoint_coeff(dScur, E, lv, t, w);
+        }
+        __syncthreads();
+        { T* tmp = dScur; dScur = dSnxt; dSnxt = tmp; }
+
+        // adjoint of exp, keeping only the level-1 part of the result
+        const T* dPn = nullptr;
+        T* dPprev = dPa;
+        for (uint32_t n = N; n >= 2; --n) {
+            const T* prev = n == 2 ? X : powers + uint64_t(n - 3) * S;  // P_{n-1}
+            for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+                const uint32_t t = lv.level_of(j);
+                const uint64_t w = j - lv.off[t];
+                dPprev[j] = exp_adjoint_prev_coeff(dE, dPn, X, lv, n, t, w);
+                if (t >= n) {
+                    uint64_t letter;
+                    const T term = exp_adjoint_level1_term(dE, dPn, prev, lv, n, t, w, &letter);
+                    atomicAdd(&g[letter], term);
+                }
+            }
+            __syncthreads();
+            dPn = dPprev;
+            dPprev = dPprev == dPa ? dPb : dPa;
+        }
+        for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) {
+            const T gi = g[i] + dE[i] + (dPn ? dPn[i] : T(0));
+            if (i < uint64_t(pv.d)) o[uint64_t(step + 1) * pv.d + i] = gi - g_next[i];
+            g_next[i] = gi;
+        }
+        __syncthreads();
+    }
+    for (uint64_t i = threadIdx.x; i < uint64_t(pv.d); i += blockDim.x) o[i] = -g_next[i];
+}
+
+constexpr uint64_t kScratchBudget = 1ull << 30;  // bytes of per-path working vectors held at once
+
+template <typename T>
+CorrectionArgs<T> make_args(const CorrectionView<T>& c, uint64_t data_dim) {
+    return CorrectionArgs<T>{c.ptr, c.len, c.batch_stride, c.segment_stride, data_dim};
+}
+
+// ----- path transform --------------------------------------------------------------------------
+
+template <typename T>
+__global__ void transform_path_kernel(const T* __restrict__ in, T* __restrict__ out, uint64_t batch, uint64_t d,
+                                      uint64_t L, uint64_t dim, uint64_t len, bool time_aug, bool lead_lag, T dt) {
+    const uint64_t per_path = len * dim;
+    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= batch * per_path) return;
+    const uint64_t b = idx / per_path, r = idx - b * per_path;
+    const uint64_t p = r / dim, ch = r - p * dim;
+    const T* x = in + b * L * d;
+    T value;
+    if (time_aug && ch == dim - 1) {
+        value = static_cast<T>(p) * dt;
+    } else if (lead_lag) {
+        const uint64_t m = p >> 1, odd = p & 1;
+        value = ch < d ? x[m * d + ch] : x[(m + odd) * d + (ch - d)];
+    } else {
+        value = x[p * d + ch];
+    }
+    out[idx] = value;
+}
+
+template <typename T>
+__global__ void transform_path_backprop_kernel(const T* __restrict__ derivs, T* __restrict__ out, uint64_t batch,
+                                               uint64_t d, uint64_t L, uint64_t dim, uint64_t len, bool lead_lag) {
+    const uint64_t per_path = L * d;
+    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= batch * per_path) return;
+    const uint64_t b = idx / per_path, r = idx - b * per_path;
+    const uint64_t k = r / d, j = r - k * d;
+    const T* g = derivs + b * len * dim;
+    T sum;
+    if (lead_lag) {
+        sum = g[(2 * k) * dim + j];
+        sum += g[(2 * k) * dim + d + j];
+        if (k + 1 < L) sum += g[(2 * k + 1) * dim + j];
+        if (k >= 1) sum += g[(2 * k - 1) * dim + d + j];
+    } else {
+        sum = g[k * dim + j];
+    }
+    out[idx] = sum;
+}
+
+// Runs `body(device pointers, stream)` with every host operand staged through one scratch block:
+// inputs copied in, outputs copied back, all on the context's compute stream.
+struct StagedOperand {
+    const void* host_in;  // nullptr for pure outputs
+    void* host_out;       // nullptr for pure inputs
+    size_t bytes;
+};
+
+template <typename Body>
+void run_staged(std::vector<StagedOperand> ops, int device, Body body) {
+    DeviceGuard guard(device >= 0 ? device : current_device());
+    DeviceContext& ctx = device_context(current_device());
+    std::lock_guard<std::mutex> lock(ctx.mu);
+    cudaStream_t st = ctx.compute;
+    size_t total = 0;
+    std::vector<size_t> offs;
+    for (auto& op : ops) {
+        offs.push_back(total);
+        total += (op.bytes + 255) / 256 * 256;
+    }
+    Scratch buf(std::max<size_t>(total, 256), st);
+    std::vector<void*> dev;
+    for (size_t i = 0; i < ops.size(); ++i) {
+        void* p = static_cast<unsigned char*>(buf.get()) + offs[i];
+        dev.push_back(p);
+        if (ops[i].host_in && ops[i].bytes)
+            SIG_CUDA_CHECK(cudaMemcpyAsync(p, ops[i].host_in, ops[i].bytes, cudaMemcpyHostToDevice, st));
+    }
+    body(dev, st);
+    for (size_t i = 0; i < ops.size(); ++i)
+        if (ops[i].host_out && ops[i].bytes)
+            SIG_CUDA_CHECK(cudaMemcpyAsync(ops[i].host_out, dev[i], ops[i].bytes, cudaMemcpyDeviceToHost, st));
+    SIG_CUDA_CHECK(cudaStreamSynchronize(st));
+}
+
+// true: all device, false: all host; throws on a mix
+bool all_on_device(std::initializer_list<const void*> ptrs, const char* who, int* device) {
+    int on = 0, off = 0;
+    for (const void* p : ptrs) {
+        if (!p) continue;
+        const PointerInfo info = classify_pointer(p);
+        if (info.on_device) { ++on; *device = info.device; } else ++off;
+    }
+    if (on && off)
+        throw std::invalid_argument(std::string(who) + ": all buffers must be device pointers or all host pointers");
+    return on > 0;
+}
+
+}  // namespace
+
+void validate_correction(const void* correction, uint64_t correction_len, uint64_t dimension, uint64_t degree,
+                         bool lead_lag) {
+    if (correction == nullptr && correction_len != 0)
+        throw std::invalid_argument("correction pointer is null but correction_len is nonzero");
+    if (lead_lag && correction_len != 0) throw std::invalid_argument("correction cannot be used with lead_lag=true");
+    if (correction_len == 0) return;
+    if (degree < 2) throw std::invalid_argument("correction must be empty when degree < 2");
+    uint64_t offset = 0, level_size = dimension;
+    for (uint64_t level = 2; level <= degree; ++level) {
+        if (level_size > correction_len) break;  // also keeps the product below from overflowing
+        level_size *= dimension;
+        offset += level_size;
+        if (offset == correction_len) return;
+        if (offset > correction_len) break;
+    }
+    throw std::invalid_argument("correction length must be a prefix of tensor levels 2..degree");
+}
+
+template <typename T>
+void correction_forward_on_device(const T* path, T* out, const SigShape& s, T end_time, const CorrectionView<T>& c,
+                                  cudaStream_t stream) {
+    const Levels lv = checked_levels(s.dim, s.degree, "signature_cuda (correction)");
+    const PathView<T> pv = make_path_view<T>(path, s.data_dim, s.data_len, s.time_aug, false, end_time);
+    const uint64_t per_path = 6 * lv.total() * sizeof(T);
+    const uint64_t chunk = std::max<uint64_t>(1, std::min<uint64_t>(std::min<uint64_t>(s.batch, 0x7fffffffull),
+                                                                   kScratchBudget / std::max<uint64_t>(per_path, 1)));
+    Scratch ws(chunk * per_path, stream);
+    for (uint64_t b0 = 0; b0 < s.batch; b0 += chunk) {
+        const uint64_t count = std::min(chunk, s.batch - b0);
+        correction_forward_kernel<T><<<static_cast<unsigned>(count), kThreads, 0, stream>>>(
+            pv, make_args(c, s.data_dim), out, s.stride, s.scalar_term, ws.as<T>(), lv, b0);
+        check_launch("corrected signature kernel");
+    }
+}
+
+template <typename T>
+void correction_backward_on_device(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
+                                   T end_time, const CorrectionView<T>& c, cudaStream_t stream) {
+    const Levels lv = checked_levels(s.dim, s.degree, "sig_backprop_cuda (correction)");
+    const PathView<T> pv = make_path_view<T>(path, s.data_dim, s.data_len, s.time_aug, false, end_time);
+    const size_t smem = 2 * s.dim * sizeof(T);
+    if (smem > 48 * 1024) throw std::invalid_argument("sig_backprop_cuda (correction): dimension too large");
+    const uint64_t per_path = backward_vectors(lv.degree) * lv.total() * sizeof(T);
+    const uint64_t chunk = std::max<uint64_t>(1, std::min<uint64_t>(std::min<uint64_t>(s.batch, 0x7fffffffull),
+                                                                   kScratchBudget / std::max<uint64_t>(per_path, 1)));
+    Scratch ws(chunk * per_path, stream);
+    for (uint64_t b0 = 0; b0 < s.batch; b0 += chunk) {
+        const uint64_t count = std::min(chunk, s.batch - b0);
+        correction_backward_kernel<T><<<static_cast<unsigned>(count), kThreads, smem, stream>>>(
+            pv, make_args(c, s.data_dim), sig, sig_derivs, s.stride, s.scalar_term, out, ws.as<T>(), lv, b0);
+        check_launch("corrected signature backward kernel");
+    }
+}
+
+template <typename T>
+void linear_sig_entry(const T* displacement, T* out, uint64_t batch, uint64_t dimension, uint64_t degree,
+                      bool scalar_term, const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("linear_sig_cuda received dimension 0");
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, dimension, 2, degree, false, false, scalar_term);
+    if (s.stride == 0) return;
+    if (!displacement || !out) throw std::invalid_argument("linear_sig_cuda received a null pointer");
+    const Levels lv = checked_levels(dimension, degree, "linear_sig_cuda");
+    const uint64_t shift = scalar_term ? 1 : 0;
+    auto run = [&](const T* v, T* o, cudaStream_t st) {
+        if (degree == 0) launch_fill<T>(o, batch * s.stride, T(1), st);
+        else launch_linear_sig<T>(v, o + shift, s.stride, lv, batch, scalar_term, st);
+    };
+    int device = -1;
+    if (all_on_device({displacement, out}, "linear_sig_cuda", &device)) {
+        DeviceGuard guard(device);
+        run(displacement, out, opt.stream);
+        if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        return;
+    }
+    run_staged({{displacement, nullptr, batch * dimension * sizeof(T)}, {nullptr, out, batch * s.stride * sizeof(T)}},
+               opt.device, [&](const std::vector<void*>& d, cudaStream_t st) {
+                   run(static_cast<const T*>(d[0]), static_cast<T*>(d[1]), st);
+               });
+}
+
+template <typename T>
+void sig_join_entry(const T* sig, const T* displacement, T* out, uint64_t batch, uint64_t dimension,
+                    uint64_t degree, bool prepend, bool scalar_term, const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("sig_join_cuda received dimension 0");
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, dimension, 2, degree, false, false, scalar_term);
+    if (s.stride == 0) return;
+    if (!sig || !displacement || !out) throw std::invalid_argument("sig_join_cuda received a null pointer");
+    const Levels lv = checked_levels(dimension, degree, "sig_join_cuda");
+    const uint64_t shift = scalar_term ? 1 : 0;
+    const uint64_t S = s.full_len - 1;
+    auto run = [&](const T* a, const T* v, T* o, cudaStream_t st) {
+        if (degree == 0) { launch_fill<T>(o, batch * s.stride, T(1), st); return; }
+        Scratch lin(batch * S * sizeof(T), st);
+        launch_linear_sig<T>(v, lin.as<T>(), S, lv, batch, false, st);
+        if (prepend) launch_chen_product<T>(lin.as<T>(), S, a + shift, s.stride, o + shift, s.stride, s, st, scalar_term);
+        else launch_chen_product<T>(a + shift, s.stride, lin.as<T>(), S, o + shift, s.stride, s, st, scalar_term);
+    };
+    int device = -1;
+    if (all_on_device({sig, displacement, out}, "sig_join_cuda", &device)) {
+        DeviceGuard guard(device);
+        run(sig, displacement, out, opt.stream);
+        if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        return;
+    }
+    const size_t nb = batch * s.stride * sizeof(T);
+    run_staged({{sig, nullptr, nb}, {displacement, nullptr, batch * dimension * sizeof(T)}, {nullptr, out, nb}},
+               opt.device, [&](const std::vector<void*>& d, cudaStream_t st) {
+                   run(static_cast<const T*>(d[0]), static_cast<const T*>(d[1]), static_cast<T*>(d[2]), st);
+               });
+}
+
+template <typename T>
+void sig_join_backprop_entry(const T* d_out, T* d_sig, T* d_displacement, const T* sig, const T* displacement,
+                             uint64_t batch, uint64_t dimension, uint64_t degree, bool prepend, bool scalar_term,
+                             const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("sig_join_backprop_cuda received dimension 0");
+    if (batch == 0) return;
+    const SigShape s = make_shape(batch, dimension, 2, degree, false, false, scalar_term);
+    if (!d_displacement || !displacement) throw std::invalid_argument("sig_join_backprop_cuda received a null pointer");
+    if (s.stride != 0 && (!d_out || !d_sig || !sig))
+        throw std::invalid_argument("sig_join_backprop_cuda received a null pointer");
+    const Levels lv = checked_levels(dimension, degree, "sig_join_backprop_cuda");
+    const uint64_t shift = scalar_term ? 1 : 0;
+    const uint64_t S = s.full_len - 1;
+    auto run = [&](const T* g, T* ds, T* dv, const T* a, const T* v, cudaStream_t st) {
+        if (scalar_term) SIG_CUDA_CHECK(cudaMemsetAsync(ds, 0, batch * s.stride * sizeof(T), st));  // scalar slots
+        if (degree == 0) {
+            SIG_CUDA_CHECK(cudaMemsetAsync(dv, 0, batch * dimension * sizeof(T), st));
+            return;
+        }
+        Scratch tmp(2 * batch * S * sizeof(T), st);
+        T* lin = tmp.as<T>();
+        T* dlin = lin + batch * S;
+        launch_linear_sig<T>(v, lin, S, lv, batch, false, st);
+        if (prepend) {  // out = lin (x) sig
+            launch_chen_left_adjoint<T>(g + shift, s.stride, a + shift, s.stride, dlin, S, s, st);
+            launch_chen_right_adjoint<T>(g + shift, s.stride, lin, S, ds + shift, s.stride, s, st);
+        } else {        // out = sig (x) lin
+            launch_chen_left_adjoint<T>(g + shift, s.stride, lin, S, ds + shift, s.stride, s, st);
+            launch_chen_right_adjoint<T>(g + shift, s.stride, a + shift, s.stride, dlin, S, s, st);
+        }
+        launch_linear_sig_adjoint<T>(v, dlin, S, dv, lv, batch, st);
+    };
+    int device = -1;
+    if (all_on_device({d_out, d_sig, d_displacement, sig, displacement}, "sig_join_backprop_cuda", &device)) {
+        DeviceGuard guard(device);
+        run(d_out, d_sig, d_displacement, sig, displacement, opt.stream);
+        if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        return;
+    }
+    const size_t nb = batch * s.stride * sizeof(T), vb = batch * dimension * sizeof(T);
+    run_staged({{d_out, nullptr, nb}, {nullptr, d_sig, nb}, {nullptr, d_displacement, vb}, {sig, nullptr, nb},
+                {displacement, nullptr, vb}},
+               opt.device, [&](const std::vector<void*>& d, cudaStream_t st) {
+                   run(static_cast<const T*>(d[0]), static_cast<T*>(d[1]), static_cast<T*>(d[2]),
+                       static_cast<const T*>(d[3]), static_cast<const T*>(d[4]), st);
+               });
+}
+
+template <typename T>
+void transform_path_entry(const T* data_in, T* data_out, uint64_t batch, uint64_t dimension, uint64_t length,
+                          bool time_aug, bool lead_lag, T end_time, const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("transform_path_cuda received path of dimension 0");
+    if (batch == 0 || length == 0) return;
+    if (!data_in || !data_out) throw std::invalid_argument("transform_path_cuda received a null pointer");
+    const SigShape s = make_shape(batch, dimension, length, 1, time_aug, lead_lag, false);
+    const T dt = s.len > 1 ? end_time / static_cast<T>(s.len - 1) : T(0);
+    const uint64_t n_out = checked_mul(checked_mul(batch, s.len, "transformed path"), s.dim, "transformed path");
+    auto run = [&](const T* in, T* o, cudaStream_t st) {
+        transform_path_kernel<T><<<grid_1d(n_out, kThreads), kThreads, 0, st>>>(in, o, batch, dimension, length, s.dim,
+                                                                                s.len, time_aug, lead_lag, dt);
+        check_launch("transform_path kernel");
+    };
+    int device = -1;
+    if (all_on_device({data_in, data_out}, "transform_path_cuda", &device)) {
+        DeviceGuard guard(device);
+        run(data_in, data_out, opt.stream);
+        if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        return;
+    }
+    run_staged({{data_in, nullptr, batch * length * dimension * sizeof(T)}, {nullptr, data_out, n_out * sizeof(T)}},
+               opt.device, [&](const std::vector<void*>& d, cudaStream_t st) {
+                   run(static_cast<const T*>(d[0]), static_cast<T*>(d[1]), st);
+               });
+}
+
+template <typename T>
+void transform_path_backprop_entry(const T* derivs, T* data_out, uint64_t batch, uint64_t dimension, uint64_t length,
+                                   bool time_aug, bool lead_lag, T, const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("transform_path_backprop_cuda received path of dimension 0");
+    if (batch == 0 || length == 0) return;
+    if (!derivs || !data_out) throw std::invalid_argument("transform_path_backprop_cuda received a null pointer");
+    const SigShape s = make_shape(batch, dimension, length, 1, time_aug, lead_lag, false);
+    const uint64_t n_in = checked_mul(checked_mul(batch, s.len, "transformed path"), s.dim, "transformed path");
+    const uint64_t n_out = batch * length * dimension;
+    auto run = [&](const T* g, T* o, cudaStream_t st) {
+        transform_path_backprop_kernel<T><<<grid_1d(n_out, kThreads), kThreads, 0, st>>>(g, o, batch, dimension, length,
+                                                                                        s.dim, s.len, lead_lag);
+        check_launch("transform_path_backprop kernel");
+    };
+    int device = -1;
+    if (all_on_device({derivs, data_out}, "transform_path_backprop_cuda", &device)) {
+        DeviceGuard guard(device);
+        run(derivs, data_out, opt.stream);
+        if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+        return;
+    }
+    run_staged({{derivs, nullptr, n_in * sizeof(T)}, {nullptr, data_out, n_out * sizeof(T)}}, opt.device,
+               [&](const std::vector<void*>& d, cudaStream_t st) {
+                   run(static_cast<const T*>(d[0]), static_cast<T*>(d[1]), st);
+               });
+}
+
+#define INSTANTIATE(T)                                                                                              \
+    template void correction_forward_on_device<T>(const T*, T*, const SigShape&, T, const CorrectionView<T>&,       \
+                                                  cudaStream_t);                                                    \
+    template void correction_backward_on_device<T>(const T*, T*, const T*, const T*, const SigShape&, T,            \
+                                                   const CorrectionView<T>&, cudaStream_t);                         \
+    template void linear_sig_entry<T>(const T*, T*, uint64_t, uint64_t, uint64_t, bool, const CallOptions&);        \
+    template void sig_join_entry<T>(const T*, const T*, T*, uint64_t, uint64_t, uint64_t, bool, bool,               \
+                                    const CallOptions&);                                                            \
+    template void sig_join_backprop_entry<T>(const T*, T*, T*, const T*, const T*, uint64_t, uint64_t, uint64_t,    \
+                                             bool, bool, const CallOptions&);                                       \
+    template void transform_path_entry<T>(const T*, T*, uint64_t, uint64_t, uint64_t, bool, bool, T,                \
+                                          const CallOptions&);                                                      \
+    template void transform_path_backprop_entry<T>(const T*, T*, uint64_t, uint64_t, uint64_t, bool, bool, T,       \
+                                                   const CallOptions&);
+INSTANTIATE(float)
+INSTANTIATE(double)
+#undef INSTANTIATE
+
+}  // namespace sigb200

@@ -98,12 +98,61 @@ class Output:
         self.pointer = _pointer(self.array, like.dtype)
 
 
-def check_correction_unsupported(correction):
-    """``correction`` is part of the reference's signature (pysiglib/sig.py:128-139); this
-    build accepts only None or an empty array."""
-    if correction is None:
-        return
-    check_type(correction, "correction", (np.ndarray, torch.Tensor))
-    size = correction.size if isinstance(correction, np.ndarray) else correction.numel()
-    if size != 0:
-        raise NotImplementedError("per-segment corrections are not implemented in pysiglib_b200")
+class CorrectionInput:
+    """Per-segment correction levels of ``sig`` / ``sig_backprop`` (reference:
+    ``pysiglib/data_handlers.py:191-260``).  Accepted shapes: ``(C,)`` one correction for every
+    segment, ``(L-1, C)`` one per segment shared by the batch, ``batch_shape + (L-1, C)``; ``C``
+    must cover tensor levels ``2..k`` of the data dimension for some ``k <= degree``."""
+
+    def __init__(self, correction, path, degree):
+        self.array = None
+        self.length = 0
+        self.pointer = None
+        self.batch_stride = 0
+        self.segment_stride = 0
+        if correction is None:
+            return
+        check_type(correction, "correction", (np.ndarray, torch.Tensor))
+        if isinstance(correction, np.ndarray) != (path.kind == "numpy"):
+            raise ValueError("correction must have the same array type as path")
+        self.array = own_contiguous(correction)
+        check_dtype(self.array, "correction")
+        kind, dtype, device = _describe(self.array)
+        if dtype != path.dtype:
+            raise ValueError("correction and path must have the same dtype")
+        if device != path.device:
+            raise ValueError("correction and path must be on the same device")
+        size = self.array.size if kind == "numpy" else self.array.numel()
+        if size == 0:
+            return
+        if path.lead_lag:
+            raise ValueError("correction cannot be used with lead_lag=True")
+        shape = tuple(self.array.shape)
+        segments = max(path.data_length - 1, 0)
+        expected = (*path.batch_shape, segments, shape[-1] if shape else 0)
+        message = ("correction shape must be (C,), (path.shape[-2] - 1, C), or " + str(expected) +
+                   " for path shape " + str(tuple(path.array.shape)))
+        if len(shape) == 0:
+            raise ValueError(message)
+        if len(shape) == 1:
+            self.length = shape[0]
+        elif len(shape) == 2 and shape[0] == segments:
+            self.length = shape[1]
+            self.segment_stride = self.length
+        else:
+            if shape != expected:
+                raise ValueError(message)
+            self.length = shape[-1]
+            self.batch_stride = segments * self.length
+            self.segment_stride = self.length
+        if degree < 2:
+            raise ValueError("correction must be empty when degree < 2")
+        offset, level_size = 0, path.data_dimension
+        for _ in range(2, degree + 1):
+            level_size *= path.data_dimension
+            offset += level_size
+            if offset >= self.length:
+                break
+        if offset != self.length:
+            raise ValueError("correction length must be a prefix of tensor levels 2..degree")
+        self.pointer = _pointer(self.array, dtype)

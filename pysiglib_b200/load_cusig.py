@@ -76,6 +76,19 @@ def _bind(lib):
         f.argtypes = (ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real, c_bool,
                       ptr, c_uint64, c_uint64, c_uint64)
         f.restype = c_int
+        f = getattr(lib, "linear_sig_cuda_" + suffix)
+        f.argtypes = (ptr, ptr, c_uint64, c_uint64, c_uint64, c_bool)
+        f.restype = c_int
+        f = getattr(lib, "sig_join_cuda_" + suffix)
+        f.argtypes = (ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_bool, c_bool)
+        f.restype = c_int
+        f = getattr(lib, "sig_join_backprop_cuda_" + suffix)
+        f.argtypes = (ptr, ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_bool, c_bool)
+        f.restype = c_int
+        for name in ("transform_path_cuda_", "transform_path_backprop_cuda_"):
+            f = getattr(lib, name + suffix)
+            f.argtypes = (ptr, ptr, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real)
+            f.restype = c_int
         # extensions
         f = getattr(lib, "sigb200_signature_" + suffix)
         f.argtypes = (ptr, ptr, c_uint64, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real, c_bool,

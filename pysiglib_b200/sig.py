@@ -10,7 +10,7 @@ import numpy as np
 import torch
 
 from . import load_cusig
-from .data_handlers import Output, PathInput, SigInput, check_correction_unsupported, check_same
+from .data_handlers import CorrectionInput, Output, PathInput, SigInput, check_same
 from .error_codes import err_msg
 from .param_checks import check_n_jobs, check_non_neg, check_type
 from .sig_length import infer_scalar_term, sig_length
@@ -54,7 +54,11 @@ def sig(
     :param end_time: final time of the time channel (``float``).
     :param horner: accepted for compatibility; the Horner scheme is always used.
     :param scalar_term: include the constant 1 of level 0 as the first entry.
-    :param correction: must be ``None`` or empty (per-segment corrections are not implemented).
+    :param correction: optional higher-level terms added to every segment's logarithm: the segment
+        from ``x_j`` to ``x_{j+1}`` contributes ``exp((x_{j+1} - x_j) + c_j)`` with ``c_j`` living on
+        tensor levels ``2..k`` (``k <= degree``) of the path's own channels.  Shape ``(C,)`` (the same
+        for every segment), ``(length - 1, C)`` or ``batch_shape + (length - 1, C)`` with
+        ``C = d^2 + .. + d^k``.  Not available with ``lead_lag``.
     :param n_jobs: accepted for compatibility (validated, otherwise ignored on the GPU).
     :return: array of the same kind, dtype and device as ``path``.
 
@@ -74,12 +78,25 @@ def sig(
     check_type(end_time, "end_time", float)
     check_type(scalar_term, "scalar_term", bool)
     check_n_jobs(n_jobs)
-    check_correction_unsupported(correction)
 
     data = PathInput(path, time_aug, lead_lag, end_time)
+    corr = CorrectionInput(correction, data, degree)
     n = sig_length(data.dimension, degree, scalar_term=scalar_term)
     result = Output(data, (n,))
     if data.batch_size == 0:
+        return result.array
+
+    if corr.length:
+        # the reference's own symbol carries the correction arguments (synchronous)
+        code = load_cusig.fn("signature_cuda", data.dtype)(
+            data.pointer, result.pointer, data.batch_size, data.data_dimension, data.data_length, degree,
+            time_aug, lead_lag, end_time, horner, scalar_term, corr.pointer, corr.length, corr.batch_stride,
+            corr.segment_stride)
+        if code:
+            raise Exception("Error in pysiglib.sig: " + err_msg(code))
+        finite = np.isfinite(result.array).all() if data.kind == "numpy" else bool(torch.isfinite(result.array).all())
+        if not finite:
+            warnings.warn(NONFINITE_WARNING, RuntimeWarning, stacklevel=2)
         return result.array
 
     bad = ctypes.c_int(0)

@@ -8,7 +8,7 @@ import numpy as np
 import torch
 
 from . import load_cusig
-from .data_handlers import Output, PathInput, SigInput, check_correction_unsupported, check_same
+from .data_handlers import CorrectionInput, Output, PathInput, SigInput, check_same
 from .error_codes import err_msg
 from .param_checks import check_n_jobs, check_non_neg, check_type
 from .sig import _current_stream
@@ -37,7 +37,8 @@ def sig_backprop(
     :param sig_derivs: ``dF/d sig``, same shape as ``sig`` (the scalar slot, if present, is ignored).
     :param degree: truncation level used for ``sig``.
     :param time_aug, lead_lag, end_time: the flags used for ``sig``.
-    :param correction: must be ``None`` or empty.
+    :param correction: the correction ``sig`` was computed with (same shapes as there); the result is
+        still the gradient with respect to the path only.
     :param n_jobs: accepted for compatibility.
     :return: ``dF/d path`` with the shape, kind, dtype and device of ``path``.
 
@@ -51,9 +52,9 @@ def sig_backprop(
     check_type(time_aug, "time_aug", bool)
     check_type(lead_lag, "lead_lag", bool)
     check_type(end_time, "end_time", float)
-    check_correction_unsupported(correction)
 
     data = PathInput(path, time_aug, lead_lag, end_time)
+    corr = CorrectionInput(correction, data, degree)
     check_type(sig, "sig", (np.ndarray, torch.Tensor))
     scalar_term = infer_scalar_term(sig, data.data_dimension, degree, time_aug=time_aug, lead_lag=lead_lag)
     n = sig_length(data.dimension, degree, scalar_term=False)
@@ -73,6 +74,15 @@ def sig_backprop(
         raise ValueError("path, sig and sig_derivs must be on the same device")
     check_n_jobs(n_jobs)
     del scalar_term  # SigInput has already stripped the scalar slot
+
+    if corr.length:
+        code = load_cusig.fn("sig_backprop_cuda", data.dtype)(
+            data.pointer, result.pointer, der_in.pointer, sig_in.pointer, data.batch_size, data.data_dimension,
+            data.data_length, degree, time_aug, lead_lag, end_time, False, corr.pointer, corr.length,
+            corr.batch_stride, corr.segment_stride)
+        if code:
+            raise Exception("Error in pysiglib.sig_backprop: " + err_msg(code))
+        return result.array
 
     code = load_cusig.fn("sigb200_sig_backprop", data.dtype)(
         data.pointer, result.pointer, der_in.pointer, sig_in.pointer, data.batch_size, data.data_dimension,

@@ -1,15 +1,21 @@
-"""Autograd bridge: ``torch_api.sig`` differentiates through the CUDA signature.
+"""Autograd bridge: the functions here differentiate through the CUDA operators.
 
-Counterpart of the reference's ``Sig`` Function and ``torch_api.sig``
-(``pysiglib/torch_api/torch_api.py:76-117``): the forward saves the path and the
-signature itself; the backward calls ``sig_backprop`` on them."""
+Counterpart of the reference's autograd Functions (``pysiglib/torch_api/torch_api.py``:
+``Sig`` 76-117, ``SigCombine`` 121-153, ``TransformPath`` 206-233, ``SigJoin`` 1182-1212): each
+forward saves what its backward needs and the backward calls the matching ``*_backprop``."""
 from typing import Union
 
 import numpy as np
 import torch
 
 from ..sig import sig as sig_forward
+from ..sig import sig_combine as sig_combine_forward
+from ..sig import sig_combine_backprop
 from ..sig_backprop import sig_backprop
+from ..sig_join import sig_join as sig_join_forward
+from ..sig_join import sig_join_backprop
+from ..transform_path import transform_path as transform_path_forward
+from ..transform_path import transform_path_backprop
 
 
 class Sig(torch.autograd.Function):
@@ -17,16 +23,18 @@ class Sig(torch.autograd.Function):
     def forward(ctx, path, correction, degree, time_aug, lead_lag, end_time, horner, scalar_term, n_jobs):
         out = sig_forward(path, degree, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time, horner=horner,
                           scalar_term=scalar_term, correction=correction, n_jobs=n_jobs)
-        ctx.save_for_backward(path, out)
+        saved_correction = path.new_empty((0,)) if correction is None else correction.detach().clone()
+        ctx.save_for_backward(path, out, saved_correction)
         ctx.args = (degree, time_aug, lead_lag, end_time, n_jobs)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
-        path, out = ctx.saved_tensors
+        path, out, saved_correction = ctx.saved_tensors
         degree, time_aug, lead_lag, end_time, n_jobs = ctx.args
+        correction = saved_correction if saved_correction.numel() != 0 else None
         grad = sig_backprop(path, out, grad_output, degree, time_aug=time_aug, lead_lag=lead_lag,
-                            end_time=end_time, n_jobs=n_jobs)
+                            end_time=end_time, correction=correction, n_jobs=n_jobs)
         return (grad,) + (None,) * 8
 
 
@@ -50,3 +58,80 @@ def sig(
 
 sig.__doc__ = sig_forward.__doc__
 signature = sig
+
+
+class SigCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, sig1, sig2, dimension, degree, time_aug, lead_lag, n_jobs):
+        out = sig_combine_forward(sig1, sig2, dimension, degree, time_aug=time_aug, lead_lag=lead_lag, n_jobs=n_jobs)
+        ctx.save_for_backward(sig1, sig2)
+        ctx.args = (dimension, degree, time_aug, lead_lag, n_jobs)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        sig1, sig2 = ctx.saved_tensors
+        dimension, degree, time_aug, lead_lag, n_jobs = ctx.args
+        g1, g2 = sig_combine_backprop(grad_output, sig1, sig2, dimension, degree, time_aug=time_aug,
+                                      lead_lag=lead_lag, n_jobs=n_jobs)
+        return g1, g2, None, None, None, None, None
+
+
+def sig_combine(sig1, sig2, dimension: int, degree: int, *, time_aug: bool = False, lead_lag: bool = False,
+                n_jobs: int = 1):
+    if not isinstance(sig1, torch.Tensor):
+        return sig_combine_forward(sig1, sig2, dimension, degree, time_aug=time_aug, lead_lag=lead_lag, n_jobs=n_jobs)
+    return SigCombine.apply(sig1, sig2, dimension, degree, time_aug, lead_lag, n_jobs)
+
+
+sig_combine.__doc__ = sig_combine_forward.__doc__
+
+
+class SigJoin(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, sig_, displacement, dimension, degree, prepend, n_jobs):
+        out = sig_join_forward(sig_, displacement, dimension, degree, prepend=bool(prepend), n_jobs=n_jobs)
+        ctx.save_for_backward(sig_, displacement)
+        ctx.args = (dimension, degree, bool(prepend), n_jobs)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        sig_, displacement = ctx.saved_tensors
+        dimension, degree, prepend, n_jobs = ctx.args
+        d_sig, d_disp = sig_join_backprop(grad_output, sig_, displacement, dimension, degree, prepend=prepend,
+                                          n_jobs=n_jobs)
+        return d_sig, d_disp, None, None, None, None
+
+
+def sig_join(sig, displacement, dimension: int, degree: int, *, prepend: bool = False, n_jobs: int = 1):
+    if not isinstance(sig, torch.Tensor):
+        return sig_join_forward(sig, displacement, dimension, degree, prepend=prepend, n_jobs=n_jobs)
+    return SigJoin.apply(sig, displacement, dimension, degree, int(prepend), n_jobs)
+
+
+sig_join.__doc__ = sig_join_forward.__doc__
+
+
+class TransformPath(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, path, time_aug, lead_lag, end_time, n_jobs):
+        out = transform_path_forward(path, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time, n_jobs=n_jobs)
+        ctx.args = (time_aug, lead_lag, end_time, n_jobs)
+        return out.clone() if out is path else out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        time_aug, lead_lag, end_time, n_jobs = ctx.args
+        grad = transform_path_backprop(grad_output, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time,
+                                       n_jobs=n_jobs)
+        return grad, None, None, None, None
+
+
+def transform_path(path, *, time_aug: bool = False, lead_lag: bool = False, end_time: float = 1., n_jobs: int = 1):
+    if not isinstance(path, torch.Tensor):
+        return transform_path_forward(path, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time, n_jobs=n_jobs)
+    return TransformPath.apply(path, time_aug, lead_lag, end_time, n_jobs)
+
+
+transform_path.__doc__ = transform_path_forward.__doc__

@@ -61,8 +61,61 @@ def test_argument_type_checks():
         psl.sig(np.zeros(5), 2)
     with pytest.raises(ValueError):
         psl.sig(np.zeros((2, 5, 0)), 2)
-    with pytest.raises(NotImplementedError):
-        psl.sig(x, 2, correction=np.ones(9))
+
+
+def test_correction_argument_contract():
+    # reference tests/test_signature.py:191-205: shape, dtype, prefix and lead_lag rules, checked before any native call
+    x = np.zeros((2, 2), dtype=np.float64)
+    with pytest.raises(ValueError, match="correction shape"):
+        psl.sig(x, 2, correction=np.array(1.0, dtype=np.float64))
+    with pytest.raises(ValueError, match="same dtype"):
+        psl.sig(x, 2, correction=np.zeros((1, 4), dtype=np.float32))
+    with pytest.raises(ValueError, match="prefix"):
+        psl.sig(x, 3, correction=np.zeros((1, 5), dtype=np.float64))
+    with pytest.raises(ValueError, match="lead_lag"):
+        psl.sig(x, 2, lead_lag=True, correction=np.zeros((1, 4), dtype=np.float64))
+    with pytest.raises(ValueError, match="degree < 2"):
+        psl.sig(x, 1, correction=np.zeros(4))
+    with pytest.raises(ValueError, match="same array type"):
+        psl.sig(x, 2, correction=torch.zeros(4, dtype=torch.float64))
+    with pytest.raises(ValueError, match="correction shape"):
+        psl.sig(np.zeros((3, 4, 2)), 2, correction=np.zeros((2, 3, 4)))
+
+
+def test_join_and_transform_argument_contract():
+    import inspect
+    assert list(inspect.signature(psl.sig_join).parameters) == ["sig", "displacement", "dimension", "degree",
+                                                                 "prepend", "n_jobs"]
+    assert list(inspect.signature(psl.sig_join_backprop).parameters) == ["d_out", "sig", "displacement", "dimension",
+                                                                          "degree", "prepend", "n_jobs"]
+    assert list(inspect.signature(psl.linear_sig).parameters) == ["displacement", "dimension", "degree",
+                                                                   "scalar_term", "n_jobs"]
+    assert list(inspect.signature(psl.transform_path).parameters) == ["path", "time_aug", "lead_lag", "end_time",
+                                                                       "n_jobs"]
+    s, v = np.zeros((3, 14)), np.zeros((3, 2))
+    with pytest.raises(ValueError, match="same batch shape"):
+        psl.sig_join(s, np.zeros((2, 2)), 2, 3)
+    with pytest.raises(ValueError, match="same dtype"):
+        psl.sig_join(s, v.astype(np.float32), 2, 3)
+    with pytest.raises(ValueError, match="incorrect length"):
+        psl.sig_join(s, np.zeros((3, 3)), 2, 3)
+    with pytest.raises(ValueError):
+        psl.sig_join(np.zeros((3, 13)), v, 2, 3)
+    with pytest.raises(TypeError):
+        psl.sig_join(s, v, 2.0, 3)
+    with pytest.raises(ValueError, match="both be numpy arrays or both torch tensors"):
+        psl.sig_join(s, torch.zeros((3, 2), dtype=torch.float64), 2, 3)
+    assert psl.sig_join(np.zeros((0, 14)), np.zeros((0, 2)), 2, 3).shape == (0, 14)
+    a, b = psl.sig_join_backprop(np.zeros((0, 14)), np.zeros((0, 14)), np.zeros((0, 2)), 2, 3)
+    assert a.shape == (0, 14) and b.shape == (0, 2)
+    assert psl.linear_sig(np.zeros((0, 2)), 2, 3).shape == (0, 14)
+    x = np.zeros((4, 5, 2))
+    assert psl.transform_path(x) is x
+    assert psl.transform_path_backprop(x) is x
+    with pytest.raises(ValueError, match="length >= 2"):
+        psl.transform_path(np.zeros((1, 2)), time_aug=True)
+    assert psl.transform_path(np.zeros((0, 5, 2)), time_aug=True, lead_lag=True).shape == (0, 9, 5)
+    assert psl.transform_path_backprop(np.zeros((0, 9, 5)), time_aug=True, lead_lag=True).shape == (0, 5, 2)
 
 
 def test_empty_batch_returns_without_native_call():
