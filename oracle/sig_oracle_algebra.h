@@ -439,6 +439,7 @@ int FN(oracle_sig_join_)(const REAL* sig, const REAL* disp, REAL* out, uint64_t 
 static void FN(linear_sig_deriv_to_increment_deriv_)(const REAL* sig, REAL* sig_deriv, REAL* inc_deriv, uint64_t dim,
                                                      uint64_t degree, const uint64_t* li) {
     for (uint64_t i = 0; i < dim; ++i) inc_deriv[i] = (REAL)0.;
+    if (degree == 0) return; /* no level 1 to read (the reference reads past its buffer here) */
     for (uint64_t level = degree; level > 1; --level) {
         const REAL one_over_level = (REAL)(1. / (double)level);
         const uint64_t level_size = li[level] - li[level - 1];

@@ -234,11 +234,12 @@ def test_error_codes_and_messages():
     out[:] = 7.0
     assert lib.signature_cuda_d(dptr, optr, 0, 2, 4, 2, False, False, 1.0, True, False, None, 0, 0, 0) == 0
     assert np.all(out == 7.0)
-    # corrections are rejected, not silently ignored
-    assert lib.signature_cuda_d(dptr, optr, 1, 2, 4, 2, False, False, 1.0, True, False, optr, 4, 0, 0) == 2
+    # a correction whose length is not a prefix of levels 2..degree is rejected (cu_signature.cu:2028-2055)
+    assert lib.signature_cuda_d(dptr, optr, 1, 2, 4, 2, False, False, 1.0, True, False, optr, 3, 0, 0) == 2
+    assert "prefix" in load_cusig.last_error_message()
     assert lib.sig_backprop_cuda_d(dptr, optr, optr, optr, 1, 0, 4, 2, False, False, 1.0, False, None, 0, 0, 0) == 2
     # symbols outside the served path exist and fail cleanly
-    assert lib.sig_join_cuda_d() == 10
+    assert lib.sig_coef_cuda_d() == 10
     assert "not part of this build" in load_cusig.last_error_message()
 
 
