@@ -181,8 +181,98 @@ def workload_config(args, cfg, world):
             "l2": "inputs larger than L2" if cfg["B"] // world * cfg["L"] * cfg["d"] * 4 > 126e6 else "L2 flushed between steps"}
 
 
+def run_neighbour_op(args):
+    """--op: times one of the operators either side of the signature (not the headline metric).
+    One GPU, device-resident inputs larger than L2, CUDA events around the public Python call;
+    prints one JSON line with the algorithmic bytes moved against the measured HBM bandwidth."""
+    import torch
+    import pysiglib_b200 as psl
+    from pysiglib_b200 import load_cusig
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(11)
+    rnd = lambda *shape: torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)
+    extra = {}
+    if args.op in ("sig_combine", "sig_join"):
+        B, d, N = args.batch or 4096, 16, 4
+        S = sum(d ** k for k in range(1, N + 1))
+        a, b, g, v = rnd(B, S) * 0.1, rnd(B, S) * 0.1, rnd(B, S), rnd(B, d) * 0.3
+        if args.op == "sig_combine":
+            fwd, bwd = (lambda: psl.sig_combine(a, b, d, N)), (lambda: psl.sig_combine_backprop(g, a, b, d, N))
+            fwd_bytes, bwd_bytes = 3 * B * S * 4, 5 * B * S * 4
+        else:
+            fwd, bwd = (lambda: psl.sig_join(a, v, d, N)), (lambda: psl.sig_join_backprop(g, a, v, d, N))
+            fwd_bytes, bwd_bytes = 2 * B * S * 4, 3 * B * S * 4
+        workload = "%s: float32, B=%d signatures of d=%d, degree %d (S=%d)" % (args.op, B, d, N, S)
+    elif args.op == "transform_path":
+        B, L, d = args.batch or 4096, args.length or 4096, 16
+        x = rnd(B, L, d)
+        g = rnd(B, 2 * L - 1, 2 * d + 1)
+        fwd = lambda: psl.transform_path(x, time_aug=True, lead_lag=True)
+        bwd = lambda: psl.transform_path_backprop(g, time_aug=True, lead_lag=True)
+        fwd_bytes = bwd_bytes = (B * L * d + B * (2 * L - 1) * (2 * d + 1)) * 4
+        workload = "transform_path: float32, B=%d, L=%d, d=%d, time_aug + lead_lag" % (B, L, d)
+    else:  # correction
+        B, L, d, N = args.batch or 2048, args.length or 256, 4, 4
+        S = sum(d ** k for k in range(1, N + 1))
+        x = torch.cumsum(rnd(B, L, d) * (1.0 / L) ** 0.5, dim=1).contiguous()
+        c = (rnd(B, L - 1, d * d) * 0.05).contiguous()
+        s0 = psl.sig(x, N, correction=c)
+        g = rnd(B, S)
+        fwd = lambda: psl.sig(x, N, correction=c)
+        bwd = lambda: psl.sig_backprop(x, s0, g, N, correction=c)
+        fwd_bytes = (B * L * d + B * (L - 1) * d * d + B * S) * 4
+        bwd_bytes = (2 * B * L * d + B * (L - 1) * d * d + 2 * B * S) * 4
+        workload = "sig with level-2 corrections: float32, B=%d, L=%d, d=%d, degree %d" % (B, L, d, N)
+        from oracle import refcuda
+        if refcuda.available() and not args.no_refcuda:
+            ref_s = refcuda.sig(x, N, correction=c)
+            extra["max_abs_diff_vs_reference_cuda"] = float((ref_s - s0).abs().max())
+            extra["reference_cuda"] = {
+                "fwd_ms": _time_ms(torch, lambda: refcuda.sig(x, N, correction=c), 1, 3),
+                "bwd_ms": _time_ms(torch, lambda: refcuda.sig_backprop(x, ref_s, g, N, correction=c), 1, 3),
+                "what": "reference cu_signature.cu correction kernels compiled for sm_100a, same inputs"}
+    warm, steps = max(args.warmup, 3), args.steps
+    before = load_cusig.launch_count()
+    with ClockSampler(0) as clocks:
+        fwd_ms = _time_ms(torch, fwd, warm, steps)
+        bwd_ms = _time_ms(torch, bwd, warm, steps)
+    launches = (load_cusig.launch_count() - before)
+    hbm_peak, note = 6650.0, "fallback"
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hbm_peak, note = float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        pass
+    gbs = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9
+    line = {"op": args.op, "config": {"workload": workload, "l2": "inputs larger than L2" if fwd_bytes > 3e8 else "inputs fit L2"},
+            "n_gpus": 1, "steps": steps, "warmup": warm, "dtype": "f32", "data": "synthetic",
+            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "roofline": {"bound": "hbm", "unit": "GB/s", "peak": hbm_peak, "peak_source": note,
+                         "forward": {"achieved": gbs(fwd_bytes, fwd_ms), "frac": gbs(fwd_bytes, fwd_ms) / hbm_peak},
+                         "backward": {"achieved": gbs(bwd_bytes, bwd_ms), "frac": gbs(bwd_bytes, bwd_ms) / hbm_peak}},
+            "clocks": clocks.summary(), "gpu_launches_counted": launches}
+    line.update(extra)
+    print(json.dumps(line))
+
+
+def _time_ms(torch, fn, warmup, steps):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / steps
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="sig", choices=["sig", "sig_combine", "sig_join", "transform_path", "correction"],
+                    help="sig (default) is the headline path; the others time one neighbouring operator on one GPU")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -207,6 +297,10 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, cfg, rank)
+        return
+    if args.op != "sig":
+        if rank == 0:
+            run_neighbour_op(args)
         return
 
     import torch

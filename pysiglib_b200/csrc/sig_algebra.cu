@@ -39,6 +39,7 @@ Levels checked_levels(uint64_t dim, uint64_t degree, const char* who) {
 }
 
 void check_launch(const char* what) {
+    count_launch();
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
 }
