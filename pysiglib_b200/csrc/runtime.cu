@@ -82,6 +82,7 @@ DeviceGuard::~DeviceGuard() {
 
 Scratch::Scratch(size_t bytes, cudaStream_t stream) : stream_(stream) {
     if (bytes == 0) return;
+    (void)device_context(current_device());  // first use on a device sets the pool to keep freed scratch
     const cudaError_t err = cudaMallocAsync(&ptr_, bytes, stream);
     if (err == cudaErrorMemoryAllocation) {
         (void)cudaGetLastError();

@@ -35,6 +35,8 @@ unsigned grid_1d(uint64_t work, int threads) {
 Levels checked_levels(uint64_t dim, uint64_t degree, const char* who) {
     if (degree > kAlgebraMaxDegree)
         throw std::invalid_argument(std::string(who) + ": degree above 64 is not supported");
+    if (sig_length_full(dim, degree) > kAlgebraMaxLength)  // throws on overflow by itself
+        throw std::invalid_argument(std::string(who) + ": signatures of 2^31 or more coefficients are not supported");
     return make_levels(dim, degree);
 }
 
@@ -46,17 +48,18 @@ void check_launch(const char* what) {
 
 // ----- linear signature and its adjoint ------------------------------------------------------
 
-// out points at the level-1 coefficient of path 0; one thread per coefficient of the batch.
+// out points at the level-1 coefficient of path 0; one thread per coefficient, paths along grid.y.
 template <typename T>
 __global__ void linear_sig_kernel(const T* __restrict__ disp, T* __restrict__ out, uint64_t out_stride, Levels lv,
                                   uint64_t batch, bool write_scalar) {
-    const uint64_t S = lv.total();
-    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= batch * S) return;
-    const uint64_t b = idx / S, j = idx - b * S;
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= lv.total()) return;
     const uint32_t t = lv.level_of(j);
-    out[b * out_stride + j] = linear_sig_coeff(disp + b * lv.dim, lv, t, j - lv.off[t]);
-    if (write_scalar && j == 0) out[b * out_stride - 1] = T(1);
+    const uint32_t w = j - lv.off[t];
+    for (uint64_t b = blockIdx.y; b < batch; b += gridDim.y) {
+        out[b * out_stride + j] = linear_sig_coeff(disp + b * lv.dim, lv, t, w);
+        if (write_scalar && j == 0) out[b * out_stride - 1] = T(1);
+    }
 }
 
 // d_disp[b][i] = sum over coefficients of dL[b] * d(linear signature)/d v_i.  One CTA per path;
@@ -68,22 +71,22 @@ __global__ void linear_sig_adjoint_kernel(const T* __restrict__ disp, const T* _
     extern __shared__ unsigned char smem_raw[];
     T* acc = reinterpret_cast<T*>(smem_raw);
     const uint64_t b = blockIdx.x;
-    const T* v = disp + b * lv.dim;
+    const T* v = disp + b * uint64_t(lv.dim);
     const T* g = dL + b * dl_stride;
-    T* target = use_shared ? acc : d_disp + b * lv.dim;
+    T* target = use_shared ? acc : d_disp + b * uint64_t(lv.dim);
     if (use_shared) {
-        for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) acc[i] = T(0);
+        for (uint32_t i = threadIdx.x; i < lv.dim; i += blockDim.x) acc[i] = T(0);
         __syncthreads();
     }
-    const uint64_t S = lv.total();
-    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+    const uint32_t S = lv.total();
+    for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) {
         const uint32_t t = lv.level_of(j);
         linear_sig_adjoint_terms(v, g[j], lv, t, j - lv.off[t],
-                                 [&](uint64_t letter, T value) { atomicAdd(&target[letter], value); });
+                                 [&](uint32_t letter, T value) { atomicAdd(&target[letter], value); });
     }
     if (use_shared) {
         __syncthreads();
-        for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) d_disp[b * lv.dim + i] = acc[i];
+        for (uint32_t i = threadIdx.x; i < lv.dim; i += blockDim.x) d_disp[b * lv.dim + i] = acc[i];
     }
 }
 
@@ -91,8 +94,8 @@ template <typename T>
 void launch_linear_sig(const T* disp, T* out_level1, uint64_t out_stride, const Levels& lv, uint64_t batch,
                        bool write_scalar, cudaStream_t stream) {
     if (lv.degree == 0 || batch == 0) return;
-    linear_sig_kernel<T><<<grid_1d(batch * lv.total(), kThreads), kThreads, 0, stream>>>(disp, out_level1, out_stride,
-                                                                                        lv, batch, write_scalar);
+    const dim3 grid(grid_1d(lv.total(), kThreads), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
+    linear_sig_kernel<T><<<grid, kThreads, 0, stream>>>(disp, out_level1, out_stride, lv, batch, write_scalar);
     check_launch("linear_sig kernel");
 }
 
@@ -101,7 +104,7 @@ void launch_linear_sig_adjoint(const T* disp, const T* dL_level1, uint64_t dl_st
                                uint64_t batch, cudaStream_t stream) {
     if (batch == 0) return;
     if (batch > 0x7fffffffull) throw std::invalid_argument("batch too large for one kernel launch");
-    const size_t smem = lv.dim * sizeof(T);
+    const size_t smem = size_t(lv.dim) * sizeof(T);
     const bool use_shared = smem <= 32 * 1024;
     if (!use_shared) SIG_CUDA_CHECK(cudaMemsetAsync(d_disp, 0, batch * lv.dim * sizeof(T), stream));
     linear_sig_adjoint_kernel<T><<<static_cast<unsigned>(batch), kThreads, use_shared ? smem : 0, stream>>>(
@@ -123,23 +126,24 @@ struct CorrectionArgs {
 template <typename T>
 __device__ void build_segment_log(T* X, const PathView<T>& pv, const T* x, int step, const CorrectionArgs<T>& c,
                                   const T* corr_path, const Levels& lv) {
-    const uint64_t S = lv.total();
-    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x)
+    const uint32_t S = lv.total();
+    for (uint32_t j = threadIdx.x; j < S; j += blockDim.x)
         X[j] = j < lv.dim ? pv.increment(x, step, static_cast<int>(j)) : T(0);
     __syncthreads();
     const T* seg = corr_path + uint64_t(step) * c.segment_stride;
-    uint64_t offset = 0, level_size = c.data_dim;
+    const uint32_t data_dim = static_cast<uint32_t>(c.data_dim);
+    uint32_t offset = 0, level_size = data_dim;  // the correction is shorter than a signature: 32-bit indices
     for (uint32_t level = 2; level <= lv.degree; ++level) {
-        level_size *= c.data_dim;
-        if (offset + level_size > c.len) break;
-        for (uint64_t w = threadIdx.x; w < level_size; w += blockDim.x) {
+        level_size *= data_dim;
+        if (uint64_t(offset) + level_size > c.len) break;
+        for (uint32_t w = threadIdx.x; w < level_size; w += blockDim.x) {
             const T value = seg[offset + w];
             if (value == T(0)) continue;
-            uint64_t rest = w, aug = 0, pw = level_size / c.data_dim;
+            uint32_t rest = w, aug = 0, pw = level_size / data_dim;
             for (uint32_t pos = 0; pos < level; ++pos) {
-                const uint64_t label = rest / pw;
+                const uint32_t label = rest / pw;
                 rest -= label * pw;
-                if (pos + 1 < level) pw /= c.data_dim;
+                if (pos + 1 < level) pw /= data_dim;
                 aug = aug * lv.dim + label;
             }
             X[lv.off[level] + aug] = value;
@@ -153,15 +157,15 @@ __device__ void build_segment_log(T* X, const PathView<T>& pv, const T* x, int s
 // (N-1 vectors) when keep_powers, else ping-ponging inside the first two.  Ends with a barrier.
 template <typename T>
 __device__ void segment_exp(const T* X, T* E, T* Einv, T* powers, bool keep_powers, const Levels& lv) {
-    const uint64_t S = lv.total();
-    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+    const uint32_t S = lv.total();
+    for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) {
         E[j] = X[j];
         if (Einv) Einv[j] = -X[j];
     }
     const T* prev = X;
     for (uint32_t n = 2; n <= lv.degree; ++n) {
         T* cur = powers + (keep_powers ? uint64_t(n - 2) : uint64_t(n & 1)) * S;
-        for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+        for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) {
             const uint32_t t = lv.level_of(j);
             const T val = exp_power_coeff(X, prev, lv, n, t, j - lv.off[t]);
             cur[j] = val;
@@ -178,17 +182,17 @@ template <typename T>
 __global__ void correction_forward_kernel(PathView<T> pv, CorrectionArgs<T> c, T* __restrict__ out,
                                           uint64_t out_stride, bool scalar_term, T* __restrict__ scratch, Levels lv,
                                           uint64_t batch_offset) {
-    const uint64_t S = lv.total();
+    const uint32_t S = lv.total();
     const uint64_t b = batch_offset + blockIdx.x;
     const T* x = pv.base + b * pv.path_stride;
     const T* corr_path = c.ptr + b * c.batch_stride;
     T* ws = scratch + uint64_t(blockIdx.x) * 6 * S;
-    T *X = ws, *powers = ws + S, *E = ws + 3 * S, *cur = ws + 4 * S, *nxt = ws + 5 * S;
+    T *X = ws, *powers = ws + S, *E = ws + 3 * uint64_t(S), *cur = ws + 4 * uint64_t(S), *nxt = ws + 5 * uint64_t(S);
 
     for (int step = 0; step < pv.steps; ++step) {
         build_segment_log(X, pv, x, step, c, corr_path, lv);
         segment_exp<T>(X, E, nullptr, powers, false, lv);
-        for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+        for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) {
             if (step == 0) {
                 nxt[j] = E[j];
             } else {
@@ -204,7 +208,7 @@ __global__ void correction_forward_kernel(PathView<T> pv, CorrectionArgs<T> c, T
         if (threadIdx.x == 0) o[0] = T(1);
         ++o;
     }
-    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) o[j] = cur[j];
+    for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) o[j] = cur[j];
 }
 
 // Buffers per path: X, P_2..P_N (at least 2), E, Einv, S x2, dS x2, dE, dP x2.
@@ -220,7 +224,7 @@ __global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, 
     extern __shared__ unsigned char smem_raw[];
     T* g = reinterpret_cast<T*>(smem_raw);  // gradient w.r.t. this step's increment
     T* g_next = g + lv.dim;                 // the same for the step after it
-    const uint64_t S = lv.total();
+    const uint32_t S = lv.total();
     const uint32_t N = lv.degree;
     const uint64_t b = batch_offset + blockIdx.x;
     const T* x = pv.base + b * pv.path_stride;
@@ -241,20 +245,20 @@ __global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, 
     T* o = out + b * pv.path_stride;
     const uint64_t shift = scalar_term ? 1 : 0;
 
-    for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+    for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) {
         Scur[j] = sig[b * sig_stride + shift + j];
         dScur[j] = sig_derivs[b * sig_stride + shift + j];
     }
-    for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) g_next[i] = T(0);
+    for (uint32_t i = threadIdx.x; i < lv.dim; i += blockDim.x) g_next[i] = T(0);
     __syncthreads();
 
     for (int step = pv.steps - 1; step >= 0; --step) {
-        for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) g[i] = T(0);
+        for (uint32_t i = threadIdx.x; i < lv.dim; i += blockDim.x) g[i] = T(0);
         build_segment_log(X, pv, x, step, c, corr_path, lv);
         segment_exp<T>(X, E, Einv, powers, true, lv);
 
         // signature of the path up to the start of this segment
-        for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+        for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) {
             const uint32_t t = lv.level_of(j);
             Snxt[j] = product_coeff(Scur, Einv, lv, t, j - lv.off[t]);
         }
@@ -262,9 +266,9 @@ __global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, 
         { T* tmp = Scur; Scur = Snxt; Snxt = tmp; }
 
         // split the adjoint of (Scur (x) E) between its factors
-        for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+        for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) {
             const uint32_t t = lv.level_of(j);
-            const uint64_t w = j - lv.off[t];
+            const uint32_t w = j - lv.off[t];
             dE[j] = right_adjoint_coeff(dScur, Scur, lv, t, w);
             dSnxt[j] = left_adjoint_coeff(dScur, E, lv, t, w);
         }
@@ -276,12 +280,12 @@ __global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, 
         T* dPprev = dPa;
         for (uint32_t n = N; n >= 2; --n) {
             const T* prev = n == 2 ? X : powers + uint64_t(n - 3) * S;  // P_{n-1}
-            for (uint64_t j = threadIdx.x; j < S; j += blockDim.x) {
+            for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) {
                 const uint32_t t = lv.level_of(j);
-                const uint64_t w = j - lv.off[t];
+                const uint32_t w = j - lv.off[t];
                 dPprev[j] = exp_adjoint_prev_coeff(dE, dPn, X, lv, n, t, w);
                 if (t >= n) {
-                    uint64_t letter;
+                    uint32_t letter;
                     const T term = exp_adjoint_level1_term(dE, dPn, prev, lv, n, t, w, &letter);
                     atomicAdd(&g[letter], term);
                 }
@@ -290,14 +294,14 @@ __global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, 
             dPn = dPprev;
             dPprev = dPprev == dPa ? dPb : dPa;
         }
-        for (uint64_t i = threadIdx.x; i < lv.dim; i += blockDim.x) {
+        for (uint32_t i = threadIdx.x; i < lv.dim; i += blockDim.x) {
             const T gi = g[i] + dE[i] + (dPn ? dPn[i] : T(0));
-            if (i < uint64_t(pv.d)) o[uint64_t(step + 1) * pv.d + i] = gi - g_next[i];
+            if (i < uint32_t(pv.d)) o[uint64_t(step + 1) * pv.d + i] = gi - g_next[i];
             g_next[i] = gi;
         }
         __syncthreads();
     }
-    for (uint64_t i = threadIdx.x; i < uint64_t(pv.d); i += blockDim.x) o[i] = -g_next[i];
+    for (uint32_t i = threadIdx.x; i < uint32_t(pv.d); i += blockDim.x) o[i] = -g_next[i];
 }
 
 constexpr uint64_t kScratchBudget = 1ull << 30;  // bytes of per-path working vectors held at once
@@ -309,46 +313,47 @@ CorrectionArgs<T> make_args(const CorrectionView<T>& c, uint64_t data_dim) {
 
 // ----- path transform --------------------------------------------------------------------------
 
+// One thread per element of one transformed path, paths along grid.y; a path holds fewer than 2^32 values.
 template <typename T>
-__global__ void transform_path_kernel(const T* __restrict__ in, T* __restrict__ out, uint64_t batch, uint64_t d,
-                                      uint64_t L, uint64_t dim, uint64_t len, bool time_aug, bool lead_lag, T dt) {
-    const uint64_t per_path = len * dim;
-    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= batch * per_path) return;
-    const uint64_t b = idx / per_path, r = idx - b * per_path;
-    const uint64_t p = r / dim, ch = r - p * dim;
-    const T* x = in + b * L * d;
-    T value;
-    if (time_aug && ch == dim - 1) {
-        value = static_cast<T>(p) * dt;
-    } else if (lead_lag) {
-        const uint64_t m = p >> 1, odd = p & 1;
-        value = ch < d ? x[m * d + ch] : x[(m + odd) * d + (ch - d)];
-    } else {
-        value = x[p * d + ch];
+__global__ void transform_path_kernel(const T* __restrict__ in, T* __restrict__ out, uint64_t batch, uint32_t d,
+                                      uint32_t L, uint32_t dim, uint32_t len, bool time_aug, bool lead_lag, T dt) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= len * dim) return;
+    const uint32_t p = r / dim, ch = r - p * dim;
+    const bool is_time = time_aug && ch == dim - 1;
+    uint32_t src = 0;
+    if (!is_time) {
+        if (lead_lag) {
+            const uint32_t m = p >> 1, odd = p & 1;
+            src = ch < d ? m * d + ch : (m + odd) * d + (ch - d);
+        } else {
+            src = p * d + ch;
+        }
     }
-    out[idx] = value;
+    const T time = static_cast<T>(p) * dt;
+    for (uint64_t b = blockIdx.y; b < batch; b += gridDim.y)
+        out[b * len * dim + r] = is_time ? time : in[b * L * d + src];
 }
 
 template <typename T>
 __global__ void transform_path_backprop_kernel(const T* __restrict__ derivs, T* __restrict__ out, uint64_t batch,
-                                               uint64_t d, uint64_t L, uint64_t dim, uint64_t len, bool lead_lag) {
-    const uint64_t per_path = L * d;
-    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= batch * per_path) return;
-    const uint64_t b = idx / per_path, r = idx - b * per_path;
-    const uint64_t k = r / d, j = r - k * d;
-    const T* g = derivs + b * len * dim;
-    T sum;
-    if (lead_lag) {
-        sum = g[(2 * k) * dim + j];
-        sum += g[(2 * k) * dim + d + j];
-        if (k + 1 < L) sum += g[(2 * k + 1) * dim + j];
-        if (k >= 1) sum += g[(2 * k - 1) * dim + d + j];
-    } else {
-        sum = g[k * dim + j];
+                                               uint32_t d, uint32_t L, uint32_t dim, uint32_t len, bool lead_lag) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= L * d) return;
+    const uint32_t k = r / d, j = r - k * d;
+    for (uint64_t b = blockIdx.y; b < batch; b += gridDim.y) {
+        const T* g = derivs + b * len * dim;
+        T sum;
+        if (lead_lag) {
+            sum = g[(2 * k) * dim + j];
+            sum += g[(2 * k) * dim + d + j];
+            if (k + 1 < L) sum += g[(2 * k + 1) * dim + j];
+            if (k >= 1) sum += g[(2 * k - 1) * dim + d + j];
+        } else {
+            sum = g[k * dim + j];
+        }
+        out[b * L * d + r] = sum;
     }
-    out[idx] = sum;
 }
 
 // Runs `body(device pointers, stream)` with every host operand staged through one scratch block:
@@ -571,9 +576,11 @@ void transform_path_entry(const T* data_in, T* data_out, uint64_t batch, uint64_
     const SigShape s = make_shape(batch, dimension, length, 1, time_aug, lead_lag, false);
     const T dt = s.len > 1 ? end_time / static_cast<T>(s.len - 1) : T(0);
     const uint64_t n_out = checked_mul(checked_mul(batch, s.len, "transformed path"), s.dim, "transformed path");
+    if (s.len * s.dim >= (1ull << 32)) throw std::invalid_argument("transform_path_cuda: path too large");
     auto run = [&](const T* in, T* o, cudaStream_t st) {
-        transform_path_kernel<T><<<grid_1d(n_out, kThreads), kThreads, 0, st>>>(in, o, batch, dimension, length, s.dim,
-                                                                                s.len, time_aug, lead_lag, dt);
+        const dim3 grid(grid_1d(s.len * s.dim, kThreads), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
+        transform_path_kernel<T><<<grid, kThreads, 0, st>>>(in, o, batch, uint32_t(dimension), uint32_t(length),
+                                                            uint32_t(s.dim), uint32_t(s.len), time_aug, lead_lag, dt);
         check_launch("transform_path kernel");
     };
     int device = -1;
@@ -598,9 +605,11 @@ void transform_path_backprop_entry(const T* derivs, T* data_out, uint64_t batch,
     const SigShape s = make_shape(batch, dimension, length, 1, time_aug, lead_lag, false);
     const uint64_t n_in = checked_mul(checked_mul(batch, s.len, "transformed path"), s.dim, "transformed path");
     const uint64_t n_out = batch * length * dimension;
+    if (s.len * s.dim >= (1ull << 32)) throw std::invalid_argument("transform_path_backprop_cuda: path too large");
     auto run = [&](const T* g, T* o, cudaStream_t st) {
-        transform_path_backprop_kernel<T><<<grid_1d(n_out, kThreads), kThreads, 0, st>>>(g, o, batch, dimension, length,
-                                                                                        s.dim, s.len, lead_lag);
+        const dim3 grid(grid_1d(length * dimension, kThreads), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
+        transform_path_backprop_kernel<T><<<grid, kThreads, 0, st>>>(g, o, batch, uint32_t(dimension), uint32_t(length),
+                                                                     uint32_t(s.dim), uint32_t(s.len), lead_lag);
         check_launch("transform_path_backprop kernel");
     };
     int device = -1;

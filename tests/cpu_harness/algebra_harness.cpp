@@ -12,7 +12,7 @@ namespace {
 
 template <typename T, typename F>
 void for_each_coeff(const Levels& lv, F f) {
-    for (uint64_t j = 0; j < lv.total(); ++j) {
+    for (uint32_t j = 0; j < lv.total(); ++j) {
         const uint32_t t = lv.level_of(j);
         f(j, t, j - lv.off[t]);
     }
@@ -29,7 +29,7 @@ void run_exp(const T* X, T* E, T* Einv, T* powers, const Levels& lv) {
     const T* prev = X;
     for (uint32_t n = 2; n <= lv.degree; ++n) {
         T* cur = powers + uint64_t(n - 2) * S;
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) {
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
             const T val = exp_power_coeff(X, prev, lv, n, t, w);
             cur[j] = val;
             E[j] += val;
@@ -49,10 +49,10 @@ void run_exp_adjoint_level1(const T* X, const T* powers, const T* dE, T* g, cons
     T* dPprev = a.data();
     for (uint32_t n = lv.degree; n >= 2; --n) {
         const T* prev = n == 2 ? X : powers + uint64_t(n - 3) * S;
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) {
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
             dPprev[j] = exp_adjoint_prev_coeff(dE, dPn, X, lv, n, t, w);
             if (t >= n) {
-                uint64_t letter;
+                uint32_t letter;
                 const T term = exp_adjoint_level1_term(dE, dPn, prev, lv, n, t, w, &letter);
                 g[letter] += term;
             }
@@ -85,7 +85,7 @@ void correction_forward(const T* path, uint64_t L, uint64_t d, uint64_t degree, 
     for (uint64_t step = 0; step + 1 < L; ++step) {
         build_log(X.data(), path, d, int(step), corr + step * seg_stride, corr_len, lv);
         run_exp<T>(X.data(), E.data(), nullptr, powers.data(), lv);
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) {
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
             nxt[j] = step == 0 ? E[j] : product_coeff(cur.data(), E.data(), lv, t, w);
         });
         cur.swap(nxt);
@@ -103,11 +103,11 @@ void correction_backward(const T* path, uint64_t L, uint64_t d, uint64_t degree,
     for (int64_t step = int64_t(L) - 2; step >= 0; --step) {
         build_log(X.data(), path, d, int(step), corr + step * seg_stride, corr_len, lv);
         run_exp<T>(X.data(), E.data(), Einv.data(), powers.data(), lv);
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) {
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
             Snxt[j] = product_coeff(Scur.data(), Einv.data(), lv, t, w);
         });
         Scur.swap(Snxt);
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) {
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
             dE[j] = right_adjoint_coeff(dScur.data(), Scur.data(), lv, t, w);
             dSnxt[j] = left_adjoint_coeff(dScur.data(), E.data(), lv, t, w);
         });
@@ -137,25 +137,25 @@ void correction_backward(const T* path, uint64_t L, uint64_t d, uint64_t degree,
     }                                                                                                                 \
     extern "C" void alg_product_##SUF(const T* A, const T* B, T* C, uint64_t dim, uint64_t degree) {                  \
         const Levels lv = make_levels(dim, degree);                                                                   \
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) { C[j] = product_coeff(A, B, lv, t, w); });     \
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) { C[j] = product_coeff(A, B, lv, t, w); });     \
     }                                                                                                                 \
     extern "C" void alg_adjoints_##SUF(const T* dC, const T* A, const T* B, T* dA, T* dB, uint64_t dim,               \
                                        uint64_t degree) {                                                             \
         const Levels lv = make_levels(dim, degree);                                                                   \
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) {                                               \
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {                                               \
             dA[j] = left_adjoint_coeff(dC, B, lv, t, w);                                                              \
             dB[j] = right_adjoint_coeff(dC, A, lv, t, w);                                                             \
         });                                                                                                           \
     }                                                                                                                 \
     extern "C" void alg_linear_sig_##SUF(const T* v, T* out, uint64_t dim, uint64_t degree) {                         \
         const Levels lv = make_levels(dim, degree);                                                                   \
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) { out[j] = linear_sig_coeff(v, lv, t, w); });   \
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) { out[j] = linear_sig_coeff(v, lv, t, w); });   \
     }                                                                                                                 \
     extern "C" void alg_linear_sig_adjoint_##SUF(const T* v, const T* dL, T* dv, uint64_t dim, uint64_t degree) {     \
         const Levels lv = make_levels(dim, degree);                                                                   \
         for (uint64_t i = 0; i < dim; ++i) dv[i] = T(0);                                                              \
-        for_each_coeff<T>(lv, [&](uint64_t j, uint32_t t, uint64_t w) {                                               \
-            linear_sig_adjoint_terms(v, dL[j], lv, t, w, [&](uint64_t letter, T value) { dv[letter] += value; });     \
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {                                               \
+            linear_sig_adjoint_terms(v, dL[j], lv, t, w, [&](uint32_t letter, T value) { dv[letter] += value; });     \
         });                                                                                                           \
     }                                                                                                                 \
     extern "C" void alg_correction_forward_##SUF(const T* path, uint64_t L, uint64_t d, uint64_t degree,              \
