@@ -124,6 +124,27 @@ int transform_path_backprop_cuda_f(const float* derivs, float* data_out, uint64_
 int transform_path_backprop_cuda_d(const double* derivs, double* data_out, uint64_t batch_size, uint64_t dimension,
                                    uint64_t length, bool time_aug, bool lead_lag, double end_time);
 
+/* Signature -> log signature.  method 0: expanded tensor logarithm in the layout of `sig` (scalar
+ * slot 0); method 1: its coordinates at the Lyndon words of length <= degree, by length then
+ * lexicographically (log_sig_length values per signature).  Methods 2 and 3 return code 2.
+ * The backward takes dLoss/d log_sig in the layout of the forward's output and writes dLoss/d sig
+ * in the layout of `sig`.
+ * Replaces: siglib/cusig/cusig.h:407-409, 427-429 (siglib/cusig/cu_log_signature.cu); bound by
+ *           pysiglib/load_siglib.py:496-505.  Synchronous; device or host pointers. */
+int sig_to_log_sig_cuda_f(const float* sig, float* out, uint64_t batch_size, uint64_t dimension, uint64_t degree,
+                          int method, bool scalar_term);
+int sig_to_log_sig_cuda_d(const double* sig, double* out, uint64_t batch_size, uint64_t dimension, uint64_t degree,
+                          int method, bool scalar_term);
+int sig_to_log_sig_backprop_cuda_f(const float* sig, float* out, const float* log_sig_derivs, uint64_t batch_size,
+                                   uint64_t dimension, uint64_t degree, int method, bool scalar_term);
+int sig_to_log_sig_backprop_cuda_d(const double* sig, double* out, const double* log_sig_derivs, uint64_t batch_size,
+                                   uint64_t dimension, uint64_t degree, int method, bool scalar_term);
+
+/* Builds the per-device Lyndon-word table of method 1 ahead of the first call (optional: the
+ * table is built on demand); method 0 needs nothing; methods 2 and 3 return code 2.
+ * Replaces: siglib/cusig/cusig.h:447; bound by pysiglib/load_siglib.py:165-183. */
+int prepare_log_sig_cuda(uint64_t dimension, uint64_t degree, int method, bool use_disk);
+
 /* Thread-local text of the last error; valid until the next call on this thread.
  * Replaces: siglib/cusig/cusig.h:43; bound by pysiglib/load_siglib.py:108-110. */
 const char* cusig_last_error_message(void);

@@ -17,7 +17,7 @@ _LIB = None
 
 def build(force=False):
     """Compile the oracle with gcc (idempotent)."""
-    src = [os.path.join(_HERE, f) for f in ("sig_oracle.c", "sig_oracle_impl.h", "sig_oracle_algebra.h")]
+    src = [os.path.join(_HERE, f) for f in ("sig_oracle.c", "sig_oracle_impl.h", "sig_oracle_algebra.h", "sig_oracle_log.h")]
     if (not force and os.path.exists(_LIB_PATH)
             and all(os.path.getmtime(_LIB_PATH) >= os.path.getmtime(s) for s in src)):
         return _LIB_PATH
@@ -54,12 +54,16 @@ def _lib():
                      [ptr, ptr, ptr, ptr, u64, u64, u64, u64, ci, real, ci, ptr, u64, u64, u64]),
                     ("oracle_tensor_exp_", [ptr, ptr, u64, u64]),
                     ("oracle_tensor_exp_backprop_", [ptr, ptr, ptr, u64, u64]),
+                    ("oracle_sig_to_log_sig_", [ptr, ptr, u64, u64, u64, ci, ci]),
+                    ("oracle_sig_to_log_sig_backprop_", [ptr, ptr, ptr, u64, u64, u64, ci, ci]),
                     ("oracle_linear_sig_", [ptr, ptr, u64, u64, u64, ci]),
                     ("oracle_sig_join_", [ptr, ptr, ptr, u64, u64, u64, ci, ci]),
                     ("oracle_sig_join_backprop_", [ptr, ptr, ptr, ptr, ptr, u64, u64, u64, ci, ci])):
                 fn = getattr(lib, name + suf)
                 fn.restype = ctypes.c_int
                 fn.argtypes = args
+        lib.oracle_lyndon_indices.restype = u64
+        lib.oracle_lyndon_indices.argtypes = [u64, u64, ctypes.POINTER(u64), u64]
         lib.oracle_sig_length.restype = u64
         lib.oracle_sig_length.argtypes = [u64, u64]
         _LIB = lib
@@ -281,3 +285,52 @@ def sig_join_backprop(d_out, sig_, displacement, dim, degree, prepend=False):
     if rc:
         raise RuntimeError("oracle_sig_join_backprop failed with code %d" % rc)
     return d_sig.reshape(a.shape), d_disp.reshape(v.shape)
+
+
+def lyndon_indices(dim, degree):
+    """Flat positions (scalar slot = 0) of the Lyndon words of length <= degree, by length then
+    lexicographically: the coordinates log-signature method 1 keeps."""
+    n = _lib().oracle_lyndon_indices(dim, degree, None, 0)
+    out = np.zeros(n, dtype=np.uint64)
+    _lib().oracle_lyndon_indices(dim, degree, out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint64)), n)
+    return out
+
+
+def log_sig_length(dim, degree):
+    return int(_lib().oracle_lyndon_indices(dim, degree, None, 0))
+
+
+def sig_to_log_sig(sig_, dim, degree, method=1):
+    """Oracle log signature from (batches of) signatures; method 0 = expanded tensor logarithm in
+    the layout of the input, method 1 = its coordinates at the Lyndon words."""
+    a = np.ascontiguousarray(sig_)
+    a2 = a.reshape(-1, a.shape[-1])
+    suf, real = _suffix(a2)
+    full = sig_length(dim, degree, True)
+    if a2.shape[1] not in (full, full - 1):
+        raise ValueError("signature has the wrong length")
+    n_out = a2.shape[1] if method == 0 else log_sig_length(dim, degree)
+    out = np.empty((a2.shape[0], n_out), dtype=a2.dtype)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_sig_to_log_sig_" + suf)(a2.ctypes.data_as(ptr), out.ctypes.data_as(ptr), a2.shape[0],
+                                                         dim, degree, method, int(a2.shape[1] == full))
+    if rc:
+        raise RuntimeError("oracle_sig_to_log_sig failed with code %d" % rc)
+    return out.reshape(a.shape[:-1] + (n_out,))
+
+
+def sig_to_log_sig_backprop(sig_, log_sig_derivs, dim, degree, method=1):
+    """Oracle dF/d sig from dF/d log_sig (layouts as in sig_to_log_sig)."""
+    a = np.ascontiguousarray(sig_)
+    a2 = a.reshape(-1, a.shape[-1])
+    g2 = np.ascontiguousarray(log_sig_derivs, dtype=a.dtype).reshape(a2.shape[0], -1)
+    suf, real = _suffix(a2)
+    full = sig_length(dim, degree, True)
+    out = np.empty_like(a2)
+    ptr = ctypes.POINTER(real)
+    rc = getattr(_lib(), "oracle_sig_to_log_sig_backprop_" + suf)(
+        a2.ctypes.data_as(ptr), out.ctypes.data_as(ptr), g2.ctypes.data_as(ptr), a2.shape[0], dim, degree, method,
+        int(a2.shape[1] == full))
+    if rc:
+        raise RuntimeError("oracle_sig_to_log_sig_backprop failed with code %d" % rc)
+    return out.reshape(a.shape)

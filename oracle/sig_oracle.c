@@ -38,6 +38,7 @@ uint64_t oracle_sig_length(uint64_t dim, uint64_t degree) {
 #define FMA(a, b, c) fmaf((a), (b), (c))
 #include "sig_oracle_impl.h"
 #include "sig_oracle_algebra.h"
+#include "sig_oracle_log.h"
 #undef REAL
 #undef SUF
 #undef FMA
@@ -47,6 +48,7 @@ uint64_t oracle_sig_length(uint64_t dim, uint64_t degree) {
 #define FMA(a, b, c) fma((a), (b), (c))
 #include "sig_oracle_impl.h"
 #include "sig_oracle_algebra.h"
+#include "sig_oracle_log.h"
 #undef REAL
 #undef SUF
 #undef FMA

@@ -107,7 +107,7 @@ void sig_backprop_sharded(const T* path, T* out, const T* sig_derivs, const T* s
 int stub_not_built(const char* name) noexcept {
     clear_last_error();
     std::string msg = std::string(name) +
-        " is not part of this build of libcusig (it serves the signature, sig_backprop, sig_combine, sig_join, linear_sig and transform_path families)";
+        " is not part of this build of libcusig (it serves the signature, sig_backprop, sig_combine, sig_join, linear_sig, transform_path and sig_to_log_sig families)";
     set_last_error(msg.c_str());
     return 10;
 }
@@ -205,14 +205,32 @@ SIG_API int sig_combine_backprop_cuda_d(const double* sig_combined_deriv, double
                                                    bool lead_lag, T end_time) {                                       \
         SIG_SAFE_CALL(transform_path_backprop_entry<T>(derivs, data_out, batch_size, dimension, length, time_aug,     \
                                                        lead_lag, end_time, sync_options()));                          \
+    }                                                                                                                 \
+    SIG_API int sig_to_log_sig_cuda_##SUF(const T* sig, T* out, uint64_t batch_size, uint64_t dimension,             \
+                                          uint64_t degree, int method, bool scalar_term) {                            \
+        SIG_SAFE_CALL(sig_to_log_sig_entry<T>(sig, out, batch_size, dimension, degree, method, scalar_term,           \
+                                              sync_options()));                                                       \
+    }                                                                                                                 \
+    SIG_API int sig_to_log_sig_backprop_cuda_##SUF(const T* sig, T* out, const T* log_sig_derivs, uint64_t batch_size, \
+                                                   uint64_t dimension, uint64_t degree, int method,                   \
+                                                   bool scalar_term) {                                                \
+        SIG_SAFE_CALL(sig_to_log_sig_backprop_entry<T>(sig, out, log_sig_derivs, batch_size, dimension, degree,       \
+                                                       method, scalar_term, sync_options()));                         \
     }
 SIG_ALGEBRA_EXPORTS(f, float)
 SIG_ALGEBRA_EXPORTS(d, double)
 #undef SIG_ALGEBRA_EXPORTS
 
+SIG_API int prepare_log_sig_cuda(uint64_t dimension, uint64_t degree, int method, bool /*use_disk*/) {
+    SIG_SAFE_CALL(prepare_log_sig_entry(dimension, degree, method));
+}
+
 SIG_API const char* cusig_last_error_message(void) { return last_error(); }
 
-SIG_API void cusig_shutdown(void) { shutdown_runtime(); }
+SIG_API void cusig_shutdown(void) {
+    release_log_sig_tables();
+    shutdown_runtime();
+}
 
 SIG_API int sigb200_signature_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
                                 uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, float end_time,
@@ -331,7 +349,6 @@ SIG_STUB_PAIR(log_sig_from_path_cuda) SIG_STUB_PAIR(log_sig_from_path_backprop_c
 SIG_STUB_PAIR(log_sig_join_cuda) SIG_STUB_PAIR(log_sig_join_backprop_cuda)
 SIG_STUB_PAIR(logsig_to_sig_cuda) SIG_STUB_PAIR(logsig_to_sig_backprop_cuda)
 SIG_STUB_PAIR(sig_coef_cuda) SIG_STUB_PAIR(sig_coef_backprop_cuda)
-SIG_STUB_PAIR(sig_to_log_sig_cuda) SIG_STUB_PAIR(sig_to_log_sig_backprop_cuda)
 SIG_STUB_PAIR(sig_kernel_cuda) SIG_STUB_PAIR(sig_kernel_backprop_cuda)
 SIG_STUB_PAIR(sig_kernel_poly_cuda) SIG_STUB_PAIR(sig_kernel_poly_backprop_cuda)
 SIG_STUB_PAIR(branched_sig_cuda) SIG_STUB_PAIR(branched_sig_backprop_cuda)
@@ -342,6 +359,6 @@ SIG_STUB_PAIR(branched_sig_kernel_poly_cuda) SIG_STUB_PAIR(branched_sig_kernel_p
 SIG_STUB_PAIR(branched_sig_to_log_sig_cuda) SIG_STUB_PAIR(branched_sig_to_log_sig_backprop_cuda)
 SIG_STUB_PAIR(branched_log_sig_join_cuda) SIG_STUB_PAIR(branched_log_sig_join_backprop_cuda)
 SIG_STUB_PAIR(branched_log_sig_from_path_cuda) SIG_STUB_PAIR(branched_log_sig_from_path_backprop_cuda)
-SIG_STUB(prepare_log_sig_cuda) SIG_STUB(clear_cache_cuda) SIG_STUB(set_cache_dir_cuda)
+SIG_STUB(clear_cache_cuda) SIG_STUB(set_cache_dir_cuda)
 SIG_STUB(prepare_branched_sig_cuda) SIG_STUB(prepare_branched_log_sig_cuda)
 SIG_STUB(prepare_branched_sig_coef_cuda)

@@ -56,6 +56,22 @@ void sig_join_backprop_entry(const T* d_out, T* d_sig, T* d_displacement, const 
                              uint64_t batch, uint64_t dimension, uint64_t degree, bool prepend, bool scalar_term,
                              const CallOptions& opt);
 
+// Signature -> log signature.  method 0: the expanded tensor logarithm, in the layout of `sig`;
+// method 1: its coordinates at the Lyndon words (log_sig_length values per signature).  Replaces
+// sig_to_log_sig_cuda_ / sig_to_log_sig_backprop_cuda_ (siglib/cusig/cu_log_signature.cu) for those
+// two methods; the backward writes dLoss/d sig in the layout of `sig` (scalar slots 0).
+template <typename T>
+void sig_to_log_sig_entry(const T* sig, T* out, uint64_t batch, uint64_t dimension, uint64_t degree, int method,
+                          bool scalar_term, const CallOptions& opt);
+template <typename T>
+void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs, uint64_t batch, uint64_t dimension,
+                                   uint64_t degree, int method, bool scalar_term, const CallOptions& opt);
+// Builds (and caches per device) the Lyndon-word index table that method 1 needs; methods 2 and 3
+// are not part of this build.
+void prepare_log_sig_entry(uint64_t dimension, uint64_t degree, int method);
+uint64_t log_sig_length_host(uint64_t dimension, uint64_t degree);
+void release_log_sig_tables() noexcept;
+
 // Materialises the time-augmented / lead-lag path, and the adjoint of that map.  Replace
 // transform_path_cuda_ and transform_path_backprop_cuda_ (siglib/cusig/cu_path_transforms.cu:100-205).
 template <typename T>

@@ -110,6 +110,49 @@ SIG_HD T right_adjoint_coeff(const T* dC, const T* A, const Levels& lv, uint32_t
     return acc;
 }
 
+// Product without the unit terms: sum_{l=1..t-1} A_l[u] B_{t-l}[v] for the word w = u v of level t.
+template <typename T>
+SIG_HD T nonunital_product_coeff(const T* A, const T* B, const Levels& lv, uint32_t t, uint32_t w) {
+    T acc = T(0);
+    uint32_t right_size = t > 1 ? lv.size(t - 1) : 1;  // d^(t-left), left = 1
+    for (uint32_t left = 1; left < t; ++left) {
+        const uint32_t u = w / right_size, v = w - u * right_size;
+        acc = alg_fma(B[lv.off[t - left] + v], A[lv.off[left] + u], acc);
+        right_size /= lv.dim;
+    }
+    return acc;
+}
+
+// Adjoints of C = (product without unit terms) of A and B:
+//   dA_l[u] = sum_{m,v} dC_{l+m}[u v] B_m[v],   dB_m[v] = sum_{l,u} dC_{l+m}[u v] A_l[u].
+template <typename T>
+SIG_HD T nonunital_left_adjoint_coeff(const T* dC, const T* B, const Levels& lv, uint32_t l, uint32_t u) {
+    T acc = T(0);
+    uint32_t msize = lv.dim;
+    for (uint32_t m = 1; l + m <= lv.degree; ++m) {
+        const T* row = dC + lv.off[l + m] + u * msize;
+        const T* b = B + lv.off[m];
+        T dot = T(0);
+        for (uint32_t v = 0; v < msize; ++v) dot = alg_fma(row[v], b[v], dot);
+        acc += dot;
+        msize *= lv.dim;
+    }
+    return acc;
+}
+template <typename T>
+SIG_HD T nonunital_right_adjoint_coeff(const T* dC, const T* A, const Levels& lv, uint32_t m, uint32_t v) {
+    T acc = T(0);
+    const uint32_t msize = lv.size(m);
+    uint32_t lsize = lv.dim;
+    for (uint32_t l = 1; l + m <= lv.degree; ++l) {
+        const T* col = dC + lv.off[l + m] + v;
+        const T* a = A + lv.off[l];
+        for (uint32_t u = 0; u < lsize; ++u) acc = alg_fma(col[u * msize], a[u], acc);
+        lsize *= lv.dim;
+    }
+    return acc;
+}
+
 // Power series of exp: P_1 = X, P_n = X (x) P_{n-1} / n (no scalar terms; P_n lives on levels >= n).
 // Returns coefficient w of level t of P_n given P_{n-1} (Pprev), 0 below level n.
 template <typename T>

@@ -42,6 +42,8 @@ def _bind(lib):
     lib.cusig_last_error_message.restype = c_char_p
     lib.cusig_shutdown.argtypes = ()
     lib.cusig_shutdown.restype = None
+    lib.prepare_log_sig_cuda.argtypes = (c_uint64, c_uint64, c_int, c_bool)
+    lib.prepare_log_sig_cuda.restype = c_int
     lib.sigb200_sig_length.argtypes = (c_uint64, c_uint64)
     lib.sigb200_sig_length.restype = c_uint64
     lib.sigb200_set_kernel_policy.argtypes = (c_int,)
@@ -84,6 +86,12 @@ def _bind(lib):
         f.restype = c_int
         f = getattr(lib, "sig_join_backprop_cuda_" + suffix)
         f.argtypes = (ptr, ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_bool, c_bool)
+        f.restype = c_int
+        f = getattr(lib, "sig_to_log_sig_cuda_" + suffix)
+        f.argtypes = (ptr, ptr, c_uint64, c_uint64, c_uint64, c_int, c_bool)
+        f.restype = c_int
+        f = getattr(lib, "sig_to_log_sig_backprop_cuda_" + suffix)
+        f.argtypes = (ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_int, c_bool)
         f.restype = c_int
         for name in ("transform_path_cuda_", "transform_path_backprop_cuda_"):
             f = getattr(lib, name + suffix)

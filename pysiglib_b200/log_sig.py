@@ -1,0 +1,156 @@
+"""``sig_to_log_sig``, its backward pass, and ``log_sig`` on the GPU, methods 0 and 1.
+
+Same names, parameters and layouts as the reference's operators (``pysiglib/log_sig.py:95-188,
+241-329, 331-470``, ``pysiglib/log_sig_backprop.py:30-137``):
+
+* method 0: the expanded tensor logarithm, in the layout of the signature (scalar slot 0);
+* method 1: its coordinates at the Lyndon words, ``log_sig_length`` values.
+
+Methods 2 (Lyndon basis) and 3 (from the path, without the signature) are not part of this
+build and raise ``NotImplementedError``."""
+from typing import Union
+
+import numpy as np
+import torch
+
+from . import load_cusig
+from .data_handlers import Output
+from .error_codes import err_msg
+from .param_checks import check_n_jobs, check_non_neg, check_type
+from .sig import _Sig, sig
+from .sig_length import aug_dim, infer_scalar_term, log_sig_length, sig_length
+
+
+def _check_method(method, where):
+    check_type(method, "method", int)
+    if method < 0 or method > 3:
+        raise ValueError("method must be one of 0, 1, 2 or 3. Got " + str(method) + " instead.")
+    if method == 3 and where != "log_sig":
+        raise ValueError("method=3 is not supported in %s. Use log_sig(path, degree, method=3) instead." % where)
+    if method >= 2:
+        raise NotImplementedError("log-signature method %d is not part of pysiglib_b200 (methods 0 and 1 are)" % method)
+
+
+def prepare_log_sig(dimension: int, degree: int, method: int, *, time_aug: bool = False, lead_lag: bool = False,
+                    use_disk: bool = False, device: str = "both"):
+    """Builds what ``method`` needs ahead of time (optional here: method 0 needs nothing, method 1's
+    table of Lyndon-word positions is otherwise built at the first call on each GPU)."""
+    check_type(dimension, "dimension", int)
+    check_non_neg(dimension, "dimension")
+    check_type(degree, "degree", int)
+    check_non_neg(degree, "degree")
+    _check_method(method, "log_sig")
+    check_type(time_aug, "time_aug", bool)
+    check_type(lead_lag, "lead_lag", bool)
+    if method == 0:
+        return
+    code = load_cusig.library().prepare_log_sig_cuda(aug_dim(dimension, time_aug, lead_lag), degree, method,
+                                                     bool(use_disk))
+    if code:
+        raise Exception("Error in pysiglib.prepare_log_sig: " + err_msg(code))
+
+
+def sig_to_log_sig(
+        sig: Union[np.ndarray, torch.Tensor],
+        dimension: int,
+        degree: int,
+        *,
+        time_aug: bool = False,
+        lead_lag: bool = False,
+        method: int = 1,
+        n_jobs: int = 1
+) -> Union[np.ndarray, torch.Tensor]:
+    """Log signature from the signature.
+
+    :param sig: ``(..., S)`` with or without the scalar term (inferred from the length).
+    :param dimension: dimension of the underlying path, before ``time_aug`` / ``lead_lag``.
+    :param method: 0 = expanded (result in the layout of ``sig``), 1 = Lyndon-word coordinates
+        (``log_sig_length`` values).
+    """
+    check_type(dimension, "dimension", int)
+    check_non_neg(dimension, "dimension")
+    check_type(degree, "degree", int)
+    check_non_neg(degree, "degree")
+    check_type(time_aug, "time_aug", bool)
+    check_type(lead_lag, "lead_lag", bool)
+    _check_method(method, "sig_to_log_sig")
+    d = aug_dim(dimension, time_aug, lead_lag)
+    a = _Sig(sig, "sig")
+    scalar_term = infer_scalar_term(a.array, dimension, degree, time_aug=time_aug, lead_lag=lead_lag)
+    out_len = log_sig_length(d, degree) if method else a.array.shape[-1]
+    result = Output(a, (out_len,))
+    if a.batch_size == 0:
+        return result.array
+    check_n_jobs(n_jobs)
+    code = load_cusig.fn("sig_to_log_sig_cuda", a.dtype)(a.pointer, result.pointer, a.batch_size, d, degree, method,
+                                                         scalar_term)
+    if code:
+        raise Exception("Error in pysiglib.sig_to_log_sig: " + err_msg(code))
+    return result.array
+
+
+def sig_to_log_sig_backprop(
+        sig: Union[np.ndarray, torch.Tensor],
+        log_sig_derivs: Union[np.ndarray, torch.Tensor],
+        dimension: int,
+        degree: int,
+        *,
+        time_aug: bool = False,
+        lead_lag: bool = False,
+        method: int = 1,
+        n_jobs: int = 1
+) -> Union[np.ndarray, torch.Tensor]:
+    """Backward pass of ``sig_to_log_sig``: ``dF/d log_sig`` (layout of the forward's result) in,
+    ``dF/d sig`` (layout of ``sig``, scalar slot 0) out."""
+    check_type(dimension, "dimension", int)
+    check_non_neg(dimension, "dimension")
+    check_type(degree, "degree", int)
+    check_non_neg(degree, "degree")
+    check_type(time_aug, "time_aug", bool)
+    check_type(lead_lag, "lead_lag", bool)
+    _check_method(method, "sig_to_log_sig_backprop")
+    d = aug_dim(dimension, time_aug, lead_lag)
+    a = _Sig(sig, "sig")
+    scalar_term = infer_scalar_term(a.array, dimension, degree, time_aug=time_aug, lead_lag=lead_lag)
+    g = _Sig(log_sig_derivs, "log_sig_derivs")
+    expected = log_sig_length(d, degree) if method else a.array.shape[-1]
+    if g.array.shape[-1] != expected:
+        raise ValueError("log_sig_derivs is of incorrect length. Expected %d, got %d" % (expected, g.array.shape[-1]))
+    if a.kind != g.kind:
+        raise ValueError("sig and log_sig_derivs must both be numpy arrays or both torch tensors")
+    if a.dtype != g.dtype:
+        raise ValueError("sig and log_sig_derivs must have the same dtype")
+    if a.batch_shape != g.batch_shape:
+        raise ValueError("sig and log_sig_derivs have different batch shapes")
+    if a.device != g.device:
+        raise ValueError("sig and log_sig_derivs must be on the same device")
+    result = Output(a, (a.array.shape[-1],))
+    if a.batch_size == 0:
+        return result.array
+    check_n_jobs(n_jobs)
+    code = load_cusig.fn("sig_to_log_sig_backprop_cuda", a.dtype)(a.pointer, result.pointer, g.pointer, a.batch_size, d,
+                                                                  degree, method, scalar_term)
+    if code:
+        raise Exception("Error in pysiglib.sig_to_log_sig_backprop: " + err_msg(code))
+    return result.array
+
+
+def log_sig(
+        path: Union[np.ndarray, torch.Tensor],
+        degree: int,
+        *,
+        time_aug: bool = False,
+        lead_lag: bool = False,
+        end_time: float = 1.,
+        method: int = 1,
+        scalar_term: bool = False,
+        correction=None,
+        n_jobs: int = 1
+) -> Union[np.ndarray, torch.Tensor]:
+    """Log signature of a path: ``sig`` followed by ``sig_to_log_sig`` (methods 0 and 1).
+    ``scalar_term`` only matters for method 0, whose result has the layout of the signature."""
+    _check_method(method, "log_sig")
+    sig_ = sig(path, degree, scalar_term=scalar_term, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time,
+               horner=True, correction=correction, n_jobs=n_jobs)
+    return sig_to_log_sig(sig_, path.shape[-1], degree, time_aug=time_aug, lead_lag=lead_lag, method=method,
+                          n_jobs=n_jobs)

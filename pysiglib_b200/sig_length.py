@@ -48,3 +48,32 @@ def infer_scalar_term(sig, dimension, degree, time_aug=False, lead_lag=False):
         return False
     raise ValueError("sig has incompatible length %d for dimension=%d, degree=%d (expected %d or %d)."
                      % (got, dimension, degree, full, full - 1))
+
+
+def _mobius(k):
+    result, p = 1, 2
+    while p * p <= k:
+        if k % p == 0:
+            k //= p
+            if k % p == 0:
+                return 0
+            result = -result
+        p += 1
+    return -result if k > 1 else result
+
+
+def log_sig_length(dimension, degree, *, time_aug=False, lead_lag=False):
+    """Number of coordinates of the degree-``degree`` log signature in a Lyndon basis: Witt's
+    formula ``sum_{i=1..N} (1/i) sum_{x | i} mu(i/x) d^x`` (reference:
+    ``pysiglib/sig_length.py:97-163``)."""
+    check_type(dimension, "dimension", int)
+    check_type(degree, "degree", int)
+    check_non_neg(dimension, "dimension")
+    check_non_neg(degree, "degree")
+    check_type(time_aug, "time_aug", bool)
+    check_type(lead_lag, "lead_lag", bool)
+    d = aug_dim(dimension, time_aug, lead_lag)
+    total = 0
+    for i in range(1, degree + 1):
+        total += sum(_mobius(i // x) * d ** x for x in range(1, i + 1) if i % x == 0) // i
+    return total

@@ -12,6 +12,9 @@ from ..sig import sig as sig_forward
 from ..sig import sig_combine as sig_combine_forward
 from ..sig import sig_combine_backprop
 from ..sig_backprop import sig_backprop
+from ..log_sig import sig_to_log_sig as sig_to_log_sig_forward
+from ..log_sig import log_sig as log_sig_forward
+from ..log_sig import sig_to_log_sig_backprop
 from ..sig_join import sig_join as sig_join_forward
 from ..sig_join import sig_join_backprop
 from ..transform_path import transform_path as transform_path_forward
@@ -135,3 +138,45 @@ def transform_path(path, *, time_aug: bool = False, lead_lag: bool = False, end_
 
 
 transform_path.__doc__ = transform_path_forward.__doc__
+
+
+class SigToLogSig(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, sig_, dimension, degree, time_aug, lead_lag, method, n_jobs):
+        out = sig_to_log_sig_forward(sig_, dimension, degree, time_aug=time_aug, lead_lag=lead_lag, method=method,
+                                     n_jobs=n_jobs)
+        ctx.save_for_backward(sig_)
+        ctx.args = (dimension, degree, time_aug, lead_lag, method, n_jobs)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        dimension, degree, time_aug, lead_lag, method, n_jobs = ctx.args
+        grad = sig_to_log_sig_backprop(ctx.saved_tensors[0], grad_output, dimension, degree, time_aug=time_aug,
+                                       lead_lag=lead_lag, method=method, n_jobs=n_jobs)
+        return grad, None, None, None, None, None, None
+
+
+def sig_to_log_sig(sig, dimension: int, degree: int, *, time_aug: bool = False, lead_lag: bool = False,
+                   method: int = 1, n_jobs: int = 1):
+    if not isinstance(sig, torch.Tensor):
+        return sig_to_log_sig_forward(sig, dimension, degree, time_aug=time_aug, lead_lag=lead_lag, method=method,
+                                      n_jobs=n_jobs)
+    return SigToLogSig.apply(sig, dimension, degree, time_aug, lead_lag, method, n_jobs)
+
+
+sig_to_log_sig.__doc__ = sig_to_log_sig_forward.__doc__
+
+
+def log_sig(path, degree: int, *, time_aug: bool = False, lead_lag: bool = False, end_time: float = 1.,
+            method: int = 1, scalar_term: bool = False, correction=None, n_jobs: int = 1):
+    if not isinstance(path, torch.Tensor):
+        return log_sig_forward(path, degree, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time, method=method,
+                               scalar_term=scalar_term, correction=correction, n_jobs=n_jobs)
+    sig_ = sig(path, degree, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time, scalar_term=scalar_term,
+               correction=correction, n_jobs=n_jobs)
+    return sig_to_log_sig(sig_, path.shape[-1], degree, time_aug=time_aug, lead_lag=lead_lag, method=method,
+                          n_jobs=n_jobs)
+
+
+log_sig.__doc__ = log_sig_forward.__doc__

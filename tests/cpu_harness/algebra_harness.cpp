@@ -121,6 +121,56 @@ void correction_backward(const T* path, uint64_t L, uint64_t d, uint64_t degree,
     for (uint64_t i = 0; i < d; ++i) out[i] = -g_next[i];
 }
 
+// Tensor logarithm in the phase order of sig_log.cu: R_k for k = N..2, then y = x - x (x) R_2.
+template <typename T>
+void run_log(const T* x, T* y, T* keep /* (N-1) vectors */, const Levels& lv) {
+    const uint64_t S = lv.total();
+    const uint32_t N = lv.degree;
+    const T* r_old = nullptr;
+    for (uint32_t k = N; k >= 2; --k) {
+        T* r_new = keep + uint64_t(k - 2) * S;
+        const T constant = T(1) / static_cast<T>(k);
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
+            T value = T(0);
+            if (t <= 1 + N - k) {
+                value = constant * x[j];
+                if (r_old) value -= nonunital_product_coeff(x, r_old, lv, t, w);
+            }
+            r_new[j] = value;
+        });
+        r_old = r_new;
+    }
+    for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
+        T value = x[j];
+        if (r_old && t >= 2) value -= nonunital_product_coeff(x, r_old, lv, t, w);
+        y[j] = value;
+    });
+}
+
+template <typename T>
+void run_log_backprop(const T* x, const T* dy, T* dx, const Levels& lv) {
+    const uint64_t S = lv.total();
+    const uint32_t N = lv.degree;
+    std::vector<T> keep(S * (N > 1 ? N - 1 : 1)), y(S), qa(S), qb(S), D(dy, dy + S);
+    for (uint64_t j = 0; j < S; ++j) dx[j] = dy[j];
+    if (N < 2) return;
+    run_log<T>(x, y.data(), keep.data(), lv);
+    const T* q = D.data();
+    T* q_new = qa.data();
+    for (uint32_t k = 1; k <= N; ++k) {
+        const T* r_next = k < N ? keep.data() + uint64_t(k - 1) * S : nullptr;
+        const T constant = T(1) / static_cast<T>(k);
+        for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
+            T add = k >= 2 ? q[j] * constant : T(0);
+            if (r_next) add -= nonunital_left_adjoint_coeff(q, r_next, lv, t, w);
+            dx[j] += add;
+            if (k < N) q_new[j] = -nonunital_right_adjoint_coeff(q, x, lv, t, w);
+        });
+        q = q_new;
+        q_new = q_new == qa.data() ? qb.data() : qa.data();
+    }
+}
+
 }  // namespace
 
 #define HARNESS(SUF, T)                                                                                               \
@@ -157,6 +207,14 @@ void correction_backward(const T* path, uint64_t L, uint64_t d, uint64_t degree,
         for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {                                               \
             linear_sig_adjoint_terms(v, dL[j], lv, t, w, [&](uint32_t letter, T value) { dv[letter] += value; });     \
         });                                                                                                           \
+    }                                                                                                                 \
+    extern "C" void alg_log_##SUF(const T* x, T* y, uint64_t dim, uint64_t degree) {                                  \
+        const Levels lv = make_levels(dim, degree);                                                                   \
+        std::vector<T> keep(lv.total() * degree);                                                                     \
+        run_log<T>(x, y, keep.data(), lv);                                                                            \
+    }                                                                                                                 \
+    extern "C" void alg_log_backprop_##SUF(const T* x, const T* dy, T* dx, uint64_t dim, uint64_t degree) {           \
+        run_log_backprop<T>(x, dy, dx, make_levels(dim, degree));                                                     \
     }                                                                                                                 \
     extern "C" void alg_correction_forward_##SUF(const T* path, uint64_t L, uint64_t d, uint64_t degree,              \
                                                  const T* corr, uint64_t corr_len, uint64_t seg_stride, T* out) {     \

@@ -96,6 +96,21 @@ def test_linear_sig_and_adjoint(harness, dim, degree, dtype):
     np.testing.assert_allclose(dv, want, **_tol(dtype))
 
 
+@pytest.mark.parametrize("dim,degree", SHAPES)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_tensor_log_and_its_adjoint(harness, dim, degree, dtype):
+    rng = np.random.default_rng(400 + dim * 10 + degree)
+    n = oracle.sig_length(dim, degree)
+    x = (rng.standard_normal(n) * 0.5).astype(dtype)
+    y = np.zeros(n, dtype=dtype)
+    _call(harness, "alg_log", dtype, x, y, dim, degree)
+    np.testing.assert_allclose(y, oracle.sig_to_log_sig(x, dim, degree, method=0), **_tol(dtype))
+    w = rng.standard_normal(n).astype(dtype)
+    dx = np.zeros(n, dtype=dtype)
+    _call(harness, "alg_log_backprop", dtype, x, w, dx, dim, degree)
+    np.testing.assert_allclose(dx, oracle.sig_to_log_sig_backprop(x, w, dim, degree, method=0), **_tol(dtype))
+
+
 @pytest.mark.parametrize("dim,degree,levels", [(1, 4, 3), (2, 3, 1), (2, 4, 3), (3, 3, 2)])
 @pytest.mark.parametrize("layout", ["constant", "per_segment"])
 @pytest.mark.parametrize("dtype", [np.float64, np.float32])

@@ -1,0 +1,129 @@
+"""GPU parity of ``sig_to_log_sig`` (+ backward) and ``log_sig`` for methods 0 and 1, against the
+CPU oracle (``oracle/sig_oracle_log.h``).  Tolerances: 1e-10 relative (float64), 1e-5 relative
+(float32), per coefficient relative to the largest magnitude of its level."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_grad_close, assert_sig_close
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+CASES = [(5, 1, 6), (7, 2, 1), (6, 2, 7), (4, 3, 4), (3, 5, 3), (2, 8, 3), (70000, 2, 3), (2, 16, 3)]
+
+
+def _sigs(seed, B, d, N, dtype, scalar_term):
+    rng = np.random.default_rng(seed)
+    path = (rng.standard_normal((B, 9, d)).cumsum(1) * 0.4).astype(dtype)
+    return oracle.sig(path, N, scalar_term=scalar_term)
+
+
+@pytest.mark.parametrize("B,d,N", CASES)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("scalar_term", [False, True])
+def test_expanded_log_and_backprop(B, d, N, dtype, scalar_term):
+    import pysiglib_b200
+    s = _sigs(B + d + N, B, d, N, dtype, scalar_term)
+    want = oracle.sig_to_log_sig(s, d, N, method=0)
+    st = torch.tensor(s, device="cuda")
+    got = pysiglib_b200.sig_to_log_sig(st, d, N, method=0)
+    assert got.shape == st.shape
+    off = 1 if scalar_term else 0
+    rtol = 1e-10 if dtype == np.float64 else 1e-5
+    assert_sig_close(got.cpu().numpy()[:, off:], want[:, off:], d, N, rtol)
+    if scalar_term:
+        assert torch.all(got[:, 0] == 0)
+    if B <= 64:
+        np.testing.assert_array_equal(pysiglib_b200.sig_to_log_sig(s, d, N, method=0), got.cpu().numpy())
+
+    w = np.random.default_rng(1).standard_normal(s.shape).astype(dtype)
+    want_g = oracle.sig_to_log_sig_backprop(s.astype(np.float64), w.astype(np.float64), d, N, method=0)
+    got_g = pysiglib_b200.sig_to_log_sig_backprop(st, torch.tensor(w, device="cuda"), d, N, method=0)
+    assert_grad_close(got_g.cpu().numpy()[:, None, :], want_g[:, None, :], 1e-10 if dtype == np.float64 else 1e-4)
+    if B <= 64:
+        host_g = pysiglib_b200.sig_to_log_sig_backprop(s, w, d, N, method=0)
+        assert_grad_close(host_g[:, None, :], want_g[:, None, :], 1e-10 if dtype == np.float64 else 1e-4)
+
+
+@pytest.mark.parametrize("B,d,N", CASES)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("scalar_term", [False, True])
+def test_lyndon_word_log_and_backprop(B, d, N, dtype, scalar_term):
+    import pysiglib_b200
+    s = _sigs(B + 2 * d + N, B, d, N, dtype, scalar_term)
+    want = oracle.sig_to_log_sig(s, d, N, method=1)
+    st = torch.tensor(s, device="cuda")
+    pysiglib_b200.prepare_log_sig(d, N, 1)
+    got = pysiglib_b200.sig_to_log_sig(st, d, N, method=1)
+    assert got.shape == (B, pysiglib_b200.log_sig_length(d, N)) == want.shape
+    # same coordinates as the expanded logarithm at the Lyndon words
+    full = pysiglib_b200.sig_to_log_sig(st, d, N, method=0)
+    idx = torch.tensor(oracle.lyndon_indices(d, N).astype(np.int64) - (0 if scalar_term else 1), device="cuda")
+    assert torch.equal(got, full[:, idx])
+    scale = np.abs(want).max(axis=1, keepdims=True)
+    tol = 1e-10 if dtype == np.float64 else 1e-5
+    assert np.all(np.abs(got.cpu().numpy() - want) <= tol * np.maximum(scale, 1e-300))
+
+    w = np.random.default_rng(2).standard_normal(want.shape).astype(dtype)
+    want_g = oracle.sig_to_log_sig_backprop(s.astype(np.float64), w.astype(np.float64), d, N, method=1)
+    got_g = pysiglib_b200.sig_to_log_sig_backprop(st, torch.tensor(w, device="cuda"), d, N, method=1)
+    assert_grad_close(got_g.cpu().numpy()[:, None, :], want_g[:, None, :], 1e-10 if dtype == np.float64 else 1e-4)
+
+
+@pytest.mark.parametrize("method", [0, 1])
+@pytest.mark.parametrize("flags", [(False, False), (True, False), (True, True)])
+def test_log_sig_from_path_and_autograd(method, flags):
+    from pysiglib_b200 import torch_api
+    import pysiglib_b200
+    ta, ll = flags
+    rng = np.random.default_rng(3)
+    path_np = (rng.standard_normal((4, 12, 2)).cumsum(1) * 0.3)
+    path = torch.tensor(path_np, device="cuda", requires_grad=True)
+    out = torch_api.log_sig(path, 3, time_aug=ta, lead_lag=ll, method=method)
+    D = (4 if ll else 2) + (1 if ta else 0)
+    want = oracle.sig_to_log_sig(oracle.sig(path_np, 3, time_aug=ta, lead_lag=ll), D, 3, method=method)
+    np.testing.assert_allclose(out.detach().cpu().numpy(), want, rtol=1e-9, atol=1e-12)
+    np.testing.assert_allclose(pysiglib_b200.log_sig(path_np, 3, time_aug=ta, lead_lag=ll, method=method), want,
+                               rtol=1e-9, atol=1e-12)
+    w = torch.tensor(rng.standard_normal(want.shape), device="cuda")
+    (out * w).sum().backward()
+    s = oracle.sig(path_np, 3, time_aug=ta, lead_lag=ll)
+    ds = oracle.sig_to_log_sig_backprop(s, w.cpu().numpy(), D, 3, method=method)
+    want_g = oracle.sig_backprop(path_np, s, ds, 3, time_aug=ta, lead_lag=ll)
+    assert_grad_close(path.grad.cpu().numpy(), want_g, 1e-9)
+
+
+def test_ito_correction_example_runs_through_log_sig():
+    # the use the reference documents for method 0 with a correction (pysiglib/log_sig.py:395-425)
+    import pysiglib_b200
+    d, N, n_steps = 2, 3, 50
+    dt = 1.0 / n_steps
+    rng = np.random.default_rng(42)
+    path = np.zeros((n_steps + 1, d))
+    path[1:] = np.cumsum(rng.normal(0, np.sqrt(dt), (n_steps, d)), axis=0)
+    corr = np.ascontiguousarray(np.broadcast_to((-0.5 * np.eye(d) * dt).reshape(1, -1), (n_steps, d * d)))
+    got = pysiglib_b200.log_sig(torch.tensor(path, device="cuda"), N, correction=torch.tensor(corr, device="cuda"),
+                                method=0)
+    want = oracle.sig_to_log_sig(oracle.sig(path, N, correction=corr), d, N, method=0)
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-9, atol=1e-12)
+
+
+def test_unbuilt_methods_and_errors():
+    import ctypes
+    import pysiglib_b200
+    from pysiglib_b200 import load_cusig
+    s = torch.zeros((2, 14), dtype=torch.float64, device="cuda")
+    with pytest.raises(NotImplementedError):
+        pysiglib_b200.sig_to_log_sig(s, 2, 3, method=2)
+    with pytest.raises(ValueError, match="method=3"):
+        pysiglib_b200.sig_to_log_sig(s, 2, 3, method=3)
+    lib = load_cusig.library()
+    p = lambda t: ctypes.cast(t.data_ptr(), ctypes.POINTER(ctypes.c_double))
+    out = torch.zeros_like(s)
+    assert lib.sig_to_log_sig_cuda_d(p(s), p(out), 2, 2, 3, 2, False) == 2
+    assert "not part of this build" in load_cusig.last_error_message()
+    assert lib.sig_to_log_sig_cuda_d(p(s), p(out), 2, 2, 0, 0, False) == 2
+    assert "degree 0" in load_cusig.last_error_message()
+    assert lib.prepare_log_sig_cuda(2, 3, 1, False) == 0
+    assert lib.prepare_log_sig_cuda(2, 3, 2, False) == 2

@@ -171,3 +171,36 @@ def test_sig_combine_argument_contract():
     assert psl.sig_combine(np.zeros((0, 14)), np.zeros((0, 14)), 2, 3).shape == (0, 14)
     d1, d2 = psl.sig_combine_backprop(np.zeros((0, 15)), np.zeros((0, 15)), np.zeros((0, 15)), 2, 3)
     assert d1.shape == d2.shape == (0, 15)
+
+
+def test_log_sig_argument_contract():
+    import inspect
+    assert list(inspect.signature(psl.sig_to_log_sig).parameters) == ["sig", "dimension", "degree", "time_aug",
+                                                                       "lead_lag", "method", "n_jobs"]
+    assert list(inspect.signature(psl.sig_to_log_sig_backprop).parameters) == [
+        "sig", "log_sig_derivs", "dimension", "degree", "time_aug", "lead_lag", "method", "n_jobs"]
+    assert list(inspect.signature(psl.log_sig).parameters) == ["path", "degree", "time_aug", "lead_lag", "end_time",
+                                                                "method", "scalar_term", "correction", "n_jobs"]
+    assert list(inspect.signature(psl.prepare_log_sig).parameters) == ["dimension", "degree", "method", "time_aug",
+                                                                        "lead_lag", "use_disk", "device"]
+    # Witt's formula (reference tests/test_sig_length.py uses the same closed form)
+    assert [psl.log_sig_length(2, n) for n in range(1, 7)] == [2, 3, 5, 8, 14, 23]
+    assert psl.log_sig_length(3, 4) == 32 and psl.log_sig_length(2, 3, time_aug=True) == 14
+    assert psl.log_sig_length(2, 3, lead_lag=True) == psl.log_sig_length(4, 3) == 4 + 6 + 20
+    s = np.zeros((3, 14))
+    with pytest.raises(ValueError, match="one of 0, 1, 2 or 3"):
+        psl.sig_to_log_sig(s, 2, 3, method=4)
+    with pytest.raises(ValueError, match="method=3"):
+        psl.sig_to_log_sig(s, 2, 3, method=3)
+    with pytest.raises(NotImplementedError):
+        psl.sig_to_log_sig(s, 2, 3, method=2)
+    with pytest.raises(TypeError):
+        psl.sig_to_log_sig(s, 2, 3, method=1.0)
+    with pytest.raises(ValueError):
+        psl.sig_to_log_sig(np.zeros((3, 13)), 2, 3)
+    with pytest.raises(ValueError, match="incorrect length"):
+        psl.sig_to_log_sig_backprop(s, np.zeros((3, 4)), 2, 3, method=1)
+    assert psl.sig_to_log_sig(np.zeros((0, 14)), 2, 3).shape == (0, 5)
+    assert psl.sig_to_log_sig(np.zeros((0, 15)), 2, 3, method=0).shape == (0, 15)
+    assert psl.sig_to_log_sig_backprop(np.zeros((0, 14)), np.zeros((0, 5)), 2, 3).shape == (0, 14)
+    psl.prepare_log_sig(2, 3, 0)
