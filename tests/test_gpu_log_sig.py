@@ -13,6 +13,18 @@ pytestmark = pytest.mark.gpu
 CASES = [(5, 1, 6), (7, 2, 1), (6, 2, 7), (4, 3, 4), (3, 5, 3), (2, 8, 3), (70000, 2, 3), (2, 16, 3)]
 
 
+def _assert_log_close(got, want, sig, d, N, rtol):
+    """Per coefficient, relative to the largest magnitude of its level in the logarithm or in the
+    signature it was computed from (the logarithm cancels terms of the size of the signature's)."""
+    start = 0
+    for k in range(1, N + 1):
+        sl = slice(start, start + d ** k)
+        start += d ** k
+        floor = np.maximum(np.abs(want[:, sl]).max(axis=1, keepdims=True), np.abs(sig[:, sl]).max(axis=1, keepdims=True))
+        err = np.abs(got[:, sl].astype(np.float64) - want[:, sl]) / np.maximum(np.maximum(np.abs(want[:, sl]), floor), 1e-300)
+        assert err.max() <= rtol, "log level %d: max scaled rel err %.3e > %.1e" % (k, err.max(), rtol)
+
+
 def _sigs(seed, B, d, N, dtype, scalar_term):
     rng = np.random.default_rng(seed)
     path = (rng.standard_normal((B, 9, d)).cumsum(1) * 0.4).astype(dtype)
@@ -31,7 +43,7 @@ def test_expanded_log_and_backprop(B, d, N, dtype, scalar_term):
     assert got.shape == st.shape
     off = 1 if scalar_term else 0
     rtol = 1e-10 if dtype == np.float64 else 1e-5
-    assert_sig_close(got.cpu().numpy()[:, off:], want[:, off:], d, N, rtol)
+    _assert_log_close(got.cpu().numpy()[:, off:], want[:, off:], s[:, off:], d, N, rtol)
     if scalar_term:
         assert torch.all(got[:, 0] == 0)
     if B <= 64:
@@ -61,9 +73,11 @@ def test_lyndon_word_log_and_backprop(B, d, N, dtype, scalar_term):
     full = pysiglib_b200.sig_to_log_sig(st, d, N, method=0)
     idx = torch.tensor(oracle.lyndon_indices(d, N).astype(np.int64) - (0 if scalar_term else 1), device="cuda")
     assert torch.equal(got, full[:, idx])
-    scale = np.abs(want).max(axis=1, keepdims=True)
-    tol = 1e-10 if dtype == np.float64 else 1e-5
-    assert np.all(np.abs(got.cpu().numpy() - want) <= tol * np.maximum(scale, 1e-300))
+    want_full = oracle.sig_to_log_sig(s, d, N, method=0)
+    off = 1 if scalar_term else 0
+    _assert_log_close(full.cpu().numpy()[:, off:], want_full[:, off:], s[:, off:], d, N, 1e-10 if dtype == np.float64 else 1e-5)
+    np.testing.assert_array_equal(want, np.concatenate([np.zeros((B, 1), dtype=dtype), want_full[:, off:]], axis=1)
+                                  [:, oracle.lyndon_indices(d, N).astype(np.int64)])
 
     w = np.random.default_rng(2).standard_normal(want.shape).astype(dtype)
     want_g = oracle.sig_to_log_sig_backprop(s.astype(np.float64), w.astype(np.float64), d, N, method=1)
