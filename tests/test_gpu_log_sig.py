@@ -14,13 +14,16 @@ CASES = [(5, 1, 6), (7, 2, 1), (6, 2, 7), (4, 3, 4), (3, 5, 3), (2, 8, 3), (7000
 
 
 def _assert_log_close(got, want, sig, d, N, rtol):
-    """Per coefficient, relative to the largest magnitude of its level in the logarithm or in the
-    signature it was computed from (the logarithm cancels terms of the size of the signature's)."""
+    """Per coefficient, relative to the largest term the series log(1+x) = x - x^2/2 + .. sums at
+    that level: the level of the signature itself and the k-th power of its first level over k
+    (the logarithm is what is left after these cancel)."""
     start = 0
+    first = np.abs(sig[:, :d]).max(axis=1, keepdims=True).astype(np.float64)
     for k in range(1, N + 1):
         sl = slice(start, start + d ** k)
         start += d ** k
         floor = np.maximum(np.abs(want[:, sl]).max(axis=1, keepdims=True), np.abs(sig[:, sl]).max(axis=1, keepdims=True))
+        floor = np.maximum(floor, first ** k / k)
         err = np.abs(got[:, sl].astype(np.float64) - want[:, sl]) / np.maximum(np.maximum(np.abs(want[:, sl]), floor), 1e-300)
         assert err.max() <= rtol, "log level %d: max scaled rel err %.3e > %.1e" % (k, err.max(), rtol)
 
