@@ -204,6 +204,17 @@ def run_neighbour_op(args):
             fwd, bwd = (lambda: psl.sig_join(a, v, d, N)), (lambda: psl.sig_join_backprop(g, a, v, d, N))
             fwd_bytes, bwd_bytes = 2 * B * S * 4, 3 * B * S * 4
         workload = "%s: float32, B=%d signatures of d=%d, degree %d (S=%d)" % (args.op, B, d, N, S)
+    elif args.op == "sig_to_log_sig":
+        B, d, N = args.batch or 4096, 16, 4
+        S = sum(d ** k for k in range(1, N + 1))
+        a = rnd(B, S) * 0.1
+        M = psl.log_sig_length(d, N)
+        g = rnd(B, M)
+        psl.prepare_log_sig(d, N, 1)
+        fwd = lambda: psl.sig_to_log_sig(a, d, N, method=1)
+        bwd = lambda: psl.sig_to_log_sig_backprop(a, g, d, N, method=1)
+        fwd_bytes, bwd_bytes = (B * S + B * M) * 4, (2 * B * S + B * M) * 4
+        workload = "sig_to_log_sig method 1: float32, B=%d signatures of d=%d, degree %d (S=%d -> %d Lyndon coordinates)" % (B, d, N, S, M)
     elif args.op == "transform_path":
         B, L, d = args.batch or 4096, args.length or 4096, 16
         x = rnd(B, L, d)
@@ -271,7 +282,7 @@ def _time_ms(torch, fn, warmup, steps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="sig", choices=["sig", "sig_combine", "sig_join", "transform_path", "correction"],
+    ap.add_argument("--op", default="sig", choices=["sig", "sig_combine", "sig_join", "sig_to_log_sig", "transform_path", "correction"],
                     help="sig (default) is the headline path; the others time one neighbouring operator on one GPU")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)

@@ -25,6 +25,16 @@ unsigned grid_1d(uint64_t work, int threads) {
     return static_cast<unsigned>(blocks);
 }
 
+// Grid for kernels that give one thread to each of `per_item` elements and walk the batch along
+// grid.y with stride gridDim.y: enough CTAs to fill the GPU several times over, but not one tiny
+// CTA per (element block, batch entry) when the batch is large.
+dim3 batched_grid(uint64_t per_item, uint64_t batch, int threads) {
+    const unsigned gx = grid_1d(per_item, threads);
+    const uint64_t target = 148ull * 64;  // CTAs
+    const uint64_t gy = std::max<uint64_t>(1, std::min<uint64_t>(std::min<uint64_t>(batch, 65535), (target + gx - 1) / gx));
+    return dim3(gx, static_cast<unsigned>(gy));
+}
+
 Levels checked_levels(uint64_t dim, uint64_t degree, const char* who) {
     if (degree > kAlgebraMaxDegree)
         throw std::invalid_argument(std::string(who) + ": degree above 64 is not supported");

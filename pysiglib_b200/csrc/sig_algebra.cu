@@ -72,7 +72,7 @@ template <typename T>
 void launch_linear_sig(const T* disp, T* out_level1, uint64_t out_stride, const Levels& lv, uint64_t batch,
                        bool write_scalar, cudaStream_t stream) {
     if (lv.degree == 0 || batch == 0) return;
-    const dim3 grid(grid_1d(lv.total(), kThreads), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
+    const dim3 grid = batched_grid(lv.total(), batch, kThreads);
     linear_sig_kernel<T><<<grid, kThreads, 0, stream>>>(disp, out_level1, out_stride, lv, batch, write_scalar);
     check_launch("linear_sig kernel");
 }
@@ -508,7 +508,7 @@ void transform_path_entry(const T* data_in, T* data_out, uint64_t batch, uint64_
     const uint64_t n_out = checked_mul(checked_mul(batch, s.len, "transformed path"), s.dim, "transformed path");
     if (s.len * s.dim >= (1ull << 32)) throw std::invalid_argument("transform_path_cuda: path too large");
     auto run = [&](const T* in, T* o, cudaStream_t st) {
-        const dim3 grid(grid_1d(s.len * s.dim, kThreads), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
+        const dim3 grid = batched_grid(s.len * s.dim, batch, kThreads);
         transform_path_kernel<T><<<grid, kThreads, 0, st>>>(in, o, batch, uint32_t(dimension), uint32_t(length),
                                                             uint32_t(s.dim), uint32_t(s.len), time_aug, lead_lag, dt);
         check_launch("transform_path kernel");
@@ -537,7 +537,7 @@ void transform_path_backprop_entry(const T* derivs, T* data_out, uint64_t batch,
     const uint64_t n_out = batch * length * dimension;
     if (s.len * s.dim >= (1ull << 32)) throw std::invalid_argument("transform_path_backprop_cuda: path too large");
     auto run = [&](const T* g, T* o, cudaStream_t st) {
-        const dim3 grid(grid_1d(length * dimension, kThreads), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
+        const dim3 grid = batched_grid(length * dimension, batch, kThreads);
         transform_path_backprop_kernel<T><<<grid, kThreads, 0, st>>>(g, o, batch, uint32_t(dimension), uint32_t(length),
                                                                      uint32_t(s.dim), uint32_t(s.len), lead_lag);
         check_launch("transform_path_backprop kernel");

@@ -120,9 +120,7 @@ __global__ void log_adjoint_kernel(const T* __restrict__ x, uint64_t x_stride, c
     }
 }
 
-dim3 coeff_grid(uint32_t count, uint64_t batch) {
-    return dim3(grid_1d(count, kThreads), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
-}
+dim3 coeff_grid(uint32_t count, uint64_t batch) { return batched_grid(count, batch, kThreads); }
 
 // ----- Lyndon words ----------------------------------------------------------------------------
 
