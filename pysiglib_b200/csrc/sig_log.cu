@@ -122,6 +122,13 @@ __global__ void log_adjoint_kernel(const T* __restrict__ x, uint64_t x_stride, c
 
 dim3 coeff_grid(uint32_t count, uint64_t batch) { return batched_grid(count, batch, kThreads); }
 
+// The adjoint sums are long for the few low-level coefficients (d^(N-1) terms for a letter) and
+// empty for the top level: give every signature its own CTAs so that the long threads of different
+// signatures run side by side instead of one after another.
+dim3 adjoint_grid(uint32_t count, uint64_t batch) {
+    return dim3(grid_1d(count, kThreads), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
+}
+
 // ----- Lyndon words ----------------------------------------------------------------------------
 
 // Positions (inside a scalar-free signature) of the Lyndon words of length 1..degree over `dim`
@@ -319,7 +326,7 @@ void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs
             for (uint32_t k = 1; k <= N; ++k) {
                 // the product at this step has right operand R_{k+1} (none for k == N)
                 const T* r_next = k < N ? keep + uint64_t(k - 1) * vec : nullptr;
-                log_adjoint_kernel<T><<<coeff_grid(lv.total(), count), kThreads, 0, st>>>(
+                log_adjoint_kernel<T><<<adjoint_grid(lv.total(), count), kThreads, 0, st>>>(
                     x, stride, q, r_next, k < N ? q_new : nullptr, dsig, stride, lv, count, k);
                 check_launch("tensor log backward kernel");
                 q = q_new;
