@@ -124,6 +124,25 @@ int transform_path_backprop_cuda_f(const float* derivs, float* data_out, uint64_
 int transform_path_backprop_cuda_d(const double* derivs, double* data_out, uint64_t batch_size, uint64_t dimension,
                                    uint64_t length, bool time_aug, bool lead_lag, double end_time);
 
+/* Signature coefficients at given words only.  `multi_idx` lists the letters of all words back
+ * to back, `degrees` their lengths (uint64 arrays, device or host memory); with `prefixes` every
+ * non-empty word contributes the coefficients of all its prefixes, else one value per word (the
+ * empty word gives 1).  `dimension` is the dimension of `path` as passed: no transform is applied.
+ * The backward takes the forward result computed with prefixes (`coefs`) and the adjoints in the
+ * same layout (`derivs`) and writes the gradient with respect to `path`.  Words up to 32 letters.
+ * Replaces: siglib/cusig/cusig.h:468-470, 492-494 (siglib/cusig/cu_sig_coef.cu); bound by
+ *           pysiglib/load_siglib.py:471-482.  Synchronous; device or host pointers. */
+int sig_coef_cuda_f(const float* path, float* out, const uint64_t* multi_idx, uint64_t num_multi_idx,
+                    const uint64_t* degrees, uint64_t batch_size, uint64_t dimension, uint64_t length, bool prefixes);
+int sig_coef_cuda_d(const double* path, double* out, const uint64_t* multi_idx, uint64_t num_multi_idx,
+                    const uint64_t* degrees, uint64_t batch_size, uint64_t dimension, uint64_t length, bool prefixes);
+int sig_coef_backprop_cuda_f(const float* path, float* out, const float* coefs, const float* derivs,
+                             const uint64_t* multi_idx, uint64_t num_multi_idx, const uint64_t* degrees,
+                             uint64_t batch_size, uint64_t dimension, uint64_t length);
+int sig_coef_backprop_cuda_d(const double* path, double* out, const double* coefs, const double* derivs,
+                             const uint64_t* multi_idx, uint64_t num_multi_idx, const uint64_t* degrees,
+                             uint64_t batch_size, uint64_t dimension, uint64_t length);
+
 /* Signature -> log signature.  method 0: expanded tensor logarithm in the layout of `sig` (scalar
  * slot 0); method 1: its coordinates at the Lyndon words of length <= degree, by length then
  * lexicographically (log_sig_length values per signature).  Methods 2 and 3 return code 2.

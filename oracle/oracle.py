@@ -17,7 +17,7 @@ _LIB = None
 
 def build(force=False):
     """Compile the oracle with gcc (idempotent)."""
-    src = [os.path.join(_HERE, f) for f in ("sig_oracle.c", "sig_oracle_impl.h", "sig_oracle_algebra.h", "sig_oracle_log.h")]
+    src = [os.path.join(_HERE, f) for f in ("sig_oracle.c", "sig_oracle_impl.h", "sig_oracle_algebra.h", "sig_oracle_log.h", "sig_oracle_coef.h")]
     if (not force and os.path.exists(_LIB_PATH)
             and all(os.path.getmtime(_LIB_PATH) >= os.path.getmtime(s) for s in src)):
         return _LIB_PATH
@@ -56,6 +56,10 @@ def _lib():
                     ("oracle_tensor_exp_backprop_", [ptr, ptr, ptr, u64, u64]),
                     ("oracle_sig_to_log_sig_", [ptr, ptr, u64, u64, u64, ci, ci]),
                     ("oracle_sig_to_log_sig_backprop_", [ptr, ptr, ptr, u64, u64, u64, ci, ci]),
+                    ("oracle_sig_coef_", [ptr, ptr, ctypes.POINTER(u64), u64, ctypes.POINTER(u64), u64, u64, u64, ci, ci,
+                                          real, ci]),
+                    ("oracle_sig_coef_backprop_", [ptr, ptr, ptr, ptr, ctypes.POINTER(u64), u64, ctypes.POINTER(u64),
+                                                   u64, u64, u64, ci, ci, real]),
                     ("oracle_linear_sig_", [ptr, ptr, u64, u64, u64, ci]),
                     ("oracle_sig_join_", [ptr, ptr, ptr, u64, u64, u64, ci, ci]),
                     ("oracle_sig_join_backprop_", [ptr, ptr, ptr, ptr, ptr, u64, u64, u64, ci, ci])):
@@ -334,3 +338,50 @@ def sig_to_log_sig_backprop(sig_, log_sig_derivs, dim, degree, method=1):
     if rc:
         raise RuntimeError("oracle_sig_to_log_sig_backprop failed with code %d" % rc)
     return out.reshape(a.shape)
+
+
+def _words(words):
+    words = [words] if isinstance(words, tuple) else list(words)
+    flat = np.array([i for w in words for i in w] + [0], dtype=np.uint64)
+    degrees = np.array([len(w) for w in words] + [0], dtype=np.uint64)
+    return words, flat, degrees
+
+
+def sig_coef(path, words, *, time_aug=False, lead_lag=False, end_time=1.0, prefixes=False):
+    """Oracle signature coefficients of ``path`` (B, L, d) or (L, d) at the given word(s)."""
+    path = np.ascontiguousarray(path)
+    single = path.ndim == 2
+    p3 = path[None] if single else path
+    B, L, d = p3.shape
+    suf, real = _suffix(p3)
+    words, flat, degrees = _words(words)
+    n_out = sum((len(w) if (prefixes and w) else 1) for w in words)
+    out = np.empty((B, n_out), dtype=p3.dtype)
+    ptr, u64p = ctypes.POINTER(real), ctypes.POINTER(ctypes.c_uint64)
+    rc = getattr(_lib(), "oracle_sig_coef_" + suf)(
+        p3.ctypes.data_as(ptr), out.ctypes.data_as(ptr), flat.ctypes.data_as(u64p), len(words),
+        degrees.ctypes.data_as(u64p), B, d, L, int(time_aug), int(lead_lag), real(end_time), int(prefixes))
+    if rc:
+        raise RuntimeError("oracle_sig_coef failed with code %d" % rc)
+    return out[0] if single else out
+
+
+def sig_coef_backprop(path, words, coefs, derivs, *, time_aug=False, lead_lag=False, end_time=1.0):
+    """Oracle gradient w.r.t. the path; ``coefs`` / ``derivs`` in the prefixes=True layout."""
+    path = np.ascontiguousarray(path)
+    single = path.ndim == 2
+    p3 = path[None] if single else path
+    B, L, d = p3.shape
+    suf, real = _suffix(p3)
+    words, flat, degrees = _words(words)
+    c2 = np.ascontiguousarray(coefs, dtype=p3.dtype).reshape(B, -1)
+    g2 = np.ascontiguousarray(derivs, dtype=p3.dtype).reshape(B, -1)
+    out = np.empty_like(p3)
+    ptr, u64p = ctypes.POINTER(real), ctypes.POINTER(ctypes.c_uint64)
+    rc = getattr(_lib(), "oracle_sig_coef_backprop_" + suf)(
+        p3.ctypes.data_as(ptr), out.ctypes.data_as(ptr), c2.ctypes.data_as(ptr), g2.ctypes.data_as(ptr),
+        flat.ctypes.data_as(u64p), len(words), degrees.ctypes.data_as(u64p), B, d, L, int(time_aug), int(lead_lag),
+        real(end_time))
+    if rc:
+        raise RuntimeError("oracle_sig_coef_backprop failed with code %d" % rc)
+    return out[0] if single else out

@@ -39,6 +39,7 @@ uint64_t oracle_sig_length(uint64_t dim, uint64_t degree) {
 #include "sig_oracle_impl.h"
 #include "sig_oracle_algebra.h"
 #include "sig_oracle_log.h"
+#include "sig_oracle_coef.h"
 #undef REAL
 #undef SUF
 #undef FMA
@@ -49,6 +50,7 @@ uint64_t oracle_sig_length(uint64_t dim, uint64_t degree) {
 #include "sig_oracle_impl.h"
 #include "sig_oracle_algebra.h"
 #include "sig_oracle_log.h"
+#include "sig_oracle_coef.h"
 #undef REAL
 #undef SUF
 #undef FMA

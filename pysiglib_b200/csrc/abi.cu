@@ -107,7 +107,7 @@ void sig_backprop_sharded(const T* path, T* out, const T* sig_derivs, const T* s
 int stub_not_built(const char* name) noexcept {
     clear_last_error();
     std::string msg = std::string(name) +
-        " is not part of this build of libcusig (it serves the signature, sig_backprop, sig_combine, sig_join, linear_sig, transform_path and sig_to_log_sig families)";
+        " is not part of this build of libcusig (it serves the signature, sig_backprop, sig_combine, sig_join, linear_sig, transform_path, sig_coef and sig_to_log_sig families)";
     set_last_error(msg.c_str());
     return 10;
 }
@@ -216,6 +216,19 @@ SIG_API int sig_combine_backprop_cuda_d(const double* sig_combined_deriv, double
                                                    bool scalar_term) {                                                \
         SIG_SAFE_CALL(sig_to_log_sig_backprop_entry<T>(sig, out, log_sig_derivs, batch_size, dimension, degree,       \
                                                        method, scalar_term, sync_options()));                         \
+    }                                                                                                                 \
+    SIG_API int sig_coef_cuda_##SUF(const T* path, T* out, const uint64_t* multi_idx, uint64_t num_multi_idx,         \
+                                    const uint64_t* degrees, uint64_t batch_size, uint64_t dimension,                 \
+                                    uint64_t length, bool prefixes) {                                                 \
+        SIG_SAFE_CALL(sig_coef_entry<T>(path, out, multi_idx, num_multi_idx, degrees, batch_size, dimension, length,  \
+                                        prefixes, sync_options()));                                                   \
+    }                                                                                                                 \
+    SIG_API int sig_coef_backprop_cuda_##SUF(const T* path, T* out, const T* coefs, const T* derivs,                  \
+                                             const uint64_t* multi_idx, uint64_t num_multi_idx,                       \
+                                             const uint64_t* degrees, uint64_t batch_size, uint64_t dimension,        \
+                                             uint64_t length) {                                                       \
+        SIG_SAFE_CALL(sig_coef_backprop_entry<T>(path, out, coefs, derivs, multi_idx, num_multi_idx, degrees,         \
+                                                 batch_size, dimension, length, sync_options()));                     \
     }
 SIG_ALGEBRA_EXPORTS(f, float)
 SIG_ALGEBRA_EXPORTS(d, double)
@@ -348,7 +361,6 @@ SIG_STUB_PAIR(log_sig_combine_cuda) SIG_STUB_PAIR(log_sig_combine_backprop_cuda)
 SIG_STUB_PAIR(log_sig_from_path_cuda) SIG_STUB_PAIR(log_sig_from_path_backprop_cuda)
 SIG_STUB_PAIR(log_sig_join_cuda) SIG_STUB_PAIR(log_sig_join_backprop_cuda)
 SIG_STUB_PAIR(logsig_to_sig_cuda) SIG_STUB_PAIR(logsig_to_sig_backprop_cuda)
-SIG_STUB_PAIR(sig_coef_cuda) SIG_STUB_PAIR(sig_coef_backprop_cuda)
 SIG_STUB_PAIR(sig_kernel_cuda) SIG_STUB_PAIR(sig_kernel_backprop_cuda)
 SIG_STUB_PAIR(sig_kernel_poly_cuda) SIG_STUB_PAIR(sig_kernel_poly_backprop_cuda)
 SIG_STUB_PAIR(branched_sig_cuda) SIG_STUB_PAIR(branched_sig_backprop_cuda)

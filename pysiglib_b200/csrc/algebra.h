@@ -72,6 +72,19 @@ void prepare_log_sig_entry(uint64_t dimension, uint64_t degree, int method);
 uint64_t log_sig_length_host(uint64_t dimension, uint64_t degree);
 void release_log_sig_tables() noexcept;
 
+// Coefficients of the signature at given words only (one thread per path and word), and the
+// gradient w.r.t. the path given the adjoints of all prefix coefficients.  multi_idx / degrees
+// (uint64, device or host memory) list the letters of all words back to back and the word lengths;
+// `dimension` is the dimension of `path` as passed (no transforms here).  Replace sig_coef_cuda_ /
+// sig_coef_backprop_cuda_ (siglib/cusig/cu_sig_coef.cu).
+template <typename T>
+void sig_coef_entry(const T* path, T* out, const uint64_t* multi_idx, uint64_t num_multi_idx, const uint64_t* degrees,
+                    uint64_t batch, uint64_t dimension, uint64_t length, bool prefixes, const CallOptions& opt);
+template <typename T>
+void sig_coef_backprop_entry(const T* path, T* out, const T* coefs, const T* derivs, const uint64_t* multi_idx,
+                             uint64_t num_multi_idx, const uint64_t* degrees, uint64_t batch, uint64_t dimension,
+                             uint64_t length, const CallOptions& opt);
+
 // Materialises the time-augmented / lead-lag path, and the adjoint of that map.  Replace
 // transform_path_cuda_ and transform_path_backprop_cuda_ (siglib/cusig/cu_path_transforms.cu:100-205).
 template <typename T>

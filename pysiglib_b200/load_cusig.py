@@ -87,6 +87,13 @@ def _bind(lib):
         f = getattr(lib, "sig_join_backprop_cuda_" + suffix)
         f.argtypes = (ptr, ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_bool, c_bool)
         f.restype = c_int
+        u64p = POINTER(c_uint64)
+        f = getattr(lib, "sig_coef_cuda_" + suffix)
+        f.argtypes = (ptr, ptr, u64p, c_uint64, u64p, c_uint64, c_uint64, c_uint64, c_bool)
+        f.restype = c_int
+        f = getattr(lib, "sig_coef_backprop_cuda_" + suffix)
+        f.argtypes = (ptr, ptr, ptr, ptr, u64p, c_uint64, u64p, c_uint64, c_uint64, c_uint64)
+        f.restype = c_int
         f = getattr(lib, "sig_to_log_sig_cuda_" + suffix)
         f.argtypes = (ptr, ptr, c_uint64, c_uint64, c_uint64, c_int, c_bool)
         f.restype = c_int

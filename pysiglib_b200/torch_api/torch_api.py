@@ -15,6 +15,8 @@ from ..sig_backprop import sig_backprop
 from ..log_sig import sig_to_log_sig as sig_to_log_sig_forward
 from ..log_sig import log_sig as log_sig_forward
 from ..log_sig import sig_to_log_sig_backprop
+from ..sig_coef import sig_coef as sig_coef_forward
+from ..sig_coef import sig_coef_backprop
 from ..sig_join import sig_join as sig_join_forward
 from ..sig_join import sig_join_backprop
 from ..transform_path import transform_path as transform_path_forward
@@ -180,3 +182,45 @@ def log_sig(path, degree: int, *, time_aug: bool = False, lead_lag: bool = False
 
 
 log_sig.__doc__ = log_sig_forward.__doc__
+
+
+def _coef_from_prefixes(words, coef, prefixes):
+    """The forward always computes all prefixes (the backward needs them); keep the last of each word."""
+    if prefixes:
+        return coef
+    if isinstance(words, tuple):
+        words = [words]
+    last, pos = [], 0
+    for w in words:
+        pos += max(len(w), 1)
+        last.append(pos - 1)
+    return coef[..., last].contiguous()
+
+
+class SigCoef(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, path, words, time_aug, lead_lag, end_time, n_jobs):
+        coefs = sig_coef_forward(path, words, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time, prefixes=True,
+                                 n_jobs=n_jobs)
+        ctx.save_for_backward(coefs, path)
+        ctx.args = (words, time_aug, lead_lag, end_time, n_jobs)
+        return coefs
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        coefs, path = ctx.saved_tensors
+        words, time_aug, lead_lag, end_time, n_jobs = ctx.args
+        grad = sig_coef_backprop(path, words, coefs, grad_output, time_aug=time_aug, lead_lag=lead_lag,
+                                 end_time=end_time, n_jobs=n_jobs)
+        return grad, None, None, None, None, None
+
+
+def sig_coef(path, words, *, time_aug: bool = False, lead_lag: bool = False, end_time: float = 1.,
+             prefixes: bool = False, n_jobs: int = 1):
+    if not isinstance(path, torch.Tensor):
+        return sig_coef_forward(path, words, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time,
+                                prefixes=prefixes, n_jobs=n_jobs)
+    return _coef_from_prefixes(words, SigCoef.apply(path, words, time_aug, lead_lag, end_time, n_jobs), prefixes)
+
+
+sig_coef.__doc__ = sig_coef_forward.__doc__

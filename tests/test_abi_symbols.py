@@ -47,7 +47,7 @@ def test_reference_loader_symbols_are_present():
 
 def test_stub_reports_a_clean_error_without_a_gpu():
     lib = load_cusig.library()
-    assert lib.sig_coef_cuda_f() == 10
+    assert lib.sig_kernel_cuda_f() == 10
     assert "not part of this build" in load_cusig.last_error_message()
     assert lib.sigb200_sig_length(3, 4) == 121
     assert lib.sigb200_sig_length(2, 64) == 0  # overflow

@@ -239,7 +239,7 @@ def test_error_codes_and_messages():
     assert "prefix" in load_cusig.last_error_message()
     assert lib.sig_backprop_cuda_d(dptr, optr, optr, optr, 1, 0, 4, 2, False, False, 1.0, False, None, 0, 0, 0) == 2
     # symbols outside the served path exist and fail cleanly
-    assert lib.sig_coef_cuda_d() == 10
+    assert lib.sig_kernel_cuda_d() == 10
     assert "not part of this build" in load_cusig.last_error_message()
 
 

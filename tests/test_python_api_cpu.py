@@ -204,3 +204,29 @@ def test_log_sig_argument_contract():
     assert psl.sig_to_log_sig(np.zeros((0, 15)), 2, 3, method=0).shape == (0, 15)
     assert psl.sig_to_log_sig_backprop(np.zeros((0, 14)), np.zeros((0, 5)), 2, 3).shape == (0, 14)
     psl.prepare_log_sig(2, 3, 0)
+
+
+def test_sig_coef_argument_contract():
+    import inspect
+    assert list(inspect.signature(psl.sig_coef).parameters) == ["path", "words", "time_aug", "lead_lag", "end_time",
+                                                                 "prefixes", "n_jobs"]
+    assert list(inspect.signature(psl.sig_coef_backprop).parameters) == ["path", "words", "coefs", "derivs", "time_aug",
+                                                                          "lead_lag", "end_time", "n_jobs"]
+    x = np.zeros((0, 5, 2))
+    assert psl.sig_coef(x, [(0,), (1, 0)]).shape == (0, 2)
+    assert psl.sig_coef(x, [(0,), (1, 0)], prefixes=True).shape == (0, 3)
+    assert psl.sig_coef_backprop(x, [(1, 0)], np.zeros((0, 2)), np.zeros((0, 2))).shape == (0, 5, 2)
+    y = np.zeros((3, 5, 2))
+    with pytest.raises(ValueError, match="range"):
+        psl.sig_coef(y, [(0, 2)])
+    with pytest.raises(TypeError):
+        psl.sig_coef(y, [[0, 1]])
+    with pytest.raises(TypeError):
+        psl.sig_coef(y, (0, 1.0))
+    with pytest.raises(ValueError, match="non-empty"):
+        psl.sig_coef(y, [])
+    with pytest.raises(ValueError, match="prefixes=True"):
+        psl.sig_coef_backprop(y, [(1, 0)], np.zeros((3, 1)), np.zeros((3, 1)))
+    sig = np.arange(14.0)
+    np.testing.assert_array_equal(psl.extract_sig_coef(sig, [(0,), (1, 0), (1, 1, 1)], 2), [0.0, 4.0, 13.0])
+    np.testing.assert_array_equal(psl.extract_sig_coef(np.arange(15.0), [(), (1,)], 2, scalar_term=True), [0.0, 2.0])
