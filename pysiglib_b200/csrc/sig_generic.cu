@@ -307,55 +307,67 @@ generic_backward_kernel(PathView<T> pv, T* out, const T* sig_derivs, const T* si
 // in: (batch, n, slen) scalar-free; out: (batch, ceil(n/2), .): out[b][j] = in[b][2j] (x) in[b][2j+1]
 // (a last unpaired segment is copied).
 //   C_m[w] = A_m[w] + sum_{i=m-1..1} A_i[w_1..w_i] * B_{m-i}[w_{i+1}..w_m] + B_m[w]
-// Both product kernels give one thread to a prefix u of length m-1 (all levels m = 1..N) and let it
-// produce the d coefficients (u, c), c = 0..d-1: the split positions of the word are decoded once per
-// prefix, the right factors are then read as runs of d consecutive values.  Prefix slot p of a
-// signature owns outputs [p d, p d + d) of the scalar-free layout (level m starts at d li[m-1]).
+// Exact division of a 32-bit index by the (runtime constant) dimension with a multiply and two
+// shifts instead of the ~20-instruction integer division (Granlund-Montgomery, round-up variant).
+struct FastDiv {
+    uint32_t divisor, magic, shift1, shift2;
+    __device__ __forceinline__ uint32_t div(uint32_t x) const {
+        if (divisor == 1) return x;
+        const uint32_t t = __umulhi(magic, x);
+        return (t + ((x - t) >> shift1)) >> shift2;
+    }
+};
+
+FastDiv make_fast_div(uint32_t d) {
+    FastDiv f{d, 0, 0, 0};
+    if (d <= 1) return f;
+    uint32_t l = 0;
+    while ((1ull << l) < d) ++l;  // ceil(log2 d)
+    f.magic = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1);
+    f.shift1 = 1;
+    f.shift2 = l - 1;
+    return f;
+}
+
+// One thread per output coefficient j of the scalar-free layout: j = p d + ch with p the slot of the
+// prefix u (length m-1, all levels m = 1..N; level m starts at d li[m-1]) and ch the last letter, so
+// consecutive threads read and write consecutive addresses.
 template <typename T>
-__device__ __forceinline__ void chen_product_slot(const T* __restrict__ a, const T* __restrict__ bb, T* __restrict__ c,
-                                                  uint32_t p, uint32_t d, int N, const uint32_t* li) {
-    // a, bb, c address position 0 of the scalar-term layout (the scalar slot itself is never touched)
+__device__ __forceinline__ T chen_product_coeff(const T* __restrict__ a, const T* __restrict__ bb, uint32_t j,
+                                                const FastDiv& fd, int N, const uint32_t* li) {
+    // a, bb address position 0 of the scalar-term layout
+    const uint32_t d = fd.divisor;
+    const uint32_t p = fd.div(j), ch = j - p * d;
     int m = 1;
     while (m < N && p >= li[m]) ++m;       // li[m-1] <= p < li[m]
     const uint32_t q = p - li[m - 1];      // index of the prefix inside level m-1
-    const uint32_t base = li[m] + q * d;   // first output position
-    T left_val[kMaxDegree];
-    uint32_t right_pos[kMaxDegree];
-    uint32_t pw = 1;                       // d^(m-1-i)
+    T acc = a[1 + j];
+    uint32_t left = q, pw = 1;             // left = q / d^(m-1-i), pw = d^(m-1-i)
     for (int i = m - 1; i >= 1; --i) {
-        const uint32_t left = q / pw;
-        left_val[i] = a[li[i] + left];
-        right_pos[i] = li[m - i] + (q - left * pw) * d;
+        acc = fma_t(a[li[i] + left], bb[li[m - i] + (q - left * pw) * d + ch], acc);
+        left = fd.div(left);
         pw *= d;
     }
-    for (uint32_t ch = 0; ch < d; ++ch) {
-        T acc = a[base + ch];
-        for (int i = m - 1; i >= 1; --i) acc = fma_t(left_val[i], bb[right_pos[i] + ch], acc);
-        c[base + ch] = acc + bb[base + ch];
-    }
+    return acc + bb[1 + j];
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kGenericThreads)
 chen_pair_kernel(const T* __restrict__ in, int n, T* __restrict__ out, uint64_t out_stride, bool out_scalar,
-                 uint64_t pairs_total, uint32_t slen, uint32_t d, int N, LevelIndex lev) {
+                 uint64_t pairs_total, uint32_t slen, FastDiv fd, int N, LevelIndex lev) {
     __shared__ uint32_t li[kMaxDegree + 2];
     for (unsigned i = threadIdx.x; i < unsigned(N + 2); i += blockDim.x) li[i] = lev.li[i];
     __syncthreads();
-    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;  // prefix slot
-    if (p >= slen / d) return;
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= slen) return;
     const int n2 = (n + 1) / 2;
-    for (uint64_t vb = blockIdx.y; vb < pairs_total; vb += gridDim.y) {  // vb = b * n2 + j
+    for (uint64_t vb = blockIdx.y; vb < pairs_total; vb += gridDim.y) {  // vb = b * n2 + pair
         const uint64_t b = vb / uint64_t(n2);
-        const int j = int(vb - b * uint64_t(n2));
-        const T* a = in + (b * uint64_t(n) + uint64_t(2 * j)) * slen - 1;
+        const int pair = int(vb - b * uint64_t(n2));
+        const T* a = in + (b * uint64_t(n) + uint64_t(2 * pair)) * slen - 1;
         T* c = out + vb * out_stride - (out_scalar ? 0 : 1);
-        if (2 * j + 1 < n) {
-            chen_product_slot<T>(a, a + slen, c, p, d, N, li);
-        } else {
-            for (uint32_t ch = 0; ch < d; ++ch) c[1 + p * d + ch] = a[1 + p * d + ch];
-        }
-        if (out_scalar && p == 0) c[0] = T(1);  // the slot before level 1 is the scalar term
+        c[1 + j] = 2 * pair + 1 < n ? chen_product_coeff<T>(a, a + slen, j, fd, N, li) : a[1 + j];
+        if (out_scalar && j == 0) c[0] = T(1);  // the slot before level 1 is the scalar term
     }
 }
 
@@ -364,17 +376,17 @@ chen_pair_kernel(const T* __restrict__ in, int n, T* __restrict__ out, uint64_t 
 template <typename T>
 __global__ void __launch_bounds__(kGenericThreads)
 chen_product_kernel(const T* __restrict__ A, uint64_t a_stride, const T* __restrict__ B, uint64_t b_stride,
-                    T* __restrict__ C, uint64_t c_stride, bool c_scalar, uint64_t batch, uint32_t slen, uint32_t d,
+                    T* __restrict__ C, uint64_t c_stride, bool c_scalar, uint64_t batch, uint32_t slen, FastDiv fd,
                     int N, LevelIndex lev) {
     __shared__ uint32_t li[kMaxDegree + 2];
     for (unsigned i = threadIdx.x; i < unsigned(N + 2); i += blockDim.x) li[i] = lev.li[i];
     __syncthreads();
-    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= slen / d) return;
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= slen) return;
     for (uint64_t b = blockIdx.y; b < batch; b += gridDim.y) {
         T* c = C + b * c_stride - 1;
-        chen_product_slot<T>(A + b * a_stride - 1, B + b * b_stride - 1, c, p, d, N, li);
-        if (c_scalar && p == 0) c[0] = T(1);
+        c[1 + j] = chen_product_coeff<T>(A + b * a_stride - 1, B + b * b_stride - 1, j, fd, N, li);
+        if (c_scalar && j == 0) c[0] = T(1);
     }
 }
 
@@ -598,10 +610,10 @@ void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int ns
         const bool final = n2 == 1;
         T* dst = final ? out : buf[round & 1];
         const uint64_t pairs = checked_mul(s.batch, uint64_t(n2), "signature output");
-        const dim3 grid(grid_1d(slen / s.dim, kGenericThreads), static_cast<unsigned>(std::min<uint64_t>(pairs, 65535)));
+        const dim3 grid(grid_1d(slen, kGenericThreads), static_cast<unsigned>(std::min<uint64_t>(pairs, 65535)));
         chen_pair_kernel<T><<<grid, kGenericThreads, 0, stream>>>(
-            cur, n, dst, final ? s.stride : slen, final && s.scalar_term, pairs, slen, static_cast<uint32_t>(s.dim),
-            static_cast<int>(s.degree), lev);
+            cur, n, dst, final ? s.stride : slen, final && s.scalar_term, pairs, slen,
+            make_fast_div(static_cast<uint32_t>(s.dim)), static_cast<int>(s.degree), lev);
         SIG_CUDA_CHECK(cudaGetLastError());
         count_launch();
         cur = dst;
@@ -616,9 +628,9 @@ void launch_chen_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_s
     check_generic_limits(s);
     const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
     if (s.batch == 0 || slen == 0) return;
-    const dim3 grid(grid_1d(slen / s.dim, kGenericThreads), static_cast<unsigned>(std::min<uint64_t>(s.batch, 65535)));
+    const dim3 grid(grid_1d(slen, kGenericThreads), static_cast<unsigned>(std::min<uint64_t>(s.batch, 65535)));
     chen_product_kernel<T><<<grid, kGenericThreads, 0, stream>>>(
-        A, a_stride, B, b_stride, C, c_stride, write_scalar, s.batch, slen, static_cast<uint32_t>(s.dim),
+        A, a_stride, B, b_stride, C, c_stride, write_scalar, s.batch, slen, make_fast_div(static_cast<uint32_t>(s.dim)),
         static_cast<int>(s.degree), make_level_index(s.dim, s.degree));
     SIG_CUDA_CHECK(cudaGetLastError());
     count_launch();
