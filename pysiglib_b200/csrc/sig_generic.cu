@@ -591,6 +591,16 @@ void launch_generic_backward(const T* path, T* out, const T* sig_derivs, const T
     count_launch();
 }
 
+// Grid of the product kernels: x over the coefficients of one signature, y over the batch, which the
+// threads walk with stride gridDim.y.  Enough CTAs to fill the GPU many times over, but not one
+// CTA per (coefficient block, signature): at a few hundred thousand tiny CTAs their launch cost dominates.
+dim3 batch_walk_grid(uint32_t slen, uint64_t batch) {
+    const unsigned gx = grid_1d(slen, kGenericThreads);
+    const uint64_t target = 148ull * 64;
+    const uint64_t gy = std::max<uint64_t>(1, std::min<uint64_t>(std::min<uint64_t>(batch, 65535), (target + gx - 1) / gx));
+    return dim3(gx, static_cast<unsigned>(gy));
+}
+
 uint64_t chen_combine_tmp_elems(const SigShape& s, int nseg) {
     // two ping-pong buffers: ceil(nseg/2) and ceil(nseg/4) signatures per path
     return s.batch * (s.full_len - 1) * uint64_t((nseg + 1) / 2 + (nseg + 3) / 4);
@@ -610,7 +620,7 @@ void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int ns
         const bool final = n2 == 1;
         T* dst = final ? out : buf[round & 1];
         const uint64_t pairs = checked_mul(s.batch, uint64_t(n2), "signature output");
-        const dim3 grid(grid_1d(slen, kGenericThreads), static_cast<unsigned>(std::min<uint64_t>(pairs, 65535)));
+        const dim3 grid = batch_walk_grid(slen, pairs);
         chen_pair_kernel<T><<<grid, kGenericThreads, 0, stream>>>(
             cur, n, dst, final ? s.stride : slen, final && s.scalar_term, pairs, slen,
             make_fast_div(static_cast<uint32_t>(s.dim)), static_cast<int>(s.degree), lev);
@@ -628,7 +638,7 @@ void launch_chen_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_s
     check_generic_limits(s);
     const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
     if (s.batch == 0 || slen == 0) return;
-    const dim3 grid(grid_1d(slen, kGenericThreads), static_cast<unsigned>(std::min<uint64_t>(s.batch, 65535)));
+    const dim3 grid = batch_walk_grid(slen, s.batch);
     chen_product_kernel<T><<<grid, kGenericThreads, 0, stream>>>(
         A, a_stride, B, b_stride, C, c_stride, write_scalar, s.batch, slen, make_fast_div(static_cast<uint32_t>(s.dim)),
         static_cast<int>(s.degree), make_level_index(s.dim, s.degree));
