@@ -106,3 +106,39 @@ def test_batch_partitioner_on_two_devices():
     for dev in ("cuda:0", "cuda:1", "cuda:0"):
         t = torch.tensor(path, device=dev)
         np.testing.assert_array_equal(psl.sig(t, 4).cpu().numpy(), one)
+
+
+def test_neighbour_operators_at_benchmark_signature_size():
+    """sig_join, sig_combine, sig_to_log_sig and corrections on signatures of the C5 shape (d=16,
+    degree 4, S=69 904): identities over the whole batch, the oracle on a few entries."""
+    B, L, d, N = 700, 24, 16, 4
+    path = make(B, L, d, torch.float32, "brownian", 21).cuda()
+    s_full = psl.sig(path, N)
+    # Chen: joining the two halves / appending the last increment gives the signature of the whole path
+    cut = L // 2
+    joined = psl.sig_combine(psl.sig(path[:, :cut + 1].contiguous(), N), psl.sig(path[:, cut:].contiguous(), N), d, N)
+    assert_sig_close(joined.cpu().numpy(), s_full.cpu().numpy(), d, N, 2e-5)
+    head = psl.sig(path[:, :-1].contiguous(), N)
+    last = (path[:, -1] - path[:, -2]).contiguous()
+    assert_sig_close(psl.sig_join(head, last, d, N).cpu().numpy(), s_full.cpu().numpy(), d, N, 2e-5)
+    # Lyndon coordinates are a gather of the expanded logarithm; the logarithm of a straight segment is the segment
+    log0 = psl.sig_to_log_sig(s_full, d, N, method=0)
+    log1 = psl.sig_to_log_sig(s_full, d, N, method=1)
+    idx = torch.tensor(oracle.lyndon_indices(d, N).astype(np.int64) - 1, device="cuda")
+    assert torch.equal(log1, log0[:, idx])
+    lin = psl.sig_to_log_sig(psl.linear_sig(last, d, N), d, N, method=0)
+    assert torch.allclose(lin[:, :d], last, rtol=0, atol=0)
+    assert float(lin[:, d:].abs().max()) <= 1e-6 * max(1.0, float(last.abs().max()) ** N)
+    sub = [0, 1, B - 1]
+    want = oracle.sig_to_log_sig(s_full[sub].cpu().numpy().astype(np.float64), d, N, method=1)
+    got = log1[sub].cpu().numpy()
+    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
+    # zero corrections reproduce the plain signature (scratch is cut into two batch chunks at this size)
+    zero = torch.zeros((d * d,), dtype=torch.float32, device="cuda")
+    zero[0] = 1e-30  # non-empty, numerically nothing
+    corrected = psl.sig(path[:, :6].contiguous(), N, correction=zero)
+    assert_sig_close(corrected.cpu().numpy(), psl.sig(path[:, :6].contiguous(), N).cpu().numpy(), d, N, 2e-5)
+    corr = (torch.randn((3, 5, d * d), generator=torch.Generator().manual_seed(3)) * 0.05).cuda()
+    got = psl.sig(path[[0, 1, B - 1], :6].contiguous(), N, correction=corr).cpu().numpy()
+    want = oracle.sig(path[[0, 1, B - 1], :6].cpu().numpy().astype(np.float64), N, correction=corr.cpu().numpy().astype(np.float64))
+    assert_sig_close(got, want, d, N, 2e-5)
