@@ -304,9 +304,69 @@ def log_sig_length(dim, degree):
     return int(_lib().oracle_lyndon_indices(dim, degree, None, 0))
 
 
+def lyndon_words(dim, degree):
+    """Lyndon words of length 1..degree over ``dim`` letters, by length then lexicographically
+    (Duval's algorithm; the order of siglib/shared/preparation/log_sig/lyndon_words.cpp:25-84)."""
+    out = []
+    for n in range(1, degree + 1):
+        w = [0]
+        while w:
+            m = len(w)
+            if m == n:
+                out.append(tuple(w))
+            while len(w) < n:
+                w.append(w[len(w) - m])
+            while w and w[-1] == dim - 1:
+                w.pop()
+            if w:
+                w[-1] += 1
+    return out
+
+
+def lyndon_bracket_expansions(dim, degree):
+    """For every Lyndon word w (in lyndon_words order) the expansion of its bracket [w] into words:
+    a dict {word: integer coefficient}; [w] = [[u], [v]] with v the longest proper Lyndon suffix
+    (standard factorisation, lyndon_words.cpp:114-138, 181-232)."""
+    words = lyndon_words(dim, degree)
+    index = {w: i for i, w in enumerate(words)}
+    exps = []
+    for w in words:
+        if len(w) == 1:
+            exps.append({w: 1})
+            continue
+        cut = next(i for i in range(1, len(w)) if w[i:] in index)
+        eu, ev = exps[index[w[:cut]]], exps[index[w[cut:]]]
+        e = {}
+        for a, ca in eu.items():
+            for b, cb in ev.items():
+                e[a + b] = e.get(a + b, 0) + ca * cb
+                e[b + a] = e.get(b + a, 0) - ca * cb
+        exps.append({k: v for k, v in e.items() if v})
+    return words, exps
+
+
+def lyndon_projection(dim, degree):
+    """P[i][j] = coefficient of the Lyndon word w_i in the bracket [w_j]: Lyndon-word coordinates
+    of a Lie element are P times its Lyndon-basis coordinates (method 1 = P @ method 2)."""
+    words, exps = lyndon_bracket_expansions(dim, degree)
+    index = {w: i for i, w in enumerate(words)}
+    P = np.zeros((len(words), len(words)))
+    for j, e in enumerate(exps):
+        for w, c in e.items():
+            if w in index:
+                P[index[w], j] = c
+    return P
+
+
 def sig_to_log_sig(sig_, dim, degree, method=1):
     """Oracle log signature from (batches of) signatures; method 0 = expanded tensor logarithm in
-    the layout of the input, method 1 = its coordinates at the Lyndon words."""
+    the layout of the input, method 1 = its coordinates at the Lyndon words, method 2 = its
+    coordinates in the Lyndon (bracket) basis, P^-1 applied to method 1 as the reference does
+    (siglib/cpsig/cp_tensor_log.h:160-170)."""
+    if method == 2:
+        words = sig_to_log_sig(sig_, dim, degree, method=1)
+        return np.linalg.solve(lyndon_projection(dim, degree), words.reshape(-1, words.shape[-1]).T.astype(np.float64)
+                               ).T.reshape(words.shape).astype(words.dtype)
     a = np.ascontiguousarray(sig_)
     a2 = a.reshape(-1, a.shape[-1])
     suf, real = _suffix(a2)
@@ -325,6 +385,11 @@ def sig_to_log_sig(sig_, dim, degree, method=1):
 
 def sig_to_log_sig_backprop(sig_, log_sig_derivs, dim, degree, method=1):
     """Oracle dF/d sig from dF/d log_sig (layouts as in sig_to_log_sig)."""
+    if method == 2:  # cp_tensor_log.h:261-283: transpose of P^-1, then the Lyndon-word backward
+        g = np.asarray(log_sig_derivs)
+        pulled = np.linalg.solve(lyndon_projection(dim, degree).T, g.reshape(-1, g.shape[-1]).T.astype(np.float64)
+                                 ).T.reshape(g.shape).astype(g.dtype)
+        return sig_to_log_sig_backprop(sig_, pulled, dim, degree, method=1)
     a = np.ascontiguousarray(sig_)
     a2 = a.reshape(-1, a.shape[-1])
     g2 = np.ascontiguousarray(log_sig_derivs, dtype=a.dtype).reshape(a2.shape[0], -1)

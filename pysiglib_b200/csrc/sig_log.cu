@@ -11,7 +11,7 @@
 //
 // Same values as siglib/cpsig/cp_tensor_log.h:47-122 (forward) and the derivative of that map
 // (the reference evaluates it as cp_tensor_log.h:176-235); replaces sig_to_log_sig_cuda_ and
-// sig_to_log_sig_backprop_cuda_ of siglib/cusig/cu_log_signature.cu for methods 0 and 1.
+// sig_to_log_sig_backprop_cuda_ of siglib/cusig/cu_log_signature.cu for methods 0, 1 and 2.
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -176,11 +176,167 @@ LyndonTable lyndon_table(uint64_t dim, uint64_t degree) {
     return table;
 }
 
+
+// ----- Lyndon basis (method 2) --------------------------------------------------------------------
+//
+// The log signature is a Lie element: log S = sum_j b_j [w_j] over the Lyndon words w_j, where the
+// bracket [w] = [[u],[v]] follows the standard factorisation w = u v (v the longest proper Lyndon
+// suffix) and [a] = a for a letter.  Expanding a bracket gives w itself plus lexicographically larger
+// words, so the matrix P[i][j] = coefficient of the word w_i in [w_j] is unit lower triangular and
+// block diagonal by word length; the Lyndon-word coordinates a of method 1 are a = P b, hence
+// b = P^-1 a.  As in the reference (siglib/shared/preparation/log_sig/lyndon_words.cpp:150-252,
+// log_sig_cache.cpp:33-46) the inverse is built once per (dimension, degree) and applied as a sparse
+// matrix; here both it and its transpose live on the device in CSR form.
+struct CsrHost {
+    std::vector<uint32_t> row_ptr, col;
+    std::vector<double> val;
+};
+
+void rows_to_csr(const std::vector<std::map<uint32_t, double>>& rows, CsrHost& out) {
+    out.row_ptr.assign(1, 0);
+    for (const auto& row : rows) {
+        for (const auto& kv : row)
+            if (kv.second != 0.0) { out.col.push_back(kv.first); out.val.push_back(kv.second); }
+        out.row_ptr.push_back(static_cast<uint32_t>(out.col.size()));
+    }
+}
+
+void build_basis_inverse(uint64_t dim, uint64_t degree, CsrHost& inv, CsrHost& inv_t) {
+    using Word = std::vector<uint32_t>;
+    // Lyndon words in the table's order, their flat codes (code(uv) = code(u) dim^|v| + code(v))
+    std::vector<Word> words;
+    {
+        Word w;
+        for (uint64_t n = 1; n <= degree; ++n) {
+            w.assign(1, 0);
+            while (!w.empty()) {
+                const size_t m = w.size();
+                if (m == n) words.push_back(w);
+                while (w.size() < n) w.push_back(w[w.size() - m]);
+                while (!w.empty() && w.back() == dim - 1) w.pop_back();
+                if (!w.empty()) ++w.back();
+            }
+        }
+    }
+    const uint32_t M = static_cast<uint32_t>(words.size());
+    auto code_of = [&](const Word& w) {
+        uint64_t c = 0;
+        for (uint32_t letter : w) c = c * dim + letter + 1;
+        return c;
+    };
+    std::map<Word, uint32_t> index_of;
+    std::map<uint64_t, uint32_t> lyndon_by_code;
+    for (uint32_t i = 0; i < M; ++i) {
+        index_of[words[i]] = i;
+        lyndon_by_code[code_of(words[i])] = i;
+    }
+    std::vector<uint64_t> dim_pow(degree + 1, 1);
+    for (uint64_t k = 1; k <= degree; ++k) dim_pow[k] = dim_pow[k - 1] * dim;
+
+    // bracket expansions: word code -> integer coefficient
+    std::vector<std::map<uint64_t, double>> expansion(M);
+    std::vector<std::map<uint32_t, double>> P(M);  // P[i][j]
+    for (uint32_t j = 0; j < M; ++j) {
+        const Word& w = words[j];
+        if (w.size() == 1) {
+            expansion[j][code_of(w)] = 1.0;
+        } else {
+            size_t cut = 1;
+            for (; cut < w.size(); ++cut)
+                if (index_of.count(Word(w.begin() + cut, w.end()))) break;  // longest proper Lyndon suffix
+            const uint32_t ju = index_of.at(Word(w.begin(), w.begin() + cut));
+            const uint32_t jv = index_of.at(Word(w.begin() + cut, w.end()));
+            const size_t lu = cut, lv = w.size() - cut;
+            for (const auto& eu : expansion[ju])
+                for (const auto& ev : expansion[jv]) {
+                    const double c = eu.second * ev.second;
+                    expansion[j][eu.first * dim_pow[lv] + ev.first] += c;
+                    expansion[j][ev.first * dim_pow[lu] + eu.first] -= c;
+                }
+        }
+        for (const auto& term : expansion[j]) {
+            if (term.second == 0.0) continue;
+            const auto it = lyndon_by_code.find(term.first);
+            if (it != lyndon_by_code.end()) P[it->second][j] = term.second;
+        }
+    }
+    // forward substitution: row i of P^-1 = e_i - sum_{j < i} P[i][j] * (row j of P^-1)
+    std::vector<std::map<uint32_t, double>> inverse(M), transpose(M);
+    for (uint32_t i = 0; i < M; ++i) {
+        if (P[i].count(i) == 0 || P[i][i] != 1.0)
+            throw std::runtime_error("Lyndon projection matrix is not unit triangular");
+        std::map<uint32_t, double>& row = inverse[i];
+        row[i] = 1.0;
+        for (const auto& kv : P[i]) {
+            const uint32_t j = kv.first;
+            if (j == i) continue;
+            if (j > i) throw std::runtime_error("Lyndon projection matrix is not lower triangular");
+            for (const auto& r : inverse[j]) row[r.first] -= kv.second * r.second;
+        }
+        for (const auto& r : row)
+            if (r.second != 0.0) transpose[r.first][i] = r.second;
+    }
+    rows_to_csr(inverse, inv);
+    rows_to_csr(transpose, inv_t);
+}
+
+struct BasisTable {
+    uint32_t rows = 0;
+    uint32_t *row_ptr = nullptr, *col = nullptr, *t_row_ptr = nullptr, *t_col = nullptr;
+    double *val = nullptr, *t_val = nullptr;
+};
+std::map<std::tuple<int, uint64_t, uint64_t>, BasisTable> g_basis;
+
+template <typename V>
+V* upload(const std::vector<V>& host) {
+    V* dev = nullptr;
+    SIG_CUDA_CHECK(cudaMalloc(&dev, std::max<size_t>(host.size(), 1) * sizeof(V)));
+    SIG_CUDA_CHECK(cudaMemcpy(dev, host.data(), host.size() * sizeof(V), cudaMemcpyHostToDevice));
+    return dev;
+}
+
+BasisTable basis_table(uint64_t dim, uint64_t degree) {
+    const int device = current_device();
+    std::lock_guard<std::mutex> lock(g_tables_mu);
+    const auto key = std::make_tuple(device, dim, degree);
+    auto it = g_basis.find(key);
+    if (it != g_basis.end()) return it->second;
+    CsrHost inv, inv_t;
+    build_basis_inverse(dim, degree, inv, inv_t);
+    BasisTable t;
+    t.rows = static_cast<uint32_t>(inv.row_ptr.size() - 1);
+    t.row_ptr = upload(inv.row_ptr);
+    t.col = upload(inv.col);
+    t.val = upload(inv.val);
+    t.t_row_ptr = upload(inv_t.row_ptr);
+    t.t_col = upload(inv_t.col);
+    t.t_val = upload(inv_t.val);
+    g_basis.emplace(key, t);
+    return t;
+}
+
+// out[b][i] = sum_k val[k] * in[b][col[k]] over row i of a CSR matrix; one thread per row.
+template <typename T>
+__global__ void basis_spmv_kernel(const T* __restrict__ in, uint64_t in_stride, T* __restrict__ out,
+                                  uint64_t out_stride, const uint32_t* __restrict__ row_ptr,
+                                  const uint32_t* __restrict__ col, const double* __restrict__ val, uint32_t rows,
+                                  uint64_t batch) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows) return;
+    const uint32_t begin = row_ptr[i], end = row_ptr[i + 1];
+    for (uint64_t b = blockIdx.y; b < batch; b += gridDim.y) {
+        const T* x = in + b * in_stride;
+        T acc = T(0);
+        for (uint32_t k = begin; k < end; ++k) acc = alg_fma(static_cast<T>(val[k]), x[col[k]], acc);
+        out[b * out_stride + i] = acc;
+    }
+}
+
 void check_method(int method, const char* who) {
-    if (method == 0 || method == 1) return;
-    if (method == 2 || method == 3)
-        throw std::invalid_argument(std::string(who) + ": log-signature method " + std::to_string(method) +
-                                    " is not part of this build of libcusig (methods 0 and 1 are)");
+    if (method == 0 || method == 1 || method == 2) return;
+    if (method == 3)
+        throw std::invalid_argument(std::string(who) + ": log-signature method 3 is not part of this build of "
+                                    "libcusig (methods 0, 1 and 2 are)");
     throw std::invalid_argument(std::string(who) + ": method must be one of 0, 1 or 2");
 }
 
@@ -220,6 +376,18 @@ void release_log_sig_tables() noexcept {
         (void)cudaGetLastError();
     }
     g_tables.clear();
+    for (auto& kv : g_basis) {
+        int prev = -1;
+        if (cudaGetDevice(&prev) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+        if (cudaSetDevice(std::get<0>(kv.first)) == cudaSuccess) {
+            BasisTable& t = kv.second;
+            (void)cudaFree(t.row_ptr); (void)cudaFree(t.col); (void)cudaFree(t.val);
+            (void)cudaFree(t.t_row_ptr); (void)cudaFree(t.t_col); (void)cudaFree(t.t_val);
+        }
+        (void)cudaSetDevice(prev);
+        (void)cudaGetLastError();
+    }
+    g_basis.clear();
 }
 
 void prepare_log_sig_entry(uint64_t dimension, uint64_t degree, int method) {
@@ -228,6 +396,7 @@ void prepare_log_sig_entry(uint64_t dimension, uint64_t degree, int method) {
     if (method == 0) return;
     (void)checked_levels(dimension, degree, "prepare_log_sig_cuda");
     (void)lyndon_table(dimension, degree);
+    if (method == 2) (void)basis_table(dimension, degree);
 }
 
 template <typename T>
@@ -245,18 +414,28 @@ void sig_to_log_sig_entry(const T* sig, T* out, uint64_t batch, uint64_t dimensi
 
     auto run = [&](const T* a, T* o, cudaStream_t st) {
         LyndonTable table;
-        if (method == 1) table = lyndon_table(dimension, degree);
-        const uint64_t out_stride = method == 1 ? table.count : in_stride;
-        const uint64_t per_sig = 2 * S * sizeof(T);
+        BasisTable basis;
+        if (method >= 1) table = lyndon_table(dimension, degree);
+        if (method == 2) basis = basis_table(dimension, degree);
+        const uint64_t out_stride = method >= 1 ? table.count : in_stride;
+        const uint64_t per_sig = (2 * S + (method == 2 ? table.count : 0)) * sizeof(T);
         const uint64_t chunk = std::max<uint64_t>(1, std::min<uint64_t>(batch, kLogScratchBudget / per_sig));
-        Scratch ws(degree >= 2 ? chunk * per_sig : 0, st);
+        Scratch ws(chunk * per_sig, st);
         for (uint64_t b0 = 0; b0 < batch; b0 += chunk) {
             const uint64_t count = std::min(chunk, batch - b0);
             const T* x = a + b0 * in_stride + shift;
             const T* r2 = degree >= 2 ? run_horner<T>(x, in_stride, ws.as<T>(), false, lv, count, st) : nullptr;
-            if (method == 1) {
+            if (method >= 1) {
+                // Lyndon-word coordinates, straight into the result (method 1) or into scratch (method 2)
+                T* words = method == 2 ? ws.as<T>() + 2 * chunk * S : o + b0 * out_stride;
                 log_final_kernel<T><<<coeff_grid(table.count, count), kThreads, 0, st>>>(
-                    x, in_stride, r2, o + b0 * out_stride, out_stride, lv, count, table.device, table.count, false);
+                    x, in_stride, r2, words, out_stride, lv, count, table.device, table.count, false);
+                if (method == 2) {
+                    check_launch("tensor log kernel");
+                    basis_spmv_kernel<T><<<coeff_grid(basis.rows, count), kThreads, 0, st>>>(
+                        words, out_stride, o + b0 * out_stride, out_stride, basis.row_ptr, basis.col, basis.val,
+                        basis.rows, count);
+                }
             } else {
                 log_final_kernel<T><<<coeff_grid(lv.total(), count), kThreads, 0, st>>>(
                     x, in_stride, r2, o + b0 * out_stride + shift, out_stride, lv, count, nullptr, lv.total(),
@@ -272,7 +451,7 @@ void sig_to_log_sig_entry(const T* sig, T* out, uint64_t batch, uint64_t dimensi
         if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
         return;
     }
-    const uint64_t out_len = method == 1 ? log_sig_length_host(dimension, degree) : in_stride;
+    const uint64_t out_len = method >= 1 ? log_sig_length_host(dimension, degree) : in_stride;
     run_staged({{sig, nullptr, batch * in_stride * sizeof(T)}, {nullptr, out, batch * out_len * sizeof(T)}}, opt.device,
                [&](const std::vector<void*>& d, cudaStream_t st) {
                    run(static_cast<const T*>(d[0]), static_cast<T*>(d[1]), st);
@@ -295,10 +474,12 @@ void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs
 
     auto run = [&](const T* a, T* o, const T* g, cudaStream_t st) {
         LyndonTable table;
-        if (method == 1) table = lyndon_table(dimension, degree);
-        const uint64_t g_stride = method == 1 ? table.count : stride;
+        BasisTable basis;
+        if (method >= 1) table = lyndon_table(dimension, degree);
+        if (method == 2) basis = basis_table(dimension, degree);
+        const uint64_t g_stride = method >= 1 ? table.count : stride;
         const uint64_t vectors = 3 + (N >= 2 ? N - 1 : 0);  // D, two adjoint buffers, R_2..R_N
-        const uint64_t per_sig = vectors * S * sizeof(T);
+        const uint64_t per_sig = (vectors * S + (method == 2 ? table.count : 0)) * sizeof(T);
         const uint64_t chunk = std::max<uint64_t>(1, std::min<uint64_t>(batch, kLogScratchBudget / per_sig));
         Scratch ws(chunk * per_sig, st);
         for (uint64_t b0 = 0; b0 < batch; b0 += chunk) {
@@ -310,13 +491,21 @@ void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs
             T* keep = qb + vec;
             const T* x = a + b0 * stride + shift;
             T* dsig = o + b0 * stride + shift;
+            const T* gw = g + b0 * g_stride + (method >= 1 ? 0 : shift);  // adjoint of the Lyndon-word coordinates
+            if (method == 2) {
+                // the forward applied P^-1 to the Lyndon-word coordinates: pull back through its transpose
+                T* pulled = ws.as<T>() + chunk * vectors * S;
+                basis_spmv_kernel<T><<<coeff_grid(basis.rows, count), kThreads, 0, st>>>(
+                    gw, g_stride, pulled, g_stride, basis.t_row_ptr, basis.t_col, basis.t_val, basis.rows, count);
+                check_launch("tensor log backward kernel");
+                gw = pulled;
+            }
             log_seed_kernel<T><<<coeff_grid(lv.total(), count), kThreads, 0, st>>>(
-                g + b0 * g_stride + (method == 1 ? 0 : shift), g_stride, D, dsig, stride, lv, count,
-                method == 1 ? table.device : nullptr, scalar_term);
+                gw, g_stride, D, dsig, stride, lv, count, method >= 1 ? table.device : nullptr, scalar_term);
             check_launch("tensor log backward kernel");
-            if (method == 1) {
+            if (method >= 1) {
                 log_scatter_kernel<T><<<coeff_grid(table.count, count), kThreads, 0, st>>>(
-                    g + b0 * g_stride, g_stride, D, dsig, stride, lv.total(), count, table.device, table.count);
+                    gw, g_stride, D, dsig, stride, lv.total(), count, table.device, table.count);
                 check_launch("tensor log backward kernel");
             }
             if (N < 2) continue;
@@ -341,7 +530,7 @@ void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs
         if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
         return;
     }
-    const uint64_t g_len = method == 1 ? log_sig_length_host(dimension, degree) : stride;
+    const uint64_t g_len = method >= 1 ? log_sig_length_host(dimension, degree) : stride;
     run_staged({{sig, nullptr, batch * stride * sizeof(T)}, {nullptr, out, batch * stride * sizeof(T)},
                 {log_sig_derivs, nullptr, batch * g_len * sizeof(T)}},
                opt.device, [&](const std::vector<void*>& d, cudaStream_t st) {

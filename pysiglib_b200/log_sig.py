@@ -1,13 +1,14 @@
-"""``sig_to_log_sig``, its backward pass, and ``log_sig`` on the GPU, methods 0 and 1.
+"""``sig_to_log_sig``, its backward pass, and ``log_sig`` on the GPU, methods 0, 1 and 2.
 
 Same names, parameters and layouts as the reference's operators (``pysiglib/log_sig.py:95-188,
 241-329, 331-470``, ``pysiglib/log_sig_backprop.py:30-137``):
 
 * method 0: the expanded tensor logarithm, in the layout of the signature (scalar slot 0);
-* method 1: its coordinates at the Lyndon words, ``log_sig_length`` values.
+* method 1: its coordinates at the Lyndon words, ``log_sig_length`` values;
+* method 2: its coordinates in the Lyndon (bracket) basis, ``log_sig_length`` values.
 
-Methods 2 (Lyndon basis) and 3 (from the path, without the signature) are not part of this
-build and raise ``NotImplementedError``."""
+Method 3 (from the path, without the signature) is not part of this build and raises
+``NotImplementedError``."""
 from typing import Union
 
 import numpy as np
@@ -27,14 +28,15 @@ def _check_method(method, where):
         raise ValueError("method must be one of 0, 1, 2 or 3. Got " + str(method) + " instead.")
     if method == 3 and where != "log_sig":
         raise ValueError("method=3 is not supported in %s. Use log_sig(path, degree, method=3) instead." % where)
-    if method >= 2:
-        raise NotImplementedError("log-signature method %d is not part of pysiglib_b200 (methods 0 and 1 are)" % method)
+    if method == 3:
+        raise NotImplementedError("log-signature method 3 is not part of pysiglib_b200 (methods 0, 1 and 2 are)")
 
 
 def prepare_log_sig(dimension: int, degree: int, method: int, *, time_aug: bool = False, lead_lag: bool = False,
                     use_disk: bool = False, device: str = "both"):
-    """Builds what ``method`` needs ahead of time (optional here: method 0 needs nothing, method 1's
-    table of Lyndon-word positions is otherwise built at the first call on each GPU)."""
+    """Builds what ``method`` needs ahead of time (optional here: method 0 needs nothing; the table of
+    Lyndon-word positions of methods 1 and 2 and the inverse projection matrix of method 2 are
+    otherwise built at the first call on each GPU)."""
     check_type(dimension, "dimension", int)
     check_non_neg(dimension, "dimension")
     check_type(degree, "degree", int)
@@ -64,8 +66,8 @@ def sig_to_log_sig(
 
     :param sig: ``(..., S)`` with or without the scalar term (inferred from the length).
     :param dimension: dimension of the underlying path, before ``time_aug`` / ``lead_lag``.
-    :param method: 0 = expanded (result in the layout of ``sig``), 1 = Lyndon-word coordinates
-        (``log_sig_length`` values).
+    :param method: 0 = expanded (result in the layout of ``sig``), 1 = Lyndon-word coordinates,
+        2 = Lyndon-basis coordinates (``log_sig_length`` values each).
     """
     check_type(dimension, "dimension", int)
     check_non_neg(dimension, "dimension")
@@ -147,7 +149,7 @@ def log_sig(
         correction=None,
         n_jobs: int = 1
 ) -> Union[np.ndarray, torch.Tensor]:
-    """Log signature of a path: ``sig`` followed by ``sig_to_log_sig`` (methods 0 and 1).
+    """Log signature of a path: ``sig`` followed by ``sig_to_log_sig`` (methods 0, 1 and 2).
     ``scalar_term`` only matters for method 0, whose result has the layout of the signature."""
     _check_method(method, "log_sig")
     sig_ = sig(path, degree, scalar_term=scalar_term, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time,

@@ -88,7 +88,44 @@ def test_lyndon_word_log_and_backprop(B, d, N, dtype, scalar_term):
     assert_grad_close(got_g.cpu().numpy()[:, None, :], want_g[:, None, :], 1e-10 if dtype == np.float64 else 1e-4)
 
 
-@pytest.mark.parametrize("method", [0, 1])
+BASIS_CASES = [(5, 1, 4), (6, 2, 7), (4, 3, 4), (3, 4, 3), (300, 2, 5)]
+
+
+@pytest.mark.parametrize("B,d,N", BASIS_CASES)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("scalar_term", [False, True])
+def test_lyndon_basis_log_and_backprop(B, d, N, dtype, scalar_term):
+    import pysiglib_b200
+    s = _sigs(B + 3 * d + N, B, d, N, dtype, scalar_term)
+    want = oracle.sig_to_log_sig(s.astype(np.float64), d, N, method=2)
+    st = torch.tensor(s, device="cuda")
+    pysiglib_b200.prepare_log_sig(d, N, 2)
+    got = pysiglib_b200.sig_to_log_sig(st, d, N, method=2)
+    assert got.shape == want.shape == (B, pysiglib_b200.log_sig_length(d, N))
+    # the Lyndon-basis coordinates rebuild the whole expanded logarithm: sum_j b_j [w_j]
+    words, exps = oracle.lyndon_bracket_expansions(d, N)
+    full = pysiglib_b200.sig_to_log_sig(st, d, N, method=0).cpu().numpy().astype(np.float64)
+    off = 1 if scalar_term else 0
+    rebuilt = np.zeros((B, oracle.sig_length(d, N, True)))
+    g = got.cpu().numpy().astype(np.float64)
+    for j, e in enumerate(exps):
+        for w, c in e.items():
+            idx = 0
+            for letter in w:
+                idx = idx * d + letter + 1
+            rebuilt[:, idx] += c * g[:, j]
+    _assert_log_close(rebuilt[:, 1:], full[:, off:], s[:, off:], d, N, 1e-9 if dtype == np.float64 else 2e-5)
+    scale = np.maximum(np.abs(want).max(axis=1, keepdims=True), np.abs(s[:, off:off + d]).max(axis=1, keepdims=True) ** N / N)
+    assert np.all(np.abs(g - want) <= (1e-9 if dtype == np.float64 else 3e-5) * np.maximum(scale, np.abs(want)))
+    np.testing.assert_array_equal(pysiglib_b200.sig_to_log_sig(s, d, N, method=2), got.cpu().numpy())
+
+    w = np.random.default_rng(4).standard_normal(want.shape).astype(dtype)
+    want_g = oracle.sig_to_log_sig_backprop(s.astype(np.float64), w.astype(np.float64), d, N, method=2)
+    got_g = pysiglib_b200.sig_to_log_sig_backprop(st, torch.tensor(w, device="cuda"), d, N, method=2)
+    assert_grad_close(got_g.cpu().numpy()[:, None, :], want_g[:, None, :], 1e-9 if dtype == np.float64 else 2e-4)
+
+
+@pytest.mark.parametrize("method", [0, 1, 2])
 @pytest.mark.parametrize("flags", [(False, False), (True, False), (True, True)])
 def test_log_sig_from_path_and_autograd(method, flags):
     from pysiglib_b200 import torch_api
@@ -132,15 +169,16 @@ def test_unbuilt_methods_and_errors():
     from pysiglib_b200 import load_cusig
     s = torch.zeros((2, 14), dtype=torch.float64, device="cuda")
     with pytest.raises(NotImplementedError):
-        pysiglib_b200.sig_to_log_sig(s, 2, 3, method=2)
+        pysiglib_b200.log_sig(torch.zeros((2, 4, 2), dtype=torch.float64, device="cuda"), 3, method=3)
     with pytest.raises(ValueError, match="method=3"):
         pysiglib_b200.sig_to_log_sig(s, 2, 3, method=3)
     lib = load_cusig.library()
     p = lambda t: ctypes.cast(t.data_ptr(), ctypes.POINTER(ctypes.c_double))
     out = torch.zeros_like(s)
-    assert lib.sig_to_log_sig_cuda_d(p(s), p(out), 2, 2, 3, 2, False) == 2
+    assert lib.sig_to_log_sig_cuda_d(p(s), p(out), 2, 2, 3, 3, False) == 2
     assert "not part of this build" in load_cusig.last_error_message()
     assert lib.sig_to_log_sig_cuda_d(p(s), p(out), 2, 2, 0, 0, False) == 2
     assert "degree 0" in load_cusig.last_error_message()
     assert lib.prepare_log_sig_cuda(2, 3, 1, False) == 0
-    assert lib.prepare_log_sig_cuda(2, 3, 2, False) == 2
+    assert lib.prepare_log_sig_cuda(2, 3, 2, False) == 0
+    assert lib.prepare_log_sig_cuda(2, 3, 3, False) == 2

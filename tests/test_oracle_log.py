@@ -85,3 +85,48 @@ def test_backprop_matches_finite_differences(method, scalar_term, d, n):
     if scalar_term:
         want[:, 0] = 0  # the scalar slot is a constant of the map (cp_tensor_log.h:190-191)
     np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-8)
+
+
+def _word_index(word, dim):
+    i = 0
+    for letter in word:
+        i = i * dim + letter + 1
+    return i
+
+
+@pytest.mark.parametrize("d,n", [(2, 3), (2, 6), (3, 4), (4, 3)])
+def test_lyndon_basis_coordinates_rebuild_the_expanded_logarithm(d, n):
+    # method 2 pins itself: sum_j b_j [w_j], expanded word by word, must be the whole tensor logarithm
+    rng = np.random.default_rng(d + n)
+    s = oracle.sig(rng.standard_normal((2, 7, d)).cumsum(1) * 0.5, n, scalar_term=True)
+    full = oracle.sig_to_log_sig(s, d, n, method=0)
+    basis = oracle.sig_to_log_sig(s, d, n, method=2)
+    words, exps = oracle.lyndon_bracket_expansions(d, n)
+    assert basis.shape == (2, len(words))
+    rebuilt = np.zeros_like(full)
+    for j, e in enumerate(exps):
+        for w, c in e.items():
+            rebuilt[:, _word_index(w, d)] += c * basis[:, j]
+    np.testing.assert_allclose(rebuilt, full, rtol=1e-9, atol=1e-12)
+    P = oracle.lyndon_projection(d, n)
+    assert np.allclose(np.diag(P), 1) and np.allclose(np.triu(P, 1), 0)
+    if (d, n) == (2, 3):
+        np.testing.assert_array_equal(P, np.eye(5))  # brackets 0, 1, [0,1], [0,[0,1]], [[0,1],1]
+
+
+@pytest.mark.parametrize("d,n", [(2, 5), (3, 4)])
+def test_lyndon_basis_backprop_matches_finite_differences(d, n):
+    rng = np.random.default_rng(d * 7 + n)
+    s = oracle.sig(rng.standard_normal((1, 6, d)).cumsum(1) * 0.5, n)
+    out = oracle.sig_to_log_sig(s, d, n, method=2)
+    w = rng.standard_normal(out.shape)
+    got = oracle.sig_to_log_sig_backprop(s, w, d, n, method=2)
+    want = np.zeros_like(s)
+    eps = 1e-6
+    for i in range(s.size):
+        hi, lo = s.copy().reshape(-1), s.copy().reshape(-1)
+        hi[i] += eps
+        lo[i] -= eps
+        f = lambda x: float((w * oracle.sig_to_log_sig(x.reshape(s.shape), d, n, method=2)).sum())
+        want.reshape(-1)[i] = (f(hi) - f(lo)) / (2 * eps)
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-8)

@@ -193,7 +193,7 @@ def test_log_sig_argument_contract():
     with pytest.raises(ValueError, match="method=3"):
         psl.sig_to_log_sig(s, 2, 3, method=3)
     with pytest.raises(NotImplementedError):
-        psl.sig_to_log_sig(s, 2, 3, method=2)
+        psl.log_sig(np.zeros((3, 5, 2)), 3, method=3)
     with pytest.raises(TypeError):
         psl.sig_to_log_sig(s, 2, 3, method=1.0)
     with pytest.raises(ValueError):
