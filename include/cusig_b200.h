@@ -145,7 +145,8 @@ int sig_coef_backprop_cuda_d(const double* path, double* out, const double* coef
 
 /* Signature -> log signature.  method 0: expanded tensor logarithm in the layout of `sig` (scalar
  * slot 0); method 1: its coordinates at the Lyndon words of length <= degree, by length then
- * lexicographically (log_sig_length values per signature).  Methods 2 and 3 return code 2.
+ * lexicographically (log_sig_length values per signature); method 2: its coordinates in the Lyndon
+ * (bracket) basis, same count.  Method 3 returns code 2.
  * The backward takes dLoss/d log_sig in the layout of the forward's output and writes dLoss/d sig
  * in the layout of `sig`.
  * Replaces: siglib/cusig/cusig.h:407-409, 427-429 (siglib/cusig/cu_log_signature.cu); bound by
@@ -159,8 +160,8 @@ int sig_to_log_sig_backprop_cuda_f(const float* sig, float* out, const float* lo
 int sig_to_log_sig_backprop_cuda_d(const double* sig, double* out, const double* log_sig_derivs, uint64_t batch_size,
                                    uint64_t dimension, uint64_t degree, int method, bool scalar_term);
 
-/* Builds the per-device Lyndon-word table of method 1 ahead of the first call (optional: the
- * table is built on demand); method 0 needs nothing; methods 2 and 3 return code 2.
+/* Builds the per-device tables of methods 1 and 2 ahead of the first call (optional: the
+ * tables are built on demand); method 0 needs nothing; method 3 returns code 2.
  * Replaces: siglib/cusig/cusig.h:447; bound by pysiglib/load_siglib.py:165-183. */
 int prepare_log_sig_cuda(uint64_t dimension, uint64_t degree, int method, bool use_disk);
 

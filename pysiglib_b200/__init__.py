@@ -1,5 +1,5 @@
 """pysiglib_b200: pySigLib's ``sig`` / ``sig_backprop`` path on NVIDIA B200 (sm_100a), with the
-operators either side of it (``sig_combine``, ``sig_join``, ``linear_sig``, ``transform_path``, ``sig_coef``, ``sig_to_log_sig`` / ``log_sig`` methods 0 and 1).
+operators either side of it (``sig_combine``, ``sig_join``, ``linear_sig``, ``transform_path``, ``sig_coef``, ``sig_to_log_sig`` / ``log_sig`` methods 0, 1 and 2).
 
 Drop-in for that path only: the functions below keep the reference's names, parameters
 and result layout, and the shared library keeps the reference's C entry points.  All

@@ -57,17 +57,18 @@ void sig_join_backprop_entry(const T* d_out, T* d_sig, T* d_displacement, const 
                              const CallOptions& opt);
 
 // Signature -> log signature.  method 0: the expanded tensor logarithm, in the layout of `sig`;
-// method 1: its coordinates at the Lyndon words (log_sig_length values per signature).  Replaces
+// method 1: its coordinates at the Lyndon words, method 2: in the Lyndon basis (log_sig_length
+// values per signature each).  Replaces
 // sig_to_log_sig_cuda_ / sig_to_log_sig_backprop_cuda_ (siglib/cusig/cu_log_signature.cu) for those
-// two methods; the backward writes dLoss/d sig in the layout of `sig` (scalar slots 0).
+// methods; the backward writes dLoss/d sig in the layout of `sig` (scalar slots 0).
 template <typename T>
 void sig_to_log_sig_entry(const T* sig, T* out, uint64_t batch, uint64_t dimension, uint64_t degree, int method,
                           bool scalar_term, const CallOptions& opt);
 template <typename T>
 void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs, uint64_t batch, uint64_t dimension,
                                    uint64_t degree, int method, bool scalar_term, const CallOptions& opt);
-// Builds (and caches per device) the Lyndon-word index table that method 1 needs; methods 2 and 3
-// are not part of this build.
+// Builds (and caches per device) the Lyndon-word table of methods 1 and 2 and the inverse
+// projection matrix of method 2; method 3 is not part of this build.
 void prepare_log_sig_entry(uint64_t dimension, uint64_t degree, int method);
 uint64_t log_sig_length_host(uint64_t dimension, uint64_t degree);
 void release_log_sig_tables() noexcept;
