@@ -125,11 +125,13 @@ SIG_HD T nonunital_product_coeff(const T* A, const T* B, const Levels& lv, uint3
 
 // Adjoints of C = (product without unit terms) of A and B:
 //   dA_l[u] = sum_{m,v} dC_{l+m}[u v] B_m[v],   dB_m[v] = sum_{l,u} dC_{l+m}[u v] A_l[u].
+// `top`: dC is known to vanish above that level (the sums stop there).
 template <typename T>
-SIG_HD T nonunital_left_adjoint_coeff(const T* dC, const T* B, const Levels& lv, uint32_t l, uint32_t u) {
+SIG_HD T nonunital_left_adjoint_coeff(const T* dC, const T* B, const Levels& lv, uint32_t l, uint32_t u,
+                                      uint32_t top) {
     T acc = T(0);
     uint32_t msize = lv.dim;
-    for (uint32_t m = 1; l + m <= lv.degree; ++m) {
+    for (uint32_t m = 1; l + m <= top; ++m) {
         const T* row = dC + lv.off[l + m] + u * msize;
         const T* b = B + lv.off[m];
         T dot = T(0);
@@ -140,11 +142,12 @@ SIG_HD T nonunital_left_adjoint_coeff(const T* dC, const T* B, const Levels& lv,
     return acc;
 }
 template <typename T>
-SIG_HD T nonunital_right_adjoint_coeff(const T* dC, const T* A, const Levels& lv, uint32_t m, uint32_t v) {
+SIG_HD T nonunital_right_adjoint_coeff(const T* dC, const T* A, const Levels& lv, uint32_t m, uint32_t v,
+                                       uint32_t top) {
     T acc = T(0);
     const uint32_t msize = lv.size(m);
     uint32_t lsize = lv.dim;
-    for (uint32_t l = 1; l + m <= lv.degree; ++l) {
+    for (uint32_t l = 1; l + m <= top; ++l) {
         const T* col = dC + lv.off[l + m] + v;
         const T* a = A + lv.off[l];
         for (uint32_t u = 0; u < lsize; ++u) acc = alg_fma(col[u * msize], a[u], acc);

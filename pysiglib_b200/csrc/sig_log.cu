@@ -110,13 +110,15 @@ __global__ void log_adjoint_kernel(const T* __restrict__ x, uint64_t x_stride, c
     if (j >= S) return;
     const uint32_t t = lv.level_of(j), w = j - lv.off[t];
     const T constant = T(1) / static_cast<T>(k);
+    // Q = dLoss/dR_k lives on the levels of R_k (<= 1 + N - k; all levels for the seed, k = 1)
+    const uint32_t top = k == 1 ? lv.degree : 1 + lv.degree - k;
     for (uint64_t b = blockIdx.y; b < batch; b += gridDim.y) {
         const T* xb = x + b * x_stride;
         const T* qb = q + b * S;
-        T add = k >= 2 ? qb[j] * constant : T(0);
-        if (r_next) add -= nonunital_left_adjoint_coeff(qb, r_next + b * S, lv, t, w);
-        dsig[b * dsig_stride + j] += add;
-        if (q_new) q_new[b * S + j] = -nonunital_right_adjoint_coeff(qb, xb, lv, t, w);
+        T add = (k >= 2 && t <= top) ? qb[j] * constant : T(0);
+        if (r_next) add -= nonunital_left_adjoint_coeff(qb, r_next + b * S, lv, t, w, top);
+        if (t <= top) dsig[b * dsig_stride + j] += add;
+        if (q_new) q_new[b * S + j] = -nonunital_right_adjoint_coeff(qb, xb, lv, t, w, top);
     }
 }
 

@@ -160,11 +160,12 @@ void run_log_backprop(const T* x, const T* dy, T* dx, const Levels& lv) {
     for (uint32_t k = 1; k <= N; ++k) {
         const T* r_next = k < N ? keep.data() + uint64_t(k - 1) * S : nullptr;
         const T constant = T(1) / static_cast<T>(k);
+        const uint32_t top = k == 1 ? N : 1 + N - k;
         for_each_coeff<T>(lv, [&](uint32_t j, uint32_t t, uint32_t w) {
-            T add = k >= 2 ? q[j] * constant : T(0);
-            if (r_next) add -= nonunital_left_adjoint_coeff(q, r_next, lv, t, w);
-            dx[j] += add;
-            if (k < N) q_new[j] = -nonunital_right_adjoint_coeff(q, x, lv, t, w);
+            T add = (k >= 2 && t <= top) ? q[j] * constant : T(0);
+            if (r_next) add -= nonunital_left_adjoint_coeff(q, r_next, lv, t, w, top);
+            if (t <= top) dx[j] += add;
+            if (k < N) q_new[j] = -nonunital_right_adjoint_coeff(q, x, lv, t, w, top);
         });
         q = q_new;
         q_new = q_new == qa.data() ? qb.data() : qa.data();
