@@ -282,21 +282,6 @@ __global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, 
     for (uint32_t i = threadIdx.x; i < uint32_t(pv.d); i += blockDim.x) o[i] = -g_next[i];
 }
 
-// Threads per CTA for the one-CTA-per-path kernels: every phase strides the S coefficients of a
-// signature over the CTA, so the CTA size that wastes the fewest lanes in the last round wins
-// (S = 340 on 256 threads runs two rounds at 66 %; on 352 threads one round at 97 %).
-int path_cta_threads(uint32_t S) {
-    if (S <= 128) return int((S + 31) / 32 * 32);
-    int best = 128;
-    uint32_t best_waste = ~0u;
-    for (int t = 128; t <= 512; t += 32) {  // at least four warps; ties go to the larger CTA (fewer rounds)
-        const uint32_t rounds = (S + t - 1) / t;
-        const uint32_t waste = rounds * t - S;
-        if (waste <= best_waste) { best = t; best_waste = waste; }
-    }
-    return best;
-}
-
 constexpr uint64_t kScratchBudget = 1ull << 30;  // bytes of per-path working vectors held at once
 
 template <typename T>
@@ -380,7 +365,7 @@ void correction_forward_on_device(const T* path, T* out, const SigShape& s, T en
     Scratch ws(chunk * per_path, stream);
     for (uint64_t b0 = 0; b0 < s.batch; b0 += chunk) {
         const uint64_t count = std::min(chunk, s.batch - b0);
-        correction_forward_kernel<T><<<static_cast<unsigned>(count), path_cta_threads(lv.total()), 0, stream>>>(
+        correction_forward_kernel<T><<<static_cast<unsigned>(count), kThreads, 0, stream>>>(
             pv, make_args(c, s.data_dim), out, s.stride, s.scalar_term, ws.as<T>(), lv, b0);
         check_launch("corrected signature kernel");
     }
@@ -399,7 +384,7 @@ void correction_backward_on_device(const T* path, T* out, const T* sig_derivs, c
     Scratch ws(chunk * per_path, stream);
     for (uint64_t b0 = 0; b0 < s.batch; b0 += chunk) {
         const uint64_t count = std::min(chunk, s.batch - b0);
-        correction_backward_kernel<T><<<static_cast<unsigned>(count), path_cta_threads(lv.total()), smem, stream>>>(
+        correction_backward_kernel<T><<<static_cast<unsigned>(count), kThreads, smem, stream>>>(
             pv, make_args(c, s.data_dim), sig, sig_derivs, s.stride, s.scalar_term, out, ws.as<T>(), lv, b0);
         check_launch("corrected signature backward kernel");
     }
