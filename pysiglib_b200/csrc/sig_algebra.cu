@@ -68,6 +68,53 @@ __global__ void linear_sig_adjoint_kernel(const T* __restrict__ disp, const T* _
     }
 }
 
+// The same adjoint through the recursion L_k = L_{k-1} (x) v / k, for dim <= blockDim: first the
+// adjoints are pushed down level by level (in place in dL, which is scratch),
+//     dL_{k-1}[u] += (1/k) sum_c v[c] dL_k[u c]        (k = N .. 2),
+// then every coefficient (u, c) of level k contributes one term L_{k-1}[u] dL_k[u c] / k to d v[c].
+// blockDim is a multiple of dim, so a thread always meets the same letter c = threadIdx % dim and
+// keeps its partial sum in a register; the partial sums meet in shared memory (dim values).
+template <typename T>
+__global__ void linear_sig_adjoint_recursive_kernel(const T* __restrict__ disp, const T* __restrict__ L,
+                                                    T* __restrict__ dL, uint64_t stride, T* __restrict__ d_disp,
+                                                    Levels lv) {
+    extern __shared__ unsigned char smem_raw[];
+    T* acc = reinterpret_cast<T*>(smem_raw);  // dim sums, then dim letters of v
+    T* vs = acc + lv.dim;
+    const uint64_t b = blockIdx.x;
+    const uint32_t d = lv.dim, N = lv.degree;
+    const T* lin = L + b * stride;
+    T* g = dL + b * stride;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        acc[i] = T(0);
+        vs[i] = disp[b * d + i];
+    }
+    __syncthreads();
+    for (uint32_t k = N; k >= 2; --k) {
+        const T inv_k = T(1) / static_cast<T>(k);
+        const uint32_t count = lv.size(k - 1);
+        const T* upper = g + lv.off[k];
+        T* lower = g + lv.off[k - 1];
+        for (uint32_t u = threadIdx.x; u < count; u += blockDim.x) {
+            T sum = T(0);
+            for (uint32_t c = 0; c < d; ++c) sum = alg_fma(vs[c], upper[u * d + c], sum);
+            lower[u] += sum * inv_k;
+        }
+        __syncthreads();
+    }
+    const uint32_t c = threadIdx.x % d;
+    T mine = threadIdx.x < d ? g[threadIdx.x] : T(0);  // level 1 passes straight through
+    const uint32_t first = N >= 2 ? lv.off[2] : lv.total();
+    for (uint32_t j = first + threadIdx.x; j < lv.total(); j += blockDim.x) {
+        const uint32_t k = lv.level_of(j);
+        const uint32_t u = (j - lv.off[k]) / d;  // (j - off[k]) % d == c because off[k] - off[2] and blockDim are multiples of d
+        mine = alg_fma(lin[lv.off[k - 1] + u], g[j] * (T(1) / static_cast<T>(k)), mine);
+    }
+    atomicAdd(&acc[c], mine);
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) d_disp[b * d + i] = acc[i];
+}
+
 template <typename T>
 void launch_linear_sig(const T* disp, T* out_level1, uint64_t out_stride, const Levels& lv, uint64_t batch,
                        bool write_scalar, cudaStream_t stream) {
@@ -77,11 +124,19 @@ void launch_linear_sig(const T* disp, T* out_level1, uint64_t out_stride, const 
     check_launch("linear_sig kernel");
 }
 
+// L: the linear signature itself (same stride as dL); dL is scratch and is overwritten when dim <= 256.
 template <typename T>
-void launch_linear_sig_adjoint(const T* disp, const T* dL_level1, uint64_t dl_stride, T* d_disp, const Levels& lv,
-                               uint64_t batch, cudaStream_t stream) {
+void launch_linear_sig_adjoint(const T* disp, const T* L, T* dL_level1, uint64_t dl_stride, T* d_disp,
+                               const Levels& lv, uint64_t batch, cudaStream_t stream) {
     if (batch == 0) return;
     if (batch > 0x7fffffffull) throw std::invalid_argument("batch too large for one kernel launch");
+    if (lv.dim <= 256) {
+        const unsigned threads = lv.dim * (256 / lv.dim);  // a multiple of dim, at most 256
+        linear_sig_adjoint_recursive_kernel<T><<<static_cast<unsigned>(batch), threads, 2 * size_t(lv.dim) * sizeof(T),
+                                                 stream>>>(disp, L, dL_level1, dl_stride, d_disp, lv);
+        check_launch("linear_sig adjoint kernel");
+        return;
+    }
     const size_t smem = size_t(lv.dim) * sizeof(T);
     const bool use_shared = smem <= 32 * 1024;
     if (!use_shared) SIG_CUDA_CHECK(cudaMemsetAsync(d_disp, 0, batch * lv.dim * sizeof(T), stream));
@@ -479,7 +534,7 @@ void sig_join_backprop_entry(const T* d_out, T* d_sig, T* d_displacement, const 
             launch_chen_left_adjoint<T>(g + shift, s.stride, lin, S, ds + shift, s.stride, s, st);
             launch_chen_right_adjoint<T>(g + shift, s.stride, a + shift, s.stride, dlin, S, s, st);
         }
-        launch_linear_sig_adjoint<T>(v, dlin, S, dv, lv, batch, st);
+        launch_linear_sig_adjoint<T>(v, lin, dlin, S, dv, lv, batch, st);
     };
     int device = -1;
     if (all_on_device({d_out, d_sig, d_displacement, sig, displacement}, "sig_join_backprop_cuda", &device)) {
