@@ -1,7 +1,7 @@
 """Pins the oracle's signature -> log-signature map (expanded and Lyndon-word coordinates).
 
-The reference's fixture holds no log-signature vectors for these methods, so the pins are
-closed forms and identities: the logarithm of a straight segment's signature is the segment,
+Closed forms and identities (the reference's golden vectors are checked in
+test_oracle_log_golden.py): the logarithm of a straight segment's signature is the segment,
 level 2 is S_2 - S_1 (x) S_1 / 2, exp(log S) = S through the oracle's tensor exponential, the
 number of Lyndon coordinates is Witt's necklace count (pysiglib/sig_length.py:97-163), and the
 backward pass agrees with central finite differences."""
