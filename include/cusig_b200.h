@@ -222,8 +222,13 @@ int sigb200_sig_backprop_sharded_d(const double* path, double* out, const double
  * The increment-gradient scratch (batch * (length-1) * dimension values) lives in a static
  * 32 MiB device buffer inside the library (sigb200_noalloc_scratch_bytes()); larger requests,
  * host pointers and shapes outside the register-tile kernel table are rejected with code 2.
+ * Every buffer must be device memory of the GPU that holds `out`; anything else is rejected with
+ * code 2 before a kernel is launched.
  * The first call on a device looks the buffer up (cudaGetSymbolAddress) and should come before
- * any stream capture.  All calls share the buffer: the used part is cleared on `stream` first,
+ * any stream capture.  That first call, and the first call of each (dimension, degree, flags,
+ * dtype) on a device, make the CUDA runtime load device code, which does take device memory:
+ * make one warm-up call per device and shape while memory is still available; later calls
+ * allocate nothing.  All calls share the buffer: the used part is cleared on `stream` first,
  * and calls whose GPU work overlaps race on it.  Asynchronous on `stream` unless synchronize != 0. */
 int sigb200_sig_backprop_noalloc_f(const float* path, float* out, const float* sig_derivs, const float* sig,
                                    uint64_t batch_size, uint64_t dimension, uint64_t length, uint64_t degree,
@@ -258,10 +263,21 @@ int sigb200_describe_plan(char* buffer, uint64_t buffer_len, uint64_t batch_size
                           uint64_t length, uint64_t degree, bool time_aug, bool lead_lag, int is_double,
                           int backward);
 
-/* FMA-pipe peak probe for the benchmark: `blocks` CTAs x 256 threads x iters x 64 independent
- * register-resident FMAs in float (is_double = 0) or double; `sink` is any 8-byte device
- * buffer.  Asynchronous on `stream`.  No counterpart in the reference. */
-int sigb200_fma_peak(int is_double, void* sink, int blocks, int iters, void* stream);
+/* Test hook: pins the register-tile variant (chain length, group) and the number of time segments
+ * of the forward (backward = 0) or backward (1) sweep for shapes that have such a variant
+ * compiled; chain_length < 0 clears it.  No counterpart in the reference. */
+void sigb200_set_forced_plan(int backward, int chain_length, int group, int segments);
+
+/* Test hook for the out-of-memory paths: the next `count` scratch / staging requests of this
+ * library report cudaErrorMemoryAllocation on the host, without touching the device.  The calls
+ * then recover by halving their batch piece, as the reference's workspace allocation does
+ * (siglib/cusig/cu_runtime_utils.h:212-235).  SIGB200_FAIL_ALLOCS=<count> in the environment
+ * arms the same thing at load time. */
+void sigb200_inject_alloc_failures(int count);
+
+/* Bytes this library's own stream-ordered memory pool currently holds on `device`
+ * (scratch and staging buffers are kept there between calls until cusig_shutdown). */
+uint64_t sigb200_pool_reserved_bytes(int device);
 
 /* Number of kernels this library has launched in the calling process (all threads). */
 uint64_t sigb200_launch_count(void);

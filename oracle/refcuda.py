@@ -26,6 +26,10 @@ def library():
             g = getattr(lib, "sig_backprop_cuda_" + suf)
             g.argtypes = (p, p, p, p, u64, u64, u64, u64, b, b, real, b, p, u64, u64, u64)
             g.restype = ctypes.c_int
+            for name in ("transform_path_cuda_", "transform_path_backprop_cuda_"):
+                t = getattr(lib, name + suf)
+                t.argtypes = (p, p, u64, u64, u64, b, b, real)
+                t.restype = ctypes.c_int
         _lib = lib
     return _lib
 
@@ -83,4 +87,33 @@ def sig_backprop(path, sig_, derivs, degree, *, time_aug=False, lead_lag=False, 
                                                          *_correction_args(correction, B, L))
     if rc:
         raise RuntimeError("reference sig_backprop_cuda failed with code %d" % rc)
+    return out
+
+
+def transform_path(path, *, time_aug=False, lead_lag=False, end_time=1.0):
+    """Reference transform_path_cuda_* on a contiguous CUDA tensor (B, L, d)."""
+    import torch
+    B, L, d = path.shape
+    out = torch.empty((B, 2 * L - 1 if lead_lag else L, (2 * d if lead_lag else d) + (1 if time_aug else 0)),
+                      dtype=path.dtype, device=path.device)
+    real = _real(path)
+    suf = "f" if real is ctypes.c_float else "d"
+    rc = getattr(library(), "transform_path_cuda_" + suf)(_ptr(path), _ptr(out), B, d, L, time_aug, lead_lag,
+                                                           real(end_time))
+    if rc:
+        raise RuntimeError("reference transform_path_cuda failed with code %d" % rc)
+    return out
+
+
+def transform_path_backprop(derivs, length, dimension, *, time_aug=False, lead_lag=False, end_time=1.0):
+    """Reference transform_path_backprop_cuda_*: derivs (B, L', d') -> gradient (B, L, d)."""
+    import torch
+    B = derivs.shape[0]
+    out = torch.empty((B, length, dimension), dtype=derivs.dtype, device=derivs.device)
+    real = _real(derivs)
+    suf = "f" if real is ctypes.c_float else "d"
+    rc = getattr(library(), "transform_path_backprop_cuda_" + suf)(_ptr(derivs), _ptr(out), B, dimension, length,
+                                                                    time_aug, lead_lag, real(end_time))
+    if rc:
+        raise RuntimeError("reference transform_path_backprop_cuda failed with code %d" % rc)
     return out

@@ -11,8 +11,8 @@ from .sig_join import linear_sig, sig_join, sig_join_backprop
 from .transform_path import transform_path, transform_path_backprop
 from .sig_length import log_sig_length, sig_length
 from .log_sig import log_sig, prepare_log_sig, sig_to_log_sig, sig_to_log_sig_backprop
-from .sharded import sig_backprop_sharded, sig_sharded
+from .sharded import all_gather_signatures, sig_backprop_sharded, sig_multi_device, sig_sharded
 from . import torch_api
 
 __version__ = "0.1.0"
-__all__ = ["sig", "signature", "sig_combine", "sig_combine_backprop", "sig_backprop", "sig_coef", "sig_coef_backprop", "extract_sig_coef", "sig_join", "sig_join_backprop", "linear_sig", "transform_path", "transform_path_backprop", "sig_length", "log_sig_length", "log_sig", "sig_to_log_sig", "sig_to_log_sig_backprop", "prepare_log_sig", "sig_sharded", "sig_backprop_sharded", "torch_api"]
+__all__ = ["sig", "signature", "sig_combine", "sig_combine_backprop", "sig_backprop", "sig_coef", "sig_coef_backprop", "extract_sig_coef", "sig_join", "sig_join_backprop", "linear_sig", "transform_path", "transform_path_backprop", "sig_length", "log_sig_length", "log_sig", "sig_to_log_sig", "sig_to_log_sig_backprop", "prepare_log_sig", "sig_sharded", "sig_backprop_sharded", "sig_multi_device", "all_gather_signatures", "torch_api"]

@@ -20,6 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "_build")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libcusig.so")
+BENCH_LIB = os.path.join(LIB_DIR, "libsigb200_bench.so")  # FMA-peak probe; loaded by bench.py only
 
 NVCC_FLAGS = ["-std=c++17", "--expt-relaxed-constexpr", "-gencode", "arch=compute_100a,code=sm_100a",
               "-lineinfo", "-O3", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-DNDEBUG"]
@@ -36,7 +37,7 @@ def _tile_parts():
 
 def _units():
     """(object name, source, extra flags) for every translation unit."""
-    units = [(n + ".o", n + ".cu", []) for n in ("abi", "dispatch", "runtime", "sig_generic", "sig_tile_dispatch", "sig_algebra", "sig_log", "sig_coef", "microbench", "noalloc")]
+    units = [(n + ".o", n + ".cu", []) for n in ("abi", "dispatch", "runtime", "sig_generic", "sig_tile_dispatch", "sig_algebra", "sig_log", "sig_coef", "noalloc")]
     for k in range(_tile_parts()):
         units.append(("sig_tile_inst_%d.o" % k, "sig_tile_inst.cu", ["-DSIG_TILE_PART=%d" % k]))
     return units
@@ -45,10 +46,11 @@ def _units():
 def _stamp(dev=False):
     h = hashlib.sha256((" ".join(NVCC_FLAGS) + (" dev" if dev else "") +
                         os.environ.get("SIGB200_NO_PACKED_F32", "0")).encode())
-    for name in sorted(os.listdir(CSRC)):
-        if name.endswith((".h", ".cuh", ".cu")):
-            with open(os.path.join(CSRC, name), "rb") as f:
-                h.update(name.encode() + f.read())
+    for folder in (CSRC, os.path.join(CSRC, "bench")):
+        for name in sorted(os.listdir(folder)):
+            if name.endswith((".h", ".cuh", ".cu")):
+                with open(os.path.join(folder, name), "rb") as f:
+                    h.update(name.encode() + f.read())
     with open(os.path.join(HERE, "..", "include", "cusig_b200.h"), "rb") as f:
         h.update(f.read())
     return h.hexdigest()
@@ -129,6 +131,11 @@ def build(force=False, jobs=None, verbose=False, dev=None):
     proc = subprocess.run(link, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (proc.stdout, proc.stderr))
+    bench = [_nvcc(), "-shared", "-o", BENCH_LIB, os.path.join(CSRC, "bench", "fma_peak.cu"), "-O3", "-lineinfo",
+             "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
+    proc = subprocess.run(bench, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("building the benchmark helper failed:\n%s\n%s" % (proc.stdout, proc.stderr))
     with open(stamp_file, "w") as f:
         f.write(stamp)
     return LIB

@@ -352,6 +352,16 @@ SIG_API int sigb200_describe_plan(char* buffer, uint64_t buffer_len, uint64_t ba
 
 SIG_API uint64_t sigb200_launch_count(void) { return launch_count(); }
 
+SIG_API void sigb200_set_forced_plan(int backward, int chain_length, int group, int segments) {
+    set_forced_plan(backward != 0, chain_length, group, segments);
+}
+
+SIG_API void sigb200_inject_alloc_failures(int count) { inject_alloc_failures(count); }
+
+SIG_API uint64_t sigb200_pool_reserved_bytes(int device) {
+    try { return pool_reserved_bytes(device); } catch (...) { return 0; }
+}
+
 // ---- stubs for the rest of the reference's CUDA surface (pysiglib/load_siglib.py:165-183,420-641) ----
 
 #define SIG_STUB(name) SIG_API int name(...) { return stub_not_built(#name); }

@@ -86,11 +86,18 @@ void run_staged(std::vector<StagedOperand> ops, int device, Body body) {
 
 // true: all device, false: all host; throws on a mix
 bool all_on_device(std::initializer_list<const void*> ptrs, const char* who, int* device) {
-    int on = 0, off = 0;
+    int on = 0, off = 0, home = -1;
     for (const void* p : ptrs) {
         if (!p) continue;
         const PointerInfo info = classify_pointer(p);
-        if (info.on_device) { ++on; *device = info.device; } else ++off;
+        if (!info.on_device) { ++off; continue; }
+        ++on;
+        if (info.managed) { if (home < 0) *device = info.device; continue; }
+        if (home >= 0 && info.device != home)
+            throw std::invalid_argument(std::string(who) + ": all buffers must live on the same device (found devices " +
+                                        std::to_string(home) + " and " + std::to_string(info.device) + ")");
+        home = info.device;
+        *device = home;
     }
     if (on && off)
         throw std::invalid_argument(std::string(who) + ": all buffers must be device pointers or all host pointers");

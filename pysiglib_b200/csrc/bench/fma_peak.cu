@@ -1,10 +1,10 @@
 // Register-resident FMA loop used by the benchmark to measure the FP32 / FP64 FMA-pipe
 // peak of the device it runs on (the denominator of the roofline of this FMA-bound path).
-#include "../../include/cusig_b200.h"
-#include "common.h"
-#include "runtime.h"
+// Built into its own small library (libsigb200_bench.so) that only bench.py loads; it is not
+// part of libcusig.so.
+#include <cuda_runtime.h>
 
-namespace sigb200 {
+namespace sigb200_bench {
 namespace {
 
 template <typename T>
@@ -55,29 +55,19 @@ __global__ void __launch_bounds__(256) fma2_peak_kernel(float* sink, int iters, 
     if (s == -1.2345f) sink[0] = s;
 }
 
-template <typename T>
-void run_fma_peak(void* sink, int blocks, int iters, cudaStream_t stream) {
-    fma_peak_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<T*>(sink), iters, T(0.999), T(0.001));
-    SIG_CUDA_CHECK(cudaGetLastError());
-    count_launch();
-}
-
-// packed f32x2 variant: same FMA count per thread (8 pair accumulators x 4 x iters x 2)
-void run_fma2_peak(void* sink, int blocks, int iters, cudaStream_t stream) {
-    fma2_peak_kernel<<<blocks, 256, 0, stream>>>(static_cast<float*>(sink), iters, 0.999f, 0.001f);
-    SIG_CUDA_CHECK(cudaGetLastError());
-    count_launch();
-}
-
 }  // namespace
-}  // namespace sigb200
+}  // namespace sigb200_bench
 
 // Launches `blocks` CTAs of 256 threads, each thread issuing iters * 64 dependent-free
-// FMAs (16 independent chains).  FMAs per launch = blocks * 256 * iters * 64.
+// FMAs (16 independent chains): FMAs per launch = blocks * 256 * iters * 64.
+// mode 0: scalar float, 1: double, 2: packed float (same FMA count: 8 pair accumulators).
+// `sink` is any 8-byte device buffer.  Asynchronous on `stream`; returns the cudaError_t of the launch.
 extern "C" __attribute__((visibility("default")))
-int sigb200_fma_peak(int is_double, void* sink, int blocks, int iters, void* stream) {
-    SIG_SAFE_CALL(
-        if (is_double == 2) sigb200::run_fma2_peak(sink, blocks, iters, static_cast<cudaStream_t>(stream));
-        else if (is_double) sigb200::run_fma_peak<double>(sink, blocks, iters, static_cast<cudaStream_t>(stream));
-        else sigb200::run_fma_peak<float>(sink, blocks, iters, static_cast<cudaStream_t>(stream)));
+int sigb200_bench_fma_peak(int mode, void* sink, int blocks, int iters, void* stream) {
+    using namespace sigb200_bench;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (mode == 2) fma2_peak_kernel<<<blocks, 256, 0, st>>>(static_cast<float*>(sink), iters, 0.999f, 0.001f);
+    else if (mode == 1) fma_peak_kernel<double><<<blocks, 256, 0, st>>>(static_cast<double*>(sink), iters, 0.999, 0.001);
+    else fma_peak_kernel<float><<<blocks, 256, 0, st>>>(static_cast<float*>(sink), iters, 0.999f, 0.001f);
+    return static_cast<int>(cudaGetLastError());
 }

@@ -16,6 +16,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <memory>
 #include <vector>
 
 #include "kernels.h"
@@ -49,70 +50,87 @@ struct HostOperand {
     uint64_t bytes_per_path;
 };
 
+// Calls run(begin, count) over [0, batch) in pieces, halving the piece after every
+// std::bad_alloc until a single path fails too (the reference's recovery from
+// cudaErrorMemoryAllocation, siglib/cusig/cu_runtime_utils.h:212-235).  run() must take its
+// scratch before it enqueues work that cannot be repeated.
+template <typename Run>
+void with_batch_backoff(uint64_t batch, Run&& run) {
+    uint64_t piece = batch, begin = 0;
+    while (begin < batch) {
+        const uint64_t count = std::min(piece, batch - begin);
+        try {
+            run(begin, count);
+            begin += count;
+        } catch (const std::bad_alloc&) {
+            if (piece <= 1) throw;
+            piece = (piece + 1) / 2;
+        }
+    }
+}
+
+// Pipelined pass over the batch for host-resident operands: the batch is cut into chunks that
+// are copied in, computed and copied out on three streams through two staging slots, so that
+// the copies of one chunk overlap the kernels of its neighbours.  `wave_paths` is the number of
+// paths that fill the GPU exactly once with the kernels compute() will launch (0 = unknown);
+// chunks are whole multiples of it so that no chunk ends in a partly filled wave.
 template <typename Compute>
 void run_host_pipeline(uint64_t batch, const std::vector<HostOperand>& inputs, void* host_out,
-                       uint64_t out_bytes_per_path, Compute&& compute) {
+                       uint64_t out_bytes_per_path, uint64_t wave_paths, Compute&& compute) {
     DeviceContext& ctx = device_context(current_device());
     std::lock_guard<std::mutex> lock(ctx.mu);
 
+    auto aligned = [](uint64_t bytes) { return (bytes + 255) / 256 * 256; };
     uint64_t per_path = out_bytes_per_path;
     for (const auto& in : inputs) per_path += in.bytes_per_path;
     per_path = std::max<uint64_t>(per_path, 1);
-    // Up to 8 chunks so copies overlap compute, but no chunk below ~32 MiB of staged operands
-    // (small calls go as one piece: chunking them only shrinks the kernels), none above 2 GiB.
+    // The first chunk's copy-in and the last chunk's copy-out are not hidden behind any kernel,
+    // so chunks are kept small: about 16 MiB of staged operands, at most 32 chunks, none above 2 GiB.
     const uint64_t total_bytes = per_path * batch;
-    const uint64_t n_target = std::min<uint64_t>(8, std::max<uint64_t>(1, total_bytes / (32ull << 20)));
+    const uint64_t n_target = std::min<uint64_t>(32, std::max<uint64_t>(1, total_bytes / (16ull << 20)));
     uint64_t chunk = (batch + n_target - 1) / n_target;
+    if (wave_paths > 0 && n_target > 1) chunk = std::max<uint64_t>(1, (chunk + wave_paths / 2) / wave_paths) * wave_paths;
     chunk = std::min<uint64_t>(chunk, std::max<uint64_t>(1, (2ull << 30) / per_path));
-    chunk = std::max<uint64_t>(chunk, 1);
-    const uint64_t n_chunks = (batch + chunk - 1) / chunk;
-    const int n_buf = n_chunks > 1 ? 2 : 1;
+    chunk = std::max<uint64_t>(std::min(chunk, batch), 1);
 
-    struct Slot {
-        std::vector<void*> in;
-        void* out = nullptr;
-        cudaEvent_t computed = nullptr, copied_out = nullptr, copied_in = nullptr;
-    };
-    std::vector<Slot> slots(n_buf);
-    cudaEvent_t ready = nullptr;
-    auto cleanup = [&]() {
+    // staging slots: kept between calls, grown on demand; on out-of-memory the chunk is halved
+    uint64_t slot_bytes = 0;
+    int n_buf = 1;
+    for (;;) {
+        slot_bytes = aligned(std::max<uint64_t>(out_bytes_per_path * chunk, 16));
+        for (const auto& in : inputs) slot_bytes += aligned(std::max<uint64_t>(in.bytes_per_path * chunk, 16));
+        n_buf = (batch + chunk - 1) / chunk > 1 ? 2 : 1;
+        try {
+            reserve_staging(ctx, slot_bytes, n_buf);
+            break;
+        } catch (const std::bad_alloc&) {
+            if (chunk <= 1) throw;
+            chunk = (chunk + 1) / 2;
+        }
+    }
+    const uint64_t n_chunks = (batch + chunk - 1) / chunk;
+
+    auto drain = [&]() {
         (void)cudaStreamSynchronize(ctx.copy_in);
         (void)cudaStreamSynchronize(ctx.compute);
         (void)cudaStreamSynchronize(ctx.copy_out);
-        for (auto& sl : slots) {
-            for (void* p : sl.in) if (p) (void)cudaFreeAsync(p, ctx.compute);
-            if (sl.out) (void)cudaFreeAsync(sl.out, ctx.compute);
-            if (sl.computed) (void)cudaEventDestroy(sl.computed);
-            if (sl.copied_out) (void)cudaEventDestroy(sl.copied_out);
-            if (sl.copied_in) (void)cudaEventDestroy(sl.copied_in);
-        }
-        if (ready) (void)cudaEventDestroy(ready);
     };
     try {
-        for (auto& sl : slots) {
-            sl.in.assign(inputs.size(), nullptr);
-            for (size_t i = 0; i < inputs.size(); ++i) {
-                const uint64_t bytes = std::max<uint64_t>(inputs[i].bytes_per_path * chunk, 16);
-                const cudaError_t err = cudaMallocAsync(&sl.in[i], bytes, ctx.compute);
-                if (err == cudaErrorMemoryAllocation) { (void)cudaGetLastError(); throw std::bad_alloc(); }
-                SIG_CUDA_CHECK(err);
-            }
-            const cudaError_t err = cudaMallocAsync(&sl.out, std::max<uint64_t>(out_bytes_per_path * chunk, 16), ctx.compute);
-            if (err == cudaErrorMemoryAllocation) { (void)cudaGetLastError(); throw std::bad_alloc(); }
-            SIG_CUDA_CHECK(err);
-            SIG_CUDA_CHECK(cudaEventCreateWithFlags(&sl.computed, cudaEventDisableTiming));
-            SIG_CUDA_CHECK(cudaEventCreateWithFlags(&sl.copied_out, cudaEventDisableTiming));
-            SIG_CUDA_CHECK(cudaEventCreateWithFlags(&sl.copied_in, cudaEventDisableTiming));
-        }
-        SIG_CUDA_CHECK(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
-        SIG_CUDA_CHECK(cudaEventRecord(ready, ctx.compute));
-        SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_in, ready, 0));
-        SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_out, ready, 0));
-
+        SIG_CUDA_CHECK(cudaEventRecord(ctx.ready, ctx.compute));
+        SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_in, ctx.ready, 0));
+        SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_out, ctx.ready, 0));
+        std::vector<void*> din(inputs.size());
         for (uint64_t c = 0; c < n_chunks; ++c) {
-            Slot& sl = slots[c % n_buf];
+            StagingSlot& sl = ctx.slots[c % n_buf];
             const uint64_t begin = c * chunk;
             const uint64_t count = std::min(chunk, batch - begin);
+            unsigned char* cursor = static_cast<unsigned char*>(sl.buffer);
+            void* dout = cursor;
+            cursor += aligned(std::max<uint64_t>(out_bytes_per_path * chunk, 16));
+            for (size_t i = 0; i < inputs.size(); ++i) {
+                din[i] = cursor;
+                cursor += aligned(std::max<uint64_t>(inputs[i].bytes_per_path * chunk, 16));
+            }
             if (c >= uint64_t(n_buf)) {
                 // the slot's previous occupant must have been consumed before it is overwritten
                 SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_in, sl.computed, 0));
@@ -121,16 +139,16 @@ void run_host_pipeline(uint64_t batch, const std::vector<HostOperand>& inputs, v
             for (size_t i = 0; i < inputs.size(); ++i) {
                 const uint64_t bpp = inputs[i].bytes_per_path;
                 if (bpp == 0) continue;
-                SIG_CUDA_CHECK(cudaMemcpyAsync(sl.in[i], static_cast<const char*>(inputs[i].host) + begin * bpp,
+                SIG_CUDA_CHECK(cudaMemcpyAsync(din[i], static_cast<const char*>(inputs[i].host) + begin * bpp,
                                                count * bpp, cudaMemcpyHostToDevice, ctx.copy_in));
             }
             SIG_CUDA_CHECK(cudaEventRecord(sl.copied_in, ctx.copy_in));
             SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.compute, sl.copied_in, 0));
-            compute(sl.in, sl.out, count, ctx.compute);
+            compute(din, dout, count, ctx.compute);
             SIG_CUDA_CHECK(cudaEventRecord(sl.computed, ctx.compute));
             SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_out, sl.computed, 0));
             if (out_bytes_per_path)
-                SIG_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(host_out) + begin * out_bytes_per_path, sl.out,
+                SIG_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(host_out) + begin * out_bytes_per_path, dout,
                                                count * out_bytes_per_path, cudaMemcpyDeviceToHost, ctx.copy_out));
             SIG_CUDA_CHECK(cudaEventRecord(sl.copied_out, ctx.copy_out));
         }
@@ -138,26 +156,73 @@ void run_host_pipeline(uint64_t batch, const std::vector<HostOperand>& inputs, v
         SIG_CUDA_CHECK(cudaStreamSynchronize(ctx.compute));
         SIG_CUDA_CHECK(cudaStreamSynchronize(ctx.copy_out));
     } catch (...) {
-        cleanup();
+        drain();
         throw;
     }
-    cleanup();
 }
+
+// Device-side "output holds NaN / Inf" flag of one forward call: an int in scratch that the
+// kernels set, read back once at the end of the call.
+struct NonfiniteFlag {
+    Scratch mem;
+    cudaStream_t stream;
+    NonfiniteFlag(cudaStream_t st) : mem(sizeof(int), st), stream(st) {
+        SIG_CUDA_CHECK(cudaMemsetAsync(mem.get(), 0, sizeof(int), st));
+    }
+    int* device() const { return mem.as<int>(); }
+    // copies the flag to `host` and waits for the stream
+    void fetch(int* host) {
+        SIG_CUDA_CHECK(cudaMemcpyAsync(host, mem.get(), sizeof(int), cudaMemcpyDeviceToHost, stream));
+        SIG_CUDA_CHECK(cudaStreamSynchronize(stream));
+    }
+};
 
 }  // namespace
 
+// One piece of a forward call; takes its scratch before it launches anything.
 template <typename T>
-void forward_on_device(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream) {
-    if (s.batch == 0 || s.stride == 0) return;
+void forward_piece(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream, int* nonfinite) {
     if (s.len <= 1 || s.degree <= 1 || s.dim == 1) {
         launch_trivial_forward<T>(path, out, s, end_time, stream);
+        if (nonfinite) launch_nonfinite_scan<T>(out, s.batch * s.stride, nonfinite, stream);
         return;
     }
-    if (kernel_policy() == 0 && launch_tile_forward<T>(path, out, s, end_time, stream)) return;
+    // the register-tile sweep checks its own results as it stores them (no extra pass over the output)
+    bool flag_done = false;
+    if (kernel_policy() == 0 && launch_tile_forward<T>(path, out, s, end_time, stream, nonfinite, &flag_done)) {
+        if (nonfinite && !flag_done) launch_nonfinite_scan<T>(out, s.batch * s.stride, nonfinite, stream);
+        return;
+    }
     const uint64_t elems = generic_forward_scratch_elems(s);
     const unsigned ctas = generic_ctas(s, sm_count_of_current_device(), elems * sizeof(T));
     Scratch scratch(checked_mul(checked_mul(elems, ctas, "scratch"), sizeof(T), "scratch"), stream);
     launch_generic_forward<T>(path, out, s, end_time, scratch.as<T>(), ctas, stream);
+    if (nonfinite) launch_nonfinite_scan<T>(out, s.batch * s.stride, nonfinite, stream);
+}
+
+template <typename T>
+void forward_on_device(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream, int* nonfinite) {
+    if (s.batch == 0 || s.stride == 0) return;
+    with_batch_backoff(s.batch, [&](uint64_t begin, uint64_t count) {
+        SigShape piece = s;
+        piece.batch = count;
+        forward_piece<T>(path + begin * s.data_len * s.data_dim, out + begin * s.stride, piece, end_time, stream,
+                         nonfinite);
+    });
+}
+
+template <typename T>
+void backward_piece(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s, T end_time,
+                    cudaStream_t stream) {
+    if (kernel_policy() == 0 && tile_backward_available<T>(s)) {
+        const uint64_t g_elems = checked_mul(s.batch, checked_mul(s.data_len - 1, s.data_dim, "scratch"), "scratch");
+        Scratch incr(checked_mul(g_elems, sizeof(T), "scratch"), stream);
+        if (launch_tile_backward<T>(path, out, sig_derivs, sig, s, end_time, incr.as<T>(), stream)) return;
+    }
+    const uint64_t elems = generic_backward_scratch_elems(s);
+    const unsigned ctas = generic_ctas(s, sm_count_of_current_device(), elems * sizeof(T));
+    Scratch scratch(checked_mul(checked_mul(elems, ctas, "scratch"), sizeof(T), "scratch"), stream);
+    launch_generic_backward<T>(path, out, sig_derivs, sig, s, end_time, scratch.as<T>(), ctas, stream);
 }
 
 template <typename T>
@@ -176,15 +241,12 @@ void backward_on_device(const T* path, T* out, const T* sig_derivs, const T* sig
     }
     if (s.degree > kMaxDegree)
         throw std::invalid_argument("sig_backprop on CUDA requires degree <= 64. Reduce the truncation level.");
-    if (kernel_policy() == 0 && tile_backward_available<T>(s)) {
-        const uint64_t g_elems = checked_mul(s.batch, checked_mul(s.data_len - 1, s.data_dim, "scratch"), "scratch");
-        Scratch incr(checked_mul(g_elems, sizeof(T), "scratch"), stream);
-        if (launch_tile_backward<T>(path, out, sig_derivs, sig, s, end_time, incr.as<T>(), stream)) return;
-    }
-    const uint64_t elems = generic_backward_scratch_elems(s);
-    const unsigned ctas = generic_ctas(s, sm_count_of_current_device(), elems * sizeof(T));
-    Scratch scratch(checked_mul(checked_mul(elems, ctas, "scratch"), sizeof(T), "scratch"), stream);
-    launch_generic_backward<T>(path, out, sig_derivs, sig, s, end_time, scratch.as<T>(), ctas, stream);
+    with_batch_backoff(s.batch, [&](uint64_t begin, uint64_t count) {
+        SigShape piece = s;
+        piece.batch = count;
+        const uint64_t p_off = begin * s.data_len * s.data_dim, s_off = begin * s.stride;
+        backward_piece<T>(path + p_off, out + p_off, sig_derivs + s_off, sig + s_off, piece, end_time, stream);
+    });
 }
 
 template <typename T>
@@ -206,16 +268,13 @@ void signature_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, 
         const uint64_t corr_elems = corrected_elems(cv, batch, s.len - 1);
         const PointerInfo po = classify_pointer(out);
         if (po.on_device) {
-            if (!classify_pointer(path).on_device || !classify_pointer(correction).on_device)
-                throw std::invalid_argument("signature_cuda: path, correction and out must all be device pointers or all host pointers");
+            require_on_device({path, correction}, po.device, "signature_cuda");
             DeviceGuard guard(po.device);
             correction_forward_on_device<T>(path, out, s, end_time, cv, opt.stream);
             if (opt.nonfinite) {
-                Scratch flag(sizeof(int), opt.stream);
-                SIG_CUDA_CHECK(cudaMemsetAsync(flag.get(), 0, sizeof(int), opt.stream));
-                launch_nonfinite_scan<T>(out, s.batch * s.stride, flag.as<int>(), opt.stream);
-                SIG_CUDA_CHECK(cudaMemcpyAsync(opt.nonfinite, flag.get(), sizeof(int), cudaMemcpyDeviceToHost, opt.stream));
-                SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+                NonfiniteFlag flag(opt.stream);
+                launch_nonfinite_scan<T>(out, s.batch * s.stride, flag.device(), opt.stream);
+                flag.fetch(opt.nonfinite);
             } else if (opt.synchronize) {
                 SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
             }
@@ -239,11 +298,12 @@ void signature_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, 
         dcv.ptr = dc;
         correction_forward_on_device<T>(dp, dout, s, end_time, dcv, st);
         SIG_CUDA_CHECK(cudaMemcpyAsync(out, dout, no * sizeof(T), cudaMemcpyDeviceToHost, st));
-        SIG_CUDA_CHECK(cudaStreamSynchronize(st));
         if (opt.nonfinite) {
-            for (uint64_t i = 0; i < no && !*opt.nonfinite; ++i)
-                if (!std::isfinite(out[i])) *opt.nonfinite = 1;
+            NonfiniteFlag flag(st);
+            launch_nonfinite_scan<T>(dout, no, flag.device(), st);
+            flag.fetch(opt.nonfinite);
         }
+        SIG_CUDA_CHECK(cudaStreamSynchronize(st));
         return;
     }
 
@@ -253,16 +313,15 @@ void signature_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, 
         throw std::invalid_argument("signature_cuda: path and out must both be device pointers or both host pointers");
 
     if (!host_call) {
+        if (length * dimension != 0) require_on_device({path}, pout.device, "signature_cuda");
         DeviceGuard guard(pout.device);
-        forward_on_device<T>(path, out, s, end_time, opt.stream);
         if (opt.nonfinite) {
-            Scratch flag(sizeof(int), opt.stream);
-            SIG_CUDA_CHECK(cudaMemsetAsync(flag.get(), 0, sizeof(int), opt.stream));
-            launch_nonfinite_scan<T>(out, s.batch * s.stride, flag.as<int>(), opt.stream);
-            SIG_CUDA_CHECK(cudaMemcpyAsync(opt.nonfinite, flag.get(), sizeof(int), cudaMemcpyDeviceToHost, opt.stream));
-            SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
-        } else if (opt.synchronize) {
-            SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
+            NonfiniteFlag flag(opt.stream);
+            forward_on_device<T>(path, out, s, end_time, opt.stream, flag.device());
+            flag.fetch(opt.nonfinite);
+        } else {
+            forward_on_device<T>(path, out, s, end_time, opt.stream, nullptr);
+            if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
         }
         return;
     }
@@ -270,18 +329,17 @@ void signature_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, 
     // host operands: stage through the device selected by the caller (current device)
     DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
     std::vector<HostOperand> ins{{path, s.data_len * s.data_dim * sizeof(T)}};
-    run_host_pipeline(batch, ins, out, s.stride * sizeof(T),
+    // the check for NaN / Inf runs on the device while the chunks are there; only the flag comes back
+    std::unique_ptr<NonfiniteFlag> flag;
+    if (opt.nonfinite) flag.reset(new NonfiniteFlag(device_context(current_device()).compute));
+    run_host_pipeline(batch, ins, out, s.stride * sizeof(T), tile_wave_paths<T>(s, false),
         [&](const std::vector<void*>& din, void* dout, uint64_t count, cudaStream_t stream) {
             SigShape cs = s;
             cs.batch = count;
-            forward_on_device<T>(static_cast<const T*>(din[0]), static_cast<T*>(dout), cs, end_time, stream);
+            forward_on_device<T>(static_cast<const T*>(din[0]), static_cast<T*>(dout), cs, end_time, stream,
+                                 flag ? flag->device() : nullptr);
         });
-    if (opt.nonfinite) {
-        bool bad = false;
-        const uint64_t n = s.batch * s.stride;
-        for (uint64_t i = 0; i < n && !bad; ++i) bad = !(std::abs(double(out[i])) <= 1.7976931348623157e308);
-        *opt.nonfinite = bad ? 1 : 0;
-    }
+    if (flag) flag->fetch(opt.nonfinite);
 }
 
 template <typename T>
@@ -311,6 +369,7 @@ void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig
         if (po.on_device ? !others_on_device : !others_on_host)
             throw std::invalid_argument("sig_backprop_cuda: all buffers must be device pointers or all host pointers");
         if (po.on_device) {
+            require_on_device({path, sig, sig_derivs, correction}, po.device, "sig_backprop_cuda");
             DeviceGuard guard(po.device);
             correction_backward_on_device<T>(path, out, sig_derivs, sig, s, end_time, cv, opt.stream);
             if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
@@ -341,9 +400,8 @@ void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig
 
     const PointerInfo pout = classify_pointer(out);
     if (pout.on_device) {
-        if (!classify_pointer(path).on_device || (needs_sig && (!classify_pointer(sig).on_device ||
-                                                                !classify_pointer(sig_derivs).on_device)))
-            throw std::invalid_argument("sig_backprop_cuda: all buffers must be device pointers or all host pointers");
+        require_on_device({path}, pout.device, "sig_backprop_cuda");
+        if (needs_sig) require_on_device({sig, sig_derivs}, pout.device, "sig_backprop_cuda");
         DeviceGuard guard(pout.device);
         backward_on_device<T>(path, out, sig_derivs, sig, s, end_time, opt.stream);
         if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
@@ -353,7 +411,7 @@ void sig_backprop_entry(const T* path, T* out, const T* sig_derivs, const T* sig
     DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
     const uint64_t sig_bytes = needs_sig ? s.stride * sizeof(T) : 0;
     std::vector<HostOperand> ins{{path, s.data_len * s.data_dim * sizeof(T)}, {sig_derivs, sig_bytes}, {sig, sig_bytes}};
-    run_host_pipeline(batch, ins, out, s.data_len * s.data_dim * sizeof(T),
+    run_host_pipeline(batch, ins, out, s.data_len * s.data_dim * sizeof(T), tile_wave_paths<T>(s, true),
         [&](const std::vector<void*>& din, void* dout, uint64_t count, cudaStream_t stream) {
             SigShape cs = s;
             cs.batch = count;
@@ -382,8 +440,7 @@ void sig_combine_entry(const T* sig1, const T* sig2, T* out, uint64_t batch, uin
     };
     const PointerInfo pout = classify_pointer(out);
     if (pout.on_device) {
-        if (!classify_pointer(sig1).on_device || !classify_pointer(sig2).on_device)
-            throw std::invalid_argument("sig_combine_cuda: all buffers must be device pointers or all host pointers");
+        require_on_device({sig1, sig2}, pout.device, "sig_combine_cuda");
         DeviceGuard guard(pout.device);
         run(sig1, sig2, out, batch, opt.stream);
         if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
@@ -391,7 +448,7 @@ void sig_combine_entry(const T* sig1, const T* sig2, T* out, uint64_t batch, uin
     }
     DeviceGuard guard(opt.device >= 0 ? opt.device : current_device());
     std::vector<HostOperand> ins{{sig1, s.stride * sizeof(T)}, {sig2, s.stride * sizeof(T)}};
-    run_host_pipeline(batch, ins, out, s.stride * sizeof(T),
+    run_host_pipeline(batch, ins, out, s.stride * sizeof(T), 0,
         [&](const std::vector<void*>& din, void* dout, uint64_t count, cudaStream_t stream) {
             run(static_cast<const T*>(din[0]), static_cast<const T*>(din[1]), static_cast<T*>(dout), count, stream);
         });
@@ -422,9 +479,7 @@ void sig_combine_backprop_entry(const T* deriv, T* sig1_deriv, T* sig2_deriv, co
     };
     const PointerInfo pout = classify_pointer(sig1_deriv);
     if (pout.on_device) {
-        if (!classify_pointer(deriv).on_device || !classify_pointer(sig2_deriv).on_device ||
-            !classify_pointer(sig1).on_device || !classify_pointer(sig2).on_device)
-            throw std::invalid_argument("sig_combine_backprop_cuda: all buffers must be device pointers or all host pointers");
+        require_on_device({deriv, sig2_deriv, sig1, sig2}, pout.device, "sig_combine_backprop_cuda");
         DeviceGuard guard(pout.device);
         run(deriv, sig1_deriv, sig2_deriv, sig1, sig2, opt.stream);
         if (opt.synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(opt.stream));
@@ -450,7 +505,7 @@ void sig_combine_backprop_entry(const T* deriv, T* sig1_deriv, T* sig2_deriv, co
     template void sig_combine_backprop_entry<T>(const T*, T*, T*, const T*, const T*, uint64_t, uint64_t, uint64_t, \
                                                 bool, const CallOptions&);                                \
     template void sig_combine_entry<T>(const T*, const T*, T*, uint64_t, uint64_t, uint64_t, bool, const CallOptions&); \
-    template void forward_on_device<T>(const T*, T*, const SigShape&, T, cudaStream_t);                   \
+    template void forward_on_device<T>(const T*, T*, const SigShape&, T, cudaStream_t, int*);             \
     template void backward_on_device<T>(const T*, T*, const T*, const T*, const SigShape&, T, cudaStream_t); \
     template void signature_entry<T>(const T*, T*, uint64_t, uint64_t, uint64_t, uint64_t, bool, bool, T, bool, \
                                      bool, const T*, uint64_t, const CallOptions&, uint64_t, uint64_t);   \

@@ -16,8 +16,10 @@ struct CallOptions {
     int* nonfinite = nullptr;       // host int: set to 1 if the forward output holds NaN / Inf
 };
 
+// `nonfinite`: device int that is set to 1 when the output holds NaN / Inf (nullptr = no check).
 template <typename T>
-void forward_on_device(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream);
+void forward_on_device(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream,
+                       int* nonfinite = nullptr);
 
 template <typename T>
 void backward_on_device(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,

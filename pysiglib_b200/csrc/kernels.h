@@ -47,8 +47,14 @@ void launch_generic_backward(const T* path, T* out, const T* sig_derivs, const T
 // them to point gradients in `out`.
 template <typename T>
 bool tile_forward_available(const SigShape& s);
+// `nonfinite` (device int, may be null): set to 1 when the stored signature holds NaN / Inf;
+// *nonfinite_checked tells whether the launched kernels did that check themselves.
 template <typename T>
-bool launch_tile_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream);
+bool launch_tile_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream,
+                         int* nonfinite = nullptr, bool* nonfinite_checked = nullptr);
+// Paths per full wave of the unsegmented register-tile sweep for this shape (0 = unknown).
+template <typename T>
+uint64_t tile_wave_paths(const SigShape& s, bool backward);
 template <typename T>
 bool tile_backward_available(const SigShape& s);
 template <typename T>

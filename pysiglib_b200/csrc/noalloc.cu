@@ -9,11 +9,19 @@
 // use a fixed buffer that is part of the library image instead.
 //
 // The scratch is a file-scope __device__ array of kNoAllocScratchBytes.  Every GPU on which
-// this library is loaded by a process holds that much memory until the process exits.
-// Host code cannot use the array's name as a pointer (on the host it names a stand-in
-// object, not device memory), so the device address is looked up once per device with
-// cudaGetSymbolAddress while that device is current, and cached.  That look-up happens in
-// the first call on a device; make that first call before any stream capture.
+// this library's device code is loaded by a process holds that much memory until the
+// process exits.  Host code cannot use the array's name as a pointer (on the host it names
+// a stand-in object, not device memory), so the device address is looked up once per device
+// with cudaGetSymbolAddress while that device is current, and cached.  That look-up happens
+// in the first call on a device; make that first call before any stream capture.
+//
+// "Allocates nothing" holds from the second call of a shape onwards.  The CUDA runtime loads
+// device code lazily: the module that holds the scratch array is brought onto a device by the
+// first cudaGetSymbolAddress there, and each kernel variant (dimension, degree, flags, dtype)
+// by its first launch or occupancy query, and both loads take device memory.  A host that is
+// about to hand the GPU's memory to its own allocator should therefore make one warm-up call
+// per device and per shape it will use while memory is still available; calls after that
+// neither allocate nor load anything.
 //
 // All calls share the one buffer and it keeps whatever the previous call left in it: the
 // part a call uses is cleared on the call's stream before the kernel runs, and two calls
@@ -70,13 +78,23 @@ void sig_backprop_noalloc(const T* path, T* out, const T* sig_derivs, const T* s
     const PointerInfo pout = classify_pointer(out);
     if (!pout.on_device || !classify_pointer(path).on_device)
         throw std::invalid_argument("the no-alloc entry points take device pointers only");
+    const bool needs_sig = !(s.len <= 1 || s.degree == 0);
+    if (needs_sig && (sig == nullptr || sig_derivs == nullptr))
+        throw std::invalid_argument("sig_backprop_cuda received a null pointer");
+    // every buffer a kernel will dereference must be device memory of out's GPU: a host pointer
+    // or another GPU's memory would fault on the device, so it is turned away here
+    if (needs_sig && (!classify_pointer(sig).on_device || !classify_pointer(sig_derivs).on_device))
+        throw std::invalid_argument("the no-alloc entry points take device pointers only");
+    require_on_device({path}, pout.device, "sigb200_sig_backprop_noalloc");
+    if (needs_sig) require_on_device({sig, sig_derivs}, pout.device, "sigb200_sig_backprop_noalloc");
     DeviceGuard guard(pout.device);
     const uint64_t out_elems = checked_mul(batch, checked_mul(L, d, "path gradient"), "path gradient");
-    if (s.len <= 1 || s.degree == 0) {
+    if (!needs_sig) {
         launch_fill<T>(out, out_elems, T(0), stream);
+    } else if (s.degree == 1) {
+        // closed form, needs no scratch at all
+        launch_degree_one_backward<T>(path, out, sig_derivs, s, end_time, stream);
     } else {
-        if (sig == nullptr || sig_derivs == nullptr)
-            throw std::invalid_argument("sig_backprop_cuda received a null pointer");
         if (!tile_backward_available<T>(s))
             throw std::invalid_argument(
                 "this (dimension, degree) is not covered by the register-tile kernels, the only ones that run "

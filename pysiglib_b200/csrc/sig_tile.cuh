@@ -12,9 +12,10 @@
 // Forward: state in registers for the whole path, written once at the end.
 // Backward: final signature and seeds loaded into registers; per step the state is
 // rewound with the negated increment, the adjoint is pulled back, and the per-unit
-// d'-vector of increment gradients is summed over the warp with a halving butterfly
-// (d' - 1 shuffles instead of 5 d'), buffered per chunk in shared memory and added to the
-// global increment-gradient buffer with one atomic per (step, channel, warp).
+// d'-vector of increment gradients is summed over the warp through a shared-memory
+// transpose (every lane parks its vector in a row, then each lane sums one column),
+// buffered per chunk in shared memory and added to the global increment-gradient buffer
+// with one atomic per (step, channel, warp).
 //
 // These kernels replace the reference's thread-per-prefix kernels
 // (siglib/cusig/cu_signature.cu:183-298 signature_per_word_ker,
@@ -37,6 +38,10 @@ constexpr int next_pow2_c(int v) {
     while (r < v) r *= 2;
     return r;
 }
+
+template <typename T> __device__ __forceinline__ T max_finite();
+template <> __device__ __forceinline__ float max_finite<float>() { return 3.402823466e+38f; }
+template <> __device__ __forceinline__ double max_finite<double>() { return 1.7976931348623157e+308; }
 
 template <typename T> struct VecOf;
 template <> struct VecOf<float> { using type = float4; static constexpr int n = 4; };
@@ -162,7 +167,7 @@ __device__ __forceinline__ void commit_increments(T* zs, const ChunkRegs<T, Sh>&
 template <typename T, typename Sh, bool FLAGS, int WPB>
 __global__ void __launch_bounds__(WPB * 32)
 tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out, uint64_t batch, uint32_t stride,
-                    bool scalar, int nseg) {
+                    bool scalar, int nseg, int* __restrict__ nonfinite) {
     constexpr int DP = RowPad<T, Sh::D>::DP;
     constexpr int WPP = (Sh::UNITS + 31) / 32;  // warps per (path, segment)
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -225,6 +230,17 @@ tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out
             T* S = out + b * stride - (scalar ? 0 : 1);
             tile_store<T, Sh>(st, ix, S);
             if (scalar && u == 0) S[0] = T(1);
+            if (nonfinite != nullptr) {
+                // NaN / Inf check of what was just stored, on the registers: every coefficient of the
+                // signature is owned by exactly one unit (chain coefficients by all units sharing the
+                // prefix, which see the same value), so the union over units covers the whole output.
+                bool bad = false;
+#pragma unroll
+                for (int k = 1; k <= Sh::P; ++k) bad |= !(fabs(st.ch[k]) <= max_finite<T>());
+#pragma unroll
+                for (int i = 0; i < Sh::TS; ++i) bad |= !(fabs(st.s[i]) <= max_finite<T>());
+                if (bad) *nonfinite = 1;
+            }
         } else {
             const uint32_t slen = stride - (scalar ? 1 : 0);
             T* S = seg_out + vp * slen - 1;
@@ -248,42 +264,6 @@ struct BackwardSegments {
 
 constexpr int next_pow2(int v) { return v <= 1 ? 1 : 2 * next_pow2((v + 1) / 2); }
 constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v / 2); }
-
-// Sum v[0..DP2) over the 32 lanes of a warp.  After the call, lane l holds in
-// v[0..max(1, DP2/32)) the totals of letters first_letter(l) .. ; every letter's total is
-// replicated over 32 / min(DP2, 32) lanes.  Each stage halves the number of values a lane
-// carries (the lane keeps one half and trades the other), so the whole reduction costs
-// about DP2 shuffles instead of 5 * DP2.
-template <typename T, int DP2, int NCUR, int MASK>
-__device__ __forceinline__ void warp_halving_stage(T (&v)[DP2], int lane) {
-    if constexpr (MASK >= 1) {
-        if constexpr (NCUR > 1) {
-            constexpr int HALF = NCUR / 2;
-            const bool upper = (lane & MASK) != 0;
-#pragma unroll
-            for (int i = 0; i < HALF; ++i) {
-                const T send = upper ? v[i] : v[i + HALF];
-                const T keep = upper ? v[i + HALF] : v[i];
-                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, MASK);
-            }
-            warp_halving_stage<T, DP2, HALF, MASK / 2>(v, lane);
-        } else {
-            v[0] += __shfl_xor_sync(0xffffffffu, v[0], MASK);
-            warp_halving_stage<T, DP2, 1, MASK / 2>(v, lane);
-        }
-    }
-}
-
-template <typename T, int DP2>
-__device__ __forceinline__ void warp_halving_reduce(T (&v)[DP2], int lane) {
-    warp_halving_stage<T, DP2, DP2, 16>(v, lane);
-}
-
-template <int DP2>
-__device__ __forceinline__ int reduced_first_letter(int lane) {
-    if constexpr (DP2 >= 32) return lane * (DP2 / 32);
-    else return lane >> (5 - ilog2(DP2));
-}
 
 // Shared-memory layout of one warp of the backward kernel (elements of T):
 //   zs   [kTileChunk][DP]   increments of the chunk

@@ -18,9 +18,8 @@
 namespace sigb200 {
 
 #define SIG_DECLARE_PART(k) void register_tile_part_##k(std::vector<TileEntry>& table);
-SIG_DECLARE_PART(0) SIG_DECLARE_PART(1) SIG_DECLARE_PART(2) SIG_DECLARE_PART(3)
-SIG_DECLARE_PART(4) SIG_DECLARE_PART(5) SIG_DECLARE_PART(6) SIG_DECLARE_PART(7)
-static_assert(SIG_TILE_PARTS == 8, "update the part list in sig_tile_dispatch.cu");
+SIG_TILE_PART_LIST(SIG_DECLARE_PART)
+#undef SIG_DECLARE_PART
 
 namespace {
 
@@ -28,9 +27,9 @@ const std::vector<TileEntry>& tile_table() {
     static std::vector<TileEntry> table;
     static std::once_flag once;
     std::call_once(once, [] {
-        register_tile_part_0(table); register_tile_part_1(table); register_tile_part_2(table);
-        register_tile_part_3(table); register_tile_part_4(table); register_tile_part_5(table);
-        register_tile_part_6(table); register_tile_part_7(table);
+#define SIG_REGISTER_PART(k) register_tile_part_##k(table);
+        SIG_TILE_PART_LIST(SIG_REGISTER_PART)
+#undef SIG_REGISTER_PART
         // big tiles first, so the first entry that yields enough warps is the most efficient one
         std::stable_sort(table.begin(), table.end(),
                          [](const TileEntry& a, const TileEntry& b) { return a.tile_values > b.tile_values; });
@@ -133,20 +132,18 @@ Plan choose(bool is_double, bool backward, const SigShape& s, int sm_count, bool
         }
     }
     plan.forward_for_segments = fwd_big;
-    // Tuning aid: SIGB200_FORCE_PLAN="P,G,segments" (forward) / SIGB200_FORCE_PLAN_BWD pins the
-    // variant and segment count when such a variant is compiled for the shape.
-    if (const char* forced = std::getenv(backward ? "SIGB200_FORCE_PLAN_BWD" : "SIGB200_FORCE_PLAN")) {
-        int fp = -1, fg = -1, fs = 1;
-        if (std::sscanf(forced, "%d,%d,%d", &fp, &fg, &fs) >= 2) {
-            for (const TileEntry& e : tile_table())
-                if (e.is_double == is_double && e.backward == backward && e.D == int(s.dim) && e.N == int(s.degree) &&
-                    e.P == fp && e.G == fg) {
-                    plan.entry = &e;
-                    plan.nseg = int(std::max<uint64_t>(1, std::min<uint64_t>(uint64_t(fs), steps)));
-                    if (backward && !fwd_big) plan.nseg = 1;
-                    return plan;
-                }
-        }
+    // Test hook (set_forced_plan): pins the variant and segment count when such a variant is
+    // compiled for the shape.
+    const ForcedPlan forced = forced_plan(backward);
+    if (forced.P >= 0) {
+        for (const TileEntry& e : tile_table())
+            if (e.is_double == is_double && e.backward == backward && e.D == int(s.dim) && e.N == int(s.degree) &&
+                e.P == forced.P && e.G == forced.G) {
+                plan.entry = &e;
+                plan.nseg = int(std::max<uint64_t>(1, std::min<uint64_t>(uint64_t(forced.segments), steps)));
+                if (backward && !fwd_big) plan.nseg = 1;
+                return plan;
+            }
     }
     if (pref == 1 || pref == 4 || (device < 0 && first)) plan.entry = first, plan.nseg = 1;
     if (pref == 2) plan.entry = last, plan.nseg = 1;
@@ -166,8 +163,28 @@ bool tile_backward_available(const SigShape& s) {
     return choose(sizeof(T) == 8, true, s, 0, false, -1).entry != nullptr;
 }
 
+// Paths that fill the GPU exactly once with the variant an unsegmented sweep of this shape
+// would run (0 when the shape is outside the table or one path already overfills a wave).
 template <typename T>
-bool launch_tile_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream) {
+uint64_t tile_wave_paths(const SigShape& s, bool backward) {
+    const int device = current_device();
+    const bool flags = s.time_aug || s.lead_lag;
+    SigShape big = s;
+    big.batch = uint64_t(1) << 20;  // the variant a full GPU gets
+    const DeviceContext& ctx = device_context(device);
+    const Plan plan = choose(sizeof(T) == 8, backward, big, ctx.sm_count, flags, device);
+    if (!plan.entry) return 0;
+    const uint64_t wpp = uint64_t((plan.entry->units + 31) / 32);
+    const uint64_t warps = uint64_t(occupancy_of(*plan.entry, flags, device)) * ctx.sm_count * kTileWarpsPerBlock;
+    return warps / wpp;
+}
+template uint64_t tile_wave_paths<float>(const SigShape&, bool);
+template uint64_t tile_wave_paths<double>(const SigShape&, bool);
+
+template <typename T>
+bool launch_tile_forward(const T* path, T* out, const SigShape& s, T end_time, cudaStream_t stream, int* nonfinite,
+                         bool* nonfinite_checked) {
+    if (nonfinite_checked) *nonfinite_checked = false;
     const int device = current_device();
     const bool flags = s.time_aug || s.lead_lag;
     const Plan plan = choose(sizeof(T) == 8, false, s, device_context(device).sm_count, flags, device);
@@ -179,12 +196,13 @@ bool launch_tile_forward(const T* path, T* out, const SigShape& s, T end_time, c
         const uint64_t per_buffer = s.batch * (s.full_len - 1);
         Scratch seg((per_buffer * uint64_t(plan.nseg) + chen_combine_tmp_elems(s, plan.nseg)) * sizeof(T), stream);
         plan.entry->launch(&pv, out, nullptr, nullptr, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term, flags,
-                           plan.nseg, seg.get(), stream);
+                           plan.nseg, seg.get(), nullptr, stream);
         launch_chen_combine<T>(out, seg.as<T>(), seg.as<T>() + per_buffer * uint64_t(plan.nseg), s, plan.nseg, stream);
         return true;
     }
     plan.entry->launch(&pv, out, nullptr, nullptr, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term, flags, 1,
-                       nullptr, stream);
+                       nullptr, nonfinite, stream);
+    if (nonfinite_checked) *nonfinite_checked = true;
     return true;
 }
 
@@ -213,7 +231,7 @@ bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* s
         T* E = segA + per;
         T* dE = E + per;
         plan.forward_for_segments->launch(&pv, nullptr, nullptr, nullptr, s.batch, stride, s.scalar_term, flags, K,
-                                          segA, stream);
+                                          segA, nullptr, stream);
         for (int k = 1; k <= K - 2; ++k)
             launch_chen_product<T>(k == 1 ? segA : E + uint64_t(k - 1) * slen, row, segA + uint64_t(k) * slen, row,
                                    E + uint64_t(k) * slen, row, s, stream);
@@ -228,9 +246,9 @@ bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* s
         segs.seg_sig = segA;
         segs.state = E;
         segs.adjoint = dE;
-        e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, stride, s.scalar_term, flags, K, &segs, stream);
+        e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, stride, s.scalar_term, flags, K, &segs, nullptr, stream);
     } else {
-        e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, stride, s.scalar_term, flags, 1, nullptr, stream);
+        e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, stride, s.scalar_term, flags, 1, nullptr, nullptr, stream);
     }
     launch_increment_to_point_grad<T>(incr_grad, out, s.batch, s.data_len, s.data_dim, stream);
     return true;
@@ -252,7 +270,7 @@ bool launch_tile_backward_prealloc(const T* path, T* out, const T* sig_derivs, c
     const uint64_t g_elems = s.batch * (s.data_len - 1) * s.data_dim;
     SIG_CUDA_CHECK(cudaMemsetAsync(incr_grad, 0, g_elems * sizeof(T), stream));
     e->launch(&pv, incr_grad, sig, sig_derivs, s.batch, static_cast<uint32_t>(s.stride), s.scalar_term,
-              s.time_aug || s.lead_lag, 1, nullptr, stream);
+              s.time_aug || s.lead_lag, 1, nullptr, nullptr, stream);
     launch_increment_to_point_grad<T>(incr_grad, out, s.batch, s.data_len, s.data_dim, stream);
     return true;
 }
@@ -278,7 +296,7 @@ std::string describe_tile_plan(bool is_double, bool backward, const SigShape& s)
 #define INSTANTIATE(T)                                                                              \
     template bool tile_forward_available<T>(const SigShape&);                                       \
     template bool tile_backward_available<T>(const SigShape&);                                      \
-    template bool launch_tile_forward<T>(const T*, T*, const SigShape&, T, cudaStream_t);           \
+    template bool launch_tile_forward<T>(const T*, T*, const SigShape&, T, cudaStream_t, int*, bool*); \
     template bool launch_tile_backward<T>(const T*, T*, const T*, const T*, const SigShape&, T, T*, cudaStream_t);
 INSTANTIATE(float)
 INSTANTIATE(double)

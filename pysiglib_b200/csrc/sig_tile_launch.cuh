@@ -21,8 +21,10 @@ struct TileEntry {
     int (*occupancy)(bool flags);  // resident CTAs per SM of the kernel on the current device
     // forward:  fn(pv, out, nullptr, nullptr, ...);  backward: fn(pv, incr_grad, sig, derivs, ...)
     // nseg / seg_out: time segmentation of the forward sweep (1 / nullptr = off; ignored backward)
+    // nonfinite: device int set to 1 by an unsegmented forward sweep that stores NaN / Inf (nullptr = no check)
     void (*launch)(const void* pv, void* out, const void* sig, const void* derivs, uint64_t batch,
-                   uint32_t stride, bool scalar, bool flags, int nseg, void* seg_out, cudaStream_t stream);
+                   uint32_t stride, bool scalar, bool flags, int nseg, void* seg_out, int* nonfinite,
+                   cudaStream_t stream);
 };
 
 inline unsigned tile_grid(uint64_t batch, int units) {
@@ -40,7 +42,7 @@ inline void tile_set_smem(Kernel kernel, size_t smem) {
 
 template <typename T, int D, int N, int P, int G>
 void tile_forward_launch(const void* pv_, void* out, const void*, const void*, uint64_t batch, uint32_t stride,
-                         bool scalar, bool flags, int nseg, void* seg_out, cudaStream_t stream) {
+                         bool scalar, bool flags, int nseg, void* seg_out, int* nonfinite, cudaStream_t stream) {
     using Sh = TileShape<D, N, P, G>;
     constexpr int W = kTileWarpsPerBlock;
     const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
@@ -48,10 +50,10 @@ void tile_forward_launch(const void* pv_, void* out, const void*, const void*, u
     const unsigned grid = tile_grid(batch * uint64_t(nseg), Sh::UNITS);
     if (flags) {
         tile_set_smem(tile_forward_kernel<T, Sh, true, W>, smem);
-        tile_forward_kernel<T, Sh, true, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), static_cast<T*>(seg_out), batch, stride, scalar, nseg);
+        tile_forward_kernel<T, Sh, true, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), static_cast<T*>(seg_out), batch, stride, scalar, nseg, nonfinite);
     } else {
         tile_set_smem(tile_forward_kernel<T, Sh, false, W>, smem);
-        tile_forward_kernel<T, Sh, false, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), static_cast<T*>(seg_out), batch, stride, scalar, nseg);
+        tile_forward_kernel<T, Sh, false, W><<<grid, W * 32, smem, stream>>>(pv, static_cast<T*>(out), static_cast<T*>(seg_out), batch, stride, scalar, nseg, nonfinite);
     }
     SIG_CUDA_CHECK(cudaGetLastError());
     count_launch();
@@ -59,7 +61,8 @@ void tile_forward_launch(const void* pv_, void* out, const void*, const void*, u
 
 template <typename T, int D, int N, int P, int G>
 void tile_backward_launch(const void* pv_, void* incr_grad, const void* sig, const void* derivs, uint64_t batch,
-                          uint32_t stride, bool scalar, bool flags, int nseg, void* segments, cudaStream_t stream) {
+                          uint32_t stride, bool scalar, bool flags, int nseg, void* segments, int* /*nonfinite*/,
+                          cudaStream_t stream) {
     using Sh = TileShape<D, N, P, G>;
     constexpr int W = kTileWarpsPerBlock;
     const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);

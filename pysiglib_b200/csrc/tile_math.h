@@ -227,13 +227,16 @@ SIG_HD T tile_chain(const T* ch, const T* zc, int target, T* hist) {
     return h;
 }
 
-// One Horner step with increment z (zg = z at the unit's children, zc = z at its chain letters).
-template <typename T, typename Sh, bool TOP = true>
-SIG_HD void tile_update(TileState<T, Sh, TOP>& st, const T (&z)[Sh::D], const T (&zg)[Sh::G], const T* zc) {
+// Levels of one Horner step with increment z (zg = z at the unit's children, zc = z at its chain
+// letters): tile depths FIRST_T .. 1 in descending order, then the chain.  FIRST_T = Q is the whole
+// step; FIRST_T = Q - 1 leaves the deepest tile level (the level-N coefficients) alone.
+template <typename T, typename Sh, bool TOP, int FIRST_T>
+SIG_HD void tile_update_levels(TileState<T, Sh, TOP>& st, const T (&z)[Sh::D], const T (&zg)[Sh::G], const T* zc) {
     constexpr int P = Sh::P, Q = Sh::Q, D = Sh::D, G = Sh::G;
+    static_assert(FIRST_T <= (TOP ? Q : Q - 1), "the state does not hold that depth");
     T w[Sh::WS];
 #pragma unroll
-    for (int t = (TOP ? Q : Q - 1); t >= 1; --t) {
+    for (int t = FIRST_T; t >= 1; --t) {
         const int target = P + t;
         const T base = tile_chain<T, Sh, P>(st.ch, zc, target, nullptr) + st.ch[P];
         if (t == 1) {
@@ -273,6 +276,12 @@ SIG_HD void tile_update(TileState<T, Sh, TOP>& st, const T (&z)[Sh::D], const T 
             if (k < target - 1) h = zc[k] * ((h + st.ch[k]) * rcp_of<T>(target - k));
         st.ch[target] = sig_fma(zc[target - 1], h + st.ch[target - 1], st.ch[target]);
     }
+}
+
+// One whole Horner step.
+template <typename T, typename Sh, bool TOP = true>
+SIG_HD void tile_update(TileState<T, Sh, TOP>& st, const T (&z)[Sh::D], const T (&zg)[Sh::G], const T* zc) {
+    tile_update_levels<T, Sh, TOP, (TOP ? Sh::Q : Sh::Q - 1)>(st, z, zg, zc);
 }
 
 // Which words a unit owns.  Units of a path are numbered u = pw * NG + grp with pw the

@@ -55,10 +55,14 @@ def _bind(lib):
     lib.sigb200_describe_plan.argtypes = (ctypes.c_char_p, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_bool,
                                           c_bool, c_int, c_int)
     lib.sigb200_describe_plan.restype = c_int
-    lib.sigb200_fma_peak.argtypes = (c_int, c_void_p, c_int, c_int, c_void_p)
-    lib.sigb200_fma_peak.restype = c_int
     lib.sigb200_noalloc_scratch_bytes.argtypes = ()
     lib.sigb200_noalloc_scratch_bytes.restype = c_uint64
+    lib.sigb200_set_forced_plan.argtypes = (c_int, c_int, c_int, c_int)
+    lib.sigb200_set_forced_plan.restype = None
+    lib.sigb200_inject_alloc_failures.argtypes = (c_int,)
+    lib.sigb200_inject_alloc_failures.restype = None
+    lib.sigb200_pool_reserved_bytes.argtypes = (c_int,)
+    lib.sigb200_pool_reserved_bytes.restype = c_uint64
     lib.sigb200_launch_count.argtypes = ()
     lib.sigb200_launch_count.restype = c_uint64
     for suffix, real in (("f", c_float), ("d", c_double)):
@@ -159,6 +163,21 @@ def set_tile_preference(preference):
     """0 automatic, 1 biggest register tile, 2 smallest, 3 automatic without time segmentation,
     4 biggest tile with forced time segmentation of the forward sweep."""
     library().sigb200_set_tile_preference(int(preference))
+
+
+def set_forced_plan(backward, chain_length, group, segments=1):
+    """Test hook: pin the register-tile variant (chain length, group) and time-segment count of the
+    forward / backward sweep; ``chain_length < 0`` clears it."""
+    library().sigb200_set_forced_plan(1 if backward else 0, int(chain_length), int(group), int(segments))
+
+
+def inject_alloc_failures(count):
+    """Test hook: the next ``count`` scratch / staging requests fail as if the GPU were out of memory."""
+    library().sigb200_inject_alloc_failures(int(count))
+
+
+def pool_reserved_bytes(device=0):
+    return int(library().sigb200_pool_reserved_bytes(int(device)))
 
 
 def kernel_family(dimension, degree, *, time_aug=False, lead_lag=False, dtype="float32", backward=False):

@@ -101,3 +101,7 @@ HARNESS(4, 4, 2, 4)
 HARNESS(5, 3, 1, 5)
 HARNESS(6, 3, 1, 3)
 HARNESS(8, 3, 1, 4)
+// long chains over few tile values: the deep-degree variants of the table
+HARNESS(3, 7, 5, 3)
+HARNESS(4, 6, 4, 2)
+HARNESS(2, 8, 6, 1)

@@ -1,7 +1,7 @@
 """The five BASELINE.json configurations at FULL size on the GPU.
 
 At these sizes the CPU oracle is too slow for the whole batch, so each case checks
-  * a seeded subset of paths against the oracle (per-coefficient tolerance as elsewhere), and
+  * 64 paths spread over the batch against the oracle (per-coefficient tolerance as elsewhere), and
   * size-independent properties on the whole batch:
       - Chen's identity: sig(path) = sig(first part) (x) sig(second part), evaluated for the
         first two levels of every path (cheap closed forms of the tensor product);
@@ -9,6 +9,8 @@ At these sizes the CPU oracle is too slow for the whole batch, so each case chec
       - backward: linearity in the seeds, zero column sums (translation invariance of the
         signature), and agreement with the oracle on the subset.
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -48,9 +50,10 @@ def test_full_size_config(name):
     s = psl.sig(x, N)
     assert s.shape == (B, sum(d ** k for k in range(1, N + 1)))
 
-    # subset against the oracle
-    pick = [0, B // 3, B - 1]
-    expect = oracle.sig(host[pick].numpy(), N, n_threads=3)
+    # subset against the oracle: 64 paths spread over the batch (all of them when the batch is smaller)
+    pick = sorted(set(np.linspace(0, B - 1, min(B, 64)).astype(int).tolist()))
+    threads = os.cpu_count() or 4
+    expect = oracle.sig(host[pick].numpy(), N, n_threads=threads)
     assert_sig_close(s[pick].cpu().numpy(), expect, d, N, rtol)
 
     # whole batch: level 1 = total increment; sym(level 2) = level1 (x) level1 / 2
@@ -85,9 +88,10 @@ def test_full_size_config(name):
     assert (g1.sum(dim=1).abs() / g1.abs().amax(dim=(1, 2))[:, None]).max().item() <= 2e-3  # translation invariance
     p_np = host[pick].numpy()
     seeds_np = s1[pick].cpu().numpy()
-    want = oracle.sig_backprop(p_np, expect, seeds_np, N, n_threads=3)
+    want = oracle.sig_backprop(p_np, expect, seeds_np, N, n_threads=threads)
     p64 = p_np.astype(np.float64)
-    truth = oracle.sig_backprop(p64, oracle.sig(p64, N, n_threads=3), seeds_np.astype(np.float64), N, n_threads=3)
+    truth = oracle.sig_backprop(p64, oracle.sig(p64, N, n_threads=threads), seeds_np.astype(np.float64), N,
+                                n_threads=threads)
     assert_grad_parity(g1[pick].cpu().numpy(), want, truth, rtol)
 
 

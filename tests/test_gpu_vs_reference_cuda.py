@@ -42,3 +42,25 @@ def test_forward_and_backward_match_reference_cuda(case):
     p64 = path_np.astype(np.float64)
     truth = oracle.sig_backprop(p64, oracle.sig(p64, N, **kw), seeds.cpu().numpy().astype(np.float64), N, **kw)
     assert_grad_parity(our_g.cpu().numpy(), ref_g.cpu().numpy(), truth, rtol)
+
+
+@pytest.mark.parametrize("time_aug,lead_lag", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_transform_path_matches_reference_cuda(time_aug, lead_lag, dtype):
+    """The standalone path transform and its backward against the reference's own kernels
+    (siglib/cusig/cu_path_transforms.cu:100-205): pure data movement, so bit-identical."""
+    import pysiglib_b200
+    B, L, d = 5, 23, 3
+    path = torch.tensor(brownian_paths(4, B, L, d, dtype), device="cuda")
+    kw = dict(time_aug=time_aug, lead_lag=lead_lag, end_time=0.7)
+    ref = refcuda.transform_path(path, **kw)
+    ours = pysiglib_b200.transform_path(path, **kw)
+    assert ours.shape == ref.shape
+    tol = 0 if not time_aug else (1e-15 if dtype == np.float64 else 1e-6)  # the time channel is k * dt either way
+    assert float((ours - ref).abs().max()) <= tol
+    derivs = torch.randn(ref.shape, dtype=ref.dtype, device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+    ref_g = refcuda.transform_path_backprop(derivs, L, d, **kw)
+    our_g = pysiglib_b200.transform_path_backprop(derivs, **kw)
+    assert our_g.shape == ref_g.shape == path.shape
+    scale = float(ref_g.abs().max())
+    assert float((our_g - ref_g).abs().max()) <= (1e-14 if dtype == np.float64 else 1e-6) * scale

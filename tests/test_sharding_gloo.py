@@ -12,7 +12,7 @@ import torch.multiprocessing as mp
 
 from conftest import brownian_paths
 from oracle import oracle
-from pysiglib_b200.sharded import shard_bounds
+from pysiglib_b200.sharded import all_gather_signatures, shard_bounds
 
 
 def _worker(rank, world, port, batch, tmpdir):
@@ -32,6 +32,8 @@ def _worker(rank, world, port, batch, tmpdir):
         pieces = [torch.zeros_like(padded) for _ in range(world)]
         dist.all_gather(pieces, padded)
         full = torch.cat([p[: e - b] for p, (b, e) in zip(pieces, shard_bounds(batch, world))])
+        # the library's own gather (one all_gather_into_tensor, ragged shards padded and trimmed)
+        assert torch.equal(all_gather_signatures(local, batch), full)
         # timing reduction used by bench.py: the slowest rank defines the step time
         t = torch.tensor([1.0 + rank], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

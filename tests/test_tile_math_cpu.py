@@ -19,7 +19,8 @@ HDR = os.path.join(HERE, "..", "pysiglib_b200", "csrc", "tile_math.h")
 LIB = os.path.join(HERE, "cpu_harness", "_build", "tile_harness.so")
 
 SHAPES = [(2, 2, 1, 2), (2, 2, 0, 2), (2, 5, 2, 2), (2, 5, 3, 1), (2, 6, 1, 1), (3, 3, 0, 3), (3, 3, 2, 1),
-          (3, 4, 1, 3), (3, 4, 2, 3), (4, 3, 1, 2), (4, 4, 2, 4), (5, 3, 1, 5), (6, 3, 1, 3), (8, 3, 1, 4)]
+          (3, 4, 1, 3), (3, 4, 2, 3), (4, 3, 1, 2), (4, 4, 2, 4), (5, 3, 1, 5), (6, 3, 1, 3), (8, 3, 1, 4),
+          (3, 7, 5, 3), (4, 6, 4, 2), (2, 8, 6, 1)]
 
 
 @pytest.fixture(scope="module")
