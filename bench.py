@@ -243,6 +243,35 @@ def workload_config(args, cfg, world):
                   else "L2 flushed (256 MB written) before every timed call"}
 
 
+def run_fma_patterns(args):
+    """--op fma_patterns: SM cycles per 128 lane-FMAs of one warp instruction stream, per operand
+    pattern of the packed / scalar FP32 FMA (pysiglib_b200/csrc/bench/fma_patterns.cu), with one and
+    with two warps per SM scheduler.  128 cycles is the nominal pipe rate."""
+    import torch
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    lib = ctypes.CDLL(os.path.join(ROOT, "pysiglib_b200", "lib", "libsigb200_bench.so"))
+    lib.sigb200_bench_fma_pattern.argtypes = (ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                              ctypes.c_void_p)
+    lib.sigb200_bench_fma_pattern.restype = ctypes.c_int
+    dev = torch.device("cuda", 0)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    sink = torch.zeros(2, dtype=torch.float32, device=dev)
+    names = ["packed, one fresh operand", "packed, row by row (the kernels' pattern)", "packed, column by column",
+             "packed, no operand reuse", "scalar, row by row"]
+    iters, out = 20000, {}
+    for mode, name in enumerate(names):
+        for warps in (1, 2):
+            cycles = torch.zeros(sms * warps, dtype=torch.int64, device=dev)
+            for it in (200, iters):   # a short warm-up launch, then the measured one
+                rc = lib.sigb200_bench_fma_pattern(mode, ctypes.c_void_p(sink.data_ptr()), sms * warps, it,
+                                                   ctypes.c_void_p(cycles.data_ptr()), None)
+                assert rc == 0, rc
+                torch.cuda.synchronize()
+            out["%s, %d warp%s per scheduler" % (name, warps, "s" if warps > 1 else "")] = float(cycles.max()) / (iters * warps)
+    print(json.dumps({"op": "fma_patterns", "unit": "SM cycles per 128 lane-FMAs per scheduler (nominal 128)", "n_gpus": 1,
+                      "cycles": out}))
+
+
 def run_neighbour_op(args):
     """--op: times one of the operators either side of the signature (not the headline metric).
     One GPU, device-resident inputs larger than L2, CUDA events around the public Python call;
@@ -255,6 +284,27 @@ def run_neighbour_op(args):
     gen = torch.Generator(device=dev).manual_seed(11)
     rnd = lambda *shape: torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)
     extra = {}
+    if args.op == "log_sig":
+        # log_sig from the path (one native call) beside sig alone and beside the two public calls the
+        # reference composes (sig, then sig_to_log_sig); FMA-bound like sig, so no HBM roofline here
+        B, L, d, N = args.batch or 4096, args.length or 4096, 16, 4
+        x = torch.cumsum(rnd(B, L, d) * (1.0 / L) ** 0.5, dim=1).contiguous()
+        psl.prepare_log_sig(d, N, 1)
+        warm, steps = max(args.warmup, 3), args.steps
+        with ClockSampler(0) as clocks:
+            sig_ms = _time_ms(torch, lambda: psl.sig(x, N), warm, steps)
+            one_ms = _time_ms(torch, lambda: psl.log_sig(x, N, method=1), warm, steps)
+            two_ms = _time_ms(torch, lambda: psl.sig_to_log_sig(psl.sig(x, N), d, N, method=1), warm, steps)
+            load_cusig.set_tile_preference(1)
+            try:
+                fused_ms = _time_ms(torch, lambda: psl.log_sig(x, N, method=1), warm, steps)
+            finally:
+                load_cusig.set_tile_preference(0)
+        print(json.dumps({"op": "log_sig", "config": {"workload": "log_sig method 1 from the path: float32, B=%d, L=%d, d=%d, degree %d" % (B, L, d, N)},
+                          "n_gpus": 1, "steps": steps, "warmup": warm, "dtype": "f32", "data": "synthetic",
+                          "sig_ms": sig_ms, "log_sig_ms": one_ms, "log_sig_over_sig": one_ms / sig_ms,
+                          "two_public_calls_ms": two_ms, "fused_sweep_forced_ms": fused_ms, "clocks": clocks.summary()}))
+        return
     if args.op in ("sig_combine", "sig_join"):
         B, d, N = args.batch or 4096, 16, 4
         S = sum(d ** k for k in range(1, N + 1))
@@ -575,7 +625,7 @@ def run_inproc_partitioner(args, cfg, torch):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="sig", choices=["sig", "sig_combine", "sig_join", "sig_to_log_sig", "transform_path", "correction"],
+    ap.add_argument("--op", default="sig", choices=["sig", "sig_combine", "sig_join", "sig_to_log_sig", "log_sig", "transform_path", "correction", "fma_patterns"],
                     help="sig (default) is the headline path; the others time one neighbouring operator on one GPU")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -606,6 +656,10 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, cfg, rank)
+        return
+    if args.op == "fma_patterns":
+        if rank == 0:
+            run_fma_patterns(args)
         return
     if args.op != "sig":
         if rank == 0:

@@ -215,6 +215,21 @@ int sigb200_sig_backprop_sharded_d(const double* path, double* out, const double
                                    bool time_aug, bool lead_lag, double end_time, bool scalar_term,
                                    const int* devices, int n_devices);
 
+/* Log signature straight from the path, methods 0 (expanded, layout of the signature; scalar_term
+ * adds the leading slot, which is 0), 1 (Lyndon-word coordinates) and 2 (Lyndon-basis coordinates).
+ * Replaces the two calls the reference's Python makes (pysiglib/log_sig.py:457: signature_cuda_* then
+ * sig_to_log_sig_cuda_*) by one in which the signature is never written to a caller-visible array;
+ * for shapes with a fused kernel it never reaches global memory at all.  `out` holds
+ * batch * (method 0: signature length, else log-signature length) values.  Device or host pointers;
+ * `nonfinite` (may be NULL) receives 1 when the signature holds NaN / Inf (then the call also waits
+ * for completion).  No counterpart among the reference's C symbols. */
+int sigb200_log_sig_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension, uint64_t length,
+                      uint64_t degree, bool time_aug, bool lead_lag, float end_time, int method, bool scalar_term,
+                      void* stream, int synchronize, int* nonfinite);
+int sigb200_log_sig_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension, uint64_t length,
+                      uint64_t degree, bool time_aug, bool lead_lag, double end_time, int method, bool scalar_term,
+                      void* stream, int synchronize, int* nonfinite);
+
 /* sig_backprop without any device-memory allocation, for hosts that cannot allocate when they
  * need the gradient: processes whose own allocator already owns the GPU's memory (a late
  * cudaMalloc can fail there), and latency-critical loops (cudaMalloc / cudaFree synchronise the

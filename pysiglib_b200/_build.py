@@ -23,7 +23,8 @@ LIB = os.path.join(LIB_DIR, "libcusig.so")
 BENCH_LIB = os.path.join(LIB_DIR, "libsigb200_bench.so")  # FMA-peak probe; loaded by bench.py only
 
 NVCC_FLAGS = ["-std=c++17", "--expt-relaxed-constexpr", "-gencode", "arch=compute_100a,code=sm_100a",
-              "-lineinfo", "-O3", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-DNDEBUG"]
+              "-lineinfo", "-O3", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-DNDEBUG",
+              "-Xfatbin=-compress-all"]  # the several hundred tile variants compress about threefold
 
 
 def _nvcc():
@@ -131,7 +132,8 @@ def build(force=False, jobs=None, verbose=False, dev=None):
     proc = subprocess.run(link, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (proc.stdout, proc.stderr))
-    bench = [_nvcc(), "-shared", "-o", BENCH_LIB, os.path.join(CSRC, "bench", "fma_peak.cu"), "-O3", "-lineinfo",
+    bench = [_nvcc(), "-shared", "-o", BENCH_LIB, os.path.join(CSRC, "bench", "fma_peak.cu"),
+             os.path.join(CSRC, "bench", "fma_patterns.cu"), "-O3", "-lineinfo",
              "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
     proc = subprocess.run(bench, capture_output=True, text=True)
     if proc.returncode != 0:

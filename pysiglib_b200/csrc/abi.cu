@@ -279,6 +279,20 @@ SIG_API int sigb200_sig_backprop_d(const double* path, double* out, const double
                                              stream_options(stream, synchronize, nullptr)));
 }
 
+SIG_API int sigb200_log_sig_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension, uint64_t length,
+                              uint64_t degree, bool time_aug, bool lead_lag, float end_time, int method,
+                              bool scalar_term, void* stream, int synchronize, int* nonfinite) {
+    SIG_SAFE_CALL(log_sig_entry<float>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag, end_time,
+                                       method, scalar_term, stream_options(stream, synchronize, nonfinite)));
+}
+
+SIG_API int sigb200_log_sig_d(const double* path, double* out, uint64_t batch_size, uint64_t dimension, uint64_t length,
+                              uint64_t degree, bool time_aug, bool lead_lag, double end_time, int method,
+                              bool scalar_term, void* stream, int synchronize, int* nonfinite) {
+    SIG_SAFE_CALL(log_sig_entry<double>(path, out, batch_size, dimension, length, degree, time_aug, lead_lag, end_time,
+                                        method, scalar_term, stream_options(stream, synchronize, nonfinite)));
+}
+
 SIG_API int sigb200_signature_sharded_f(const float* path, float* out, uint64_t batch_size, uint64_t dimension,
                                         uint64_t length, uint64_t degree, bool time_aug, bool lead_lag,
                                         float end_time, bool scalar_term, const int* devices, int n_devices) {

@@ -69,6 +69,12 @@ void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs
                                    uint64_t degree, int method, bool scalar_term, const CallOptions& opt);
 // Builds (and caches per device) the Lyndon-word table of methods 1 and 2 and the inverse
 // projection matrix of method 2; method 3 is not part of this build.
+// Log signature from the path in one call (methods 0, 1, 2); `scalar_term` only matters for method 0,
+// whose result has the layout of the signature.  opt.nonfinite reports NaN / Inf in the signature.
+template <typename T>
+void log_sig_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, uint64_t length, uint64_t degree,
+                   bool time_aug, bool lead_lag, T end_time, int method, bool scalar_term, const CallOptions& opt);
+
 void prepare_log_sig_entry(uint64_t dimension, uint64_t degree, int method);
 uint64_t log_sig_length_host(uint64_t dimension, uint64_t degree);
 void release_log_sig_tables() noexcept;

@@ -98,10 +98,18 @@ def emit(path, dev, parts_n):
                     continue
                 deep = N > COVER.get(D, 0)
                 for backward, budget in ((0, bf), (1, bb)):
-                    for ts, units, P, G in variants(D, N, budget)[:1 if deep else 3]:
-                        cost = ts * (3 if backward else 1)
+                    for rank, (ts, units, P, G) in enumerate(variants(D, N, budget)[:1 if deep else 3]):
+                        # the biggest forward tile of a shape also gets the fused log-signature sweep
+                        # (where a path fits a portable cluster of 8 CTAs of 4 warps and the shared copy of
+                        # the levels below N stays under 96 KB)
+                        # and the tile is shallow: at most 16 rows of level-N coefficients per unit)
+                        rows = 1 if N - P < 2 else G * D ** (N - P - 2)
+                        fits = (units <= 1024 and geom(D, N) * (8 if tname == "double" else 4) <= 96 * 1024
+                                and N - P <= 3 and rows <= 16)
+                        log = 1 if (not backward and rank == 0 and fits) else 0
+                        cost = ts * (3 if backward else (2 if log else 1))
                         est = bwd_instr(D, N, P, G) if backward else fwd_instr(D, N, P, G)
-                        entries.append((cost, "X(%s, %d, %d, %d, %d, %d, %d)" % (tname, backward, D, N, P, G, est)))
+                        entries.append((cost, "X(%s, %d, %d, %d, %d, %d, %d, %d)" % (tname, backward, D, N, P, G, est, log)))
     entries.sort(key=lambda e: -e[0])
     parts = [[] for _ in range(parts_n)]
     loads = [0] * parts_n
@@ -111,7 +119,7 @@ def emit(path, dev, parts_n):
         loads[i] += cost
     with open(path, "w") as f:
         f.write("// Generated by gen_tile_table.py; do not edit by hand.\n")
-        f.write("// X(type, backward, D, N, P, G, est): one compiled register-tile kernel variant; est = estimated\n// issue slots per unit and step (cost model of the run-time variant choice).\n")
+        f.write("// X(type, backward, D, N, P, G, est, log): one compiled register-tile kernel variant; est = estimated\n// issue slots per unit and step (cost model of the run-time variant choice); log = 1: the fused\n// log-signature sweep is compiled for it too.\n")
         f.write("#pragma once\n#define SIG_TILE_PARTS %d\n" % parts_n)
         f.write("#define SIG_TILE_PART_LIST(F) " + " ".join("F(%d)" % i for i in range(parts_n)) + "\n")
         for i, part in enumerate(parts):

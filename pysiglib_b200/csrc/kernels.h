@@ -61,6 +61,16 @@ template <typename T>
 bool launch_tile_backward(const T* path, T* out, const T* sig_derivs, const T* sig, const SigShape& s,
                           T end_time, T* incr_grad, cudaStream_t stream);
 
+// log(signature) of every path in one launch, without the signature going to global memory (the
+// fused sweep of sig_tile.cuh).  rank == nullptr: expanded logarithm, `out` laid out like the signature
+// (out_shift = 1 leaves the scalar slot, set to 0); otherwise rank[p] = output index of the word at
+// scalar-free position p, or -1 to drop it.  Returns false when nothing was launched: the shape has
+// no fused kernel, or (unless `force`) the two-step route is the faster one for it.
+template <typename T>
+bool launch_tile_forward_log(const T* path, T* out, const SigShape& s, T end_time, uint32_t out_stride,
+                             uint32_t out_shift, const int32_t* rank, int* nonfinite, cudaStream_t stream,
+                             bool force = false);
+
 // What the tile dispatcher would launch for this shape on the current device ("generic" if none).
 std::string describe_tile_plan(bool is_double, bool backward, const SigShape& s);
 

@@ -19,6 +19,7 @@
 #include "algebra.h"
 #include "algebra_host.h"
 #include "algebra_math.h"
+#include "dispatch.h"
 #include "kernels.h"
 #include "runtime.h"
 
@@ -178,6 +179,30 @@ LyndonTable lyndon_table(uint64_t dim, uint64_t degree) {
     return table;
 }
 
+// Inverse of the Lyndon-position table for the fused sweep: rank[p] = index of the Lyndon word that
+// sits at scalar-free position p, -1 for every other word.
+struct LyndonRank {
+    int32_t* device = nullptr;
+    uint32_t count = 0;
+};
+std::map<std::tuple<int, uint64_t, uint64_t>, LyndonRank> g_ranks;
+
+LyndonRank lyndon_rank_table(uint64_t dim, uint64_t degree) {
+    const int device = current_device();
+    std::lock_guard<std::mutex> lock(g_tables_mu);
+    const auto key = std::make_tuple(device, dim, degree);
+    auto it = g_ranks.find(key);
+    if (it != g_ranks.end()) return it->second;
+    const std::vector<uint32_t> positions = lyndon_positions(dim, degree);
+    std::vector<int32_t> host(sig_length_full(dim, degree) - 1, -1);
+    for (size_t i = 0; i < positions.size(); ++i) host[positions[i]] = static_cast<int32_t>(i);
+    LyndonRank table;
+    table.count = static_cast<uint32_t>(positions.size());
+    SIG_CUDA_CHECK(cudaMalloc(&table.device, std::max<size_t>(host.size(), 1) * sizeof(int32_t)));
+    SIG_CUDA_CHECK(cudaMemcpy(table.device, host.data(), host.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+    g_ranks.emplace(key, table);
+    return table;
+}
 
 // ----- Lyndon basis (method 2) --------------------------------------------------------------------
 //
@@ -369,6 +394,17 @@ uint64_t log_sig_length_host(uint64_t dimension, uint64_t degree) {
 }
 
 void release_log_sig_tables() noexcept {
+    {
+        std::lock_guard<std::mutex> lock(g_tables_mu);
+        for (auto& kv : g_ranks) {
+            int prev = -1;
+            if (cudaGetDevice(&prev) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+            if (cudaSetDevice(std::get<0>(kv.first)) == cudaSuccess && kv.second.device) (void)cudaFree(kv.second.device);
+            (void)cudaSetDevice(prev);
+            (void)cudaGetLastError();
+        }
+        g_ranks.clear();
+    }
     std::lock_guard<std::mutex> lock(g_tables_mu);
     for (auto& kv : g_tables) {
         int prev = -1;
@@ -460,6 +496,92 @@ void sig_to_log_sig_entry(const T* sig, T* out, uint64_t batch, uint64_t dimensi
                });
 }
 
+// Log signature straight from the path (methods 0, 1, 2).  Replaces the reference's Python-level
+// composition sig -> sig_to_log_sig (pysiglib/log_sig.py:457) by one native call in which the
+// signature never becomes a caller-visible array: when the shape has a fused sweep
+// (launch_tile_forward_log) it never leaves the SMs at all; otherwise it is computed into pooled
+// scratch, one batch chunk at a time, and fed to the kernels of sig_to_log_sig.
+template <typename T>
+void log_sig_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, uint64_t length, uint64_t degree,
+                   bool time_aug, bool lead_lag, T end_time, int method, bool scalar_term, const CallOptions& opt) {
+    if (dimension == 0) throw std::invalid_argument("log_sig received path of dimension 0");
+    if (degree == 0) throw std::invalid_argument("log signature received degree 0");
+    check_method(method, "log_sig");
+    if (opt.nonfinite) *opt.nonfinite = 0;
+    if (batch == 0) return;
+    if (!path || !out) throw std::invalid_argument("log_sig received a null pointer");
+    const SigShape s = make_shape(batch, dimension, length, degree, time_aug, lead_lag, method == 0 && scalar_term);
+    const Levels lv = checked_levels(s.dim, degree, "log_sig");
+    const uint64_t S = lv.total();
+    const uint64_t out_len = method >= 1 ? log_sig_length_host(s.dim, degree) : s.stride;
+
+    auto run = [&](const T* dpath, T* dout, cudaStream_t st, int* flag) {
+        LyndonRank rank;
+        BasisTable basis;
+        if (method >= 1) rank = lyndon_rank_table(s.dim, degree);
+        if (method == 2) basis = basis_table(s.dim, degree);
+        // method 2: Lyndon-word coordinates into scratch, then the sparse change of basis
+        Scratch words(method == 2 ? batch * out_len * sizeof(T) : 0, st);
+        T* target = method == 2 ? words.as<T>() : dout;
+        const uint32_t shift = method == 0 && scalar_term ? 1 : 0;
+        // tile preference 1 ("always the biggest tile", a test hook) also forces the fused sweep
+        bool fused = kernel_policy() == 0 &&
+                     launch_tile_forward_log<T>(dpath, target, s, end_time, static_cast<uint32_t>(out_len), shift,
+                                                method >= 1 ? rank.device : nullptr, flag, st, tile_preference() == 1);
+        if (!fused) {
+            // signature of a batch chunk into scratch (scalar-free), then the tensor-logarithm kernels
+            SigShape cs = make_shape(batch, dimension, length, degree, time_aug, lead_lag, false);
+            const uint64_t per_path = 3 * S * sizeof(T);
+            const uint64_t chunk = std::max<uint64_t>(1, std::min<uint64_t>(batch, kLogScratchBudget / per_path));
+            Scratch ws(chunk * per_path, st);
+            LyndonTable table;
+            if (method >= 1) table = lyndon_table(s.dim, degree);
+            for (uint64_t b0 = 0; b0 < batch; b0 += chunk) {
+                const uint64_t count = std::min(chunk, batch - b0);
+                cs.batch = count;
+                T* sig = ws.as<T>() + 2 * chunk * S;
+                forward_on_device<T>(dpath + b0 * length * dimension, sig, cs, end_time, st, flag);
+                const T* r2 = degree >= 2 ? run_horner<T>(sig, S, ws.as<T>(), false, lv, count, st) : nullptr;
+                if (method >= 1) {
+                    log_final_kernel<T><<<coeff_grid(table.count, count), kThreads, 0, st>>>(
+                        sig, S, r2, target + b0 * out_len, out_len, lv, count, table.device, table.count, false);
+                } else {
+                    log_final_kernel<T><<<coeff_grid(lv.total(), count), kThreads, 0, st>>>(
+                        sig, S, r2, target + b0 * out_len + shift, out_len, lv, count, nullptr, lv.total(), shift != 0);
+                }
+                check_launch("tensor log kernel");
+            }
+        }
+        if (method == 2) {
+            basis_spmv_kernel<T><<<coeff_grid(basis.rows, batch), kThreads, 0, st>>>(
+                target, out_len, dout, out_len, basis.row_ptr, basis.col, basis.val, basis.rows, batch);
+            check_launch("tensor log kernel");
+        }
+    };
+    auto with_flag = [&](const T* dpath, T* dout, cudaStream_t st, bool synchronize) {
+        if (opt.nonfinite) {
+            Scratch flag(sizeof(int), st);
+            SIG_CUDA_CHECK(cudaMemsetAsync(flag.get(), 0, sizeof(int), st));
+            run(dpath, dout, st, flag.as<int>());
+            SIG_CUDA_CHECK(cudaMemcpyAsync(opt.nonfinite, flag.get(), sizeof(int), cudaMemcpyDeviceToHost, st));
+            SIG_CUDA_CHECK(cudaStreamSynchronize(st));
+        } else {
+            run(dpath, dout, st, nullptr);
+            if (synchronize) SIG_CUDA_CHECK(cudaStreamSynchronize(st));
+        }
+    };
+    int device = -1;
+    if (all_on_device({path, out}, "log_sig", &device)) {
+        DeviceGuard guard(device);
+        with_flag(path, out, opt.stream, opt.synchronize);
+        return;
+    }
+    run_staged({{path, nullptr, batch * length * dimension * sizeof(T)}, {nullptr, out, batch * out_len * sizeof(T)}},
+               opt.device, [&](const std::vector<void*>& d, cudaStream_t st) {
+                   with_flag(static_cast<const T*>(d[0]), static_cast<T*>(d[1]), st, false);
+               });
+}
+
 template <typename T>
 void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs, uint64_t batch, uint64_t dimension,
                                    uint64_t degree, int method, bool scalar_term, const CallOptions& opt) {
@@ -546,6 +668,10 @@ void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs
                                                    const CallOptions&);
 INSTANTIATE(float)
 INSTANTIATE(double)
+template void log_sig_entry<float>(const float*, float*, uint64_t, uint64_t, uint64_t, uint64_t, bool, bool, float, int,
+                                   bool, const CallOptions&);
+template void log_sig_entry<double>(const double*, double*, uint64_t, uint64_t, uint64_t, uint64_t, bool, bool, double,
+                                    int, bool, const CallOptions&);
 #undef INSTANTIATE
 
 }  // namespace sigb200

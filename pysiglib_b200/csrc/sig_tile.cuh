@@ -22,6 +22,7 @@
 // siglib/cusig/cu_signature_horner.cuh:219-249 forward_kernel, :309-363 backward_kernel).
 #pragma once
 
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -161,32 +162,12 @@ __device__ __forceinline__ void commit_increments(T* zs, const ChunkRegs<T, Sh>&
     }
 }
 
-// Forward sweep.  With nseg > 1 every path is cut into nseg time segments that are swept
-// independently (more warps for small batches) and written to `seg_out` ((batch, nseg, S),
-// scalar-free); Chen-product launches then join them into `out`.
-template <typename T, typename Sh, bool FLAGS, int WPB>
-__global__ void __launch_bounds__(WPB * 32)
-tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out, uint64_t batch, uint32_t stride,
-                    bool scalar, int nseg, int* __restrict__ nonfinite) {
+// Forward sweep of one unit over the steps [j_begin, j_end) of the path starting at x; zs is the
+// warp's slice of shared memory.  The state is (re)initialised by the first step.
+template <typename T, typename Sh, bool FLAGS>
+__device__ __forceinline__ void tile_sweep_forward(TileState<T, Sh>& st, const PathView<T>& pv, const T* x, int j_begin,
+                                                   int j_end, T* zs, const UnitIndex<Sh>& ix, int lane) {
     constexpr int DP = RowPad<T, Sh::D>::DP;
-    constexpr int WPP = (Sh::UNITS + 31) / 32;  // warps per (path, segment)
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * DP;
-
-    const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
-    if (gw >= batch * uint64_t(nseg) * WPP) return;
-    const uint64_t vp = gw / WPP;               // virtual path = b * nseg + segment
-    const uint64_t b = vp / uint64_t(nseg);
-    const int seg = int(vp - b * uint64_t(nseg));
-    const int j_begin = int(int64_t(pv.steps) * seg / nseg);
-    const int j_end = int(int64_t(pv.steps) * (seg + 1) / nseg);
-    const int u = int(gw - vp * WPP) * 32 + lane;
-    const bool active = u < Sh::UNITS;
-    const UnitIndex<Sh> ix = decode_unit<Sh>(active ? u : 0);
-    const T* x = pv.base + b * pv.path_stride;
-
-    TileState<T, Sh> st;
     StepOperands<T, Sh> op;
     // Register prefetch of the next chunk: pays in float32 (measured +4..9 % on B200); in
     // float64 the extra registers cost more than the hidden latency gains.
@@ -225,27 +206,170 @@ tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out
             }
         }
     }
+}
+
+// true when any coefficient the unit holds is NaN / Inf.  Every coefficient of the signature is
+// owned by some unit (chain coefficients by all units sharing the prefix, which see the same
+// value), so the union over units covers the whole signature.
+template <typename T, typename Sh>
+__device__ __forceinline__ bool tile_nonfinite(const TileState<T, Sh>& st) {
+    bool bad = false;
+#pragma unroll
+    for (int k = 1; k <= Sh::P; ++k) bad |= !(fabs(st.ch[k]) <= max_finite<T>());
+#pragma unroll
+    for (int i = 0; i < Sh::TS; ++i) bad |= !(fabs(st.s[i]) <= max_finite<T>());
+    return bad;
+}
+
+// Forward sweep.  With nseg > 1 every path is cut into nseg time segments that are swept
+// independently (more warps for small batches) and written to `seg_out` ((batch, nseg, S),
+// scalar-free); Chen-product launches then join them into `out`.
+template <typename T, typename Sh, bool FLAGS, int WPB>
+__global__ void __launch_bounds__(WPB * 32)
+tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out, uint64_t batch, uint32_t stride,
+                    bool scalar, int nseg, int* __restrict__ nonfinite) {
+    constexpr int DP = RowPad<T, Sh::D>::DP;
+    constexpr int WPP = (Sh::UNITS + 31) / 32;  // warps per (path, segment)
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * DP;
+
+    const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
+    if (gw >= batch * uint64_t(nseg) * WPP) return;
+    const uint64_t vp = gw / WPP;               // virtual path = b * nseg + segment
+    const uint64_t b = vp / uint64_t(nseg);
+    const int seg = int(vp - b * uint64_t(nseg));
+    const int j_begin = int(int64_t(pv.steps) * seg / nseg);
+    const int j_end = int(int64_t(pv.steps) * (seg + 1) / nseg);
+    const int u = int(gw - vp * WPP) * 32 + lane;
+    const bool active = u < Sh::UNITS;
+    const UnitIndex<Sh> ix = decode_unit<Sh>(active ? u : 0);
+    const T* x = pv.base + b * pv.path_stride;
+
+    TileState<T, Sh> st;
+    tile_sweep_forward<T, Sh, FLAGS>(st, pv, x, j_begin, j_end, zs, ix, lane);
     if (active) {
         if (nseg == 1) {
             T* S = out + b * stride - (scalar ? 0 : 1);
             tile_store<T, Sh>(st, ix, S);
             if (scalar && u == 0) S[0] = T(1);
-            if (nonfinite != nullptr) {
-                // NaN / Inf check of what was just stored, on the registers: every coefficient of the
-                // signature is owned by exactly one unit (chain coefficients by all units sharing the
-                // prefix, which see the same value), so the union over units covers the whole output.
-                bool bad = false;
-#pragma unroll
-                for (int k = 1; k <= Sh::P; ++k) bad |= !(fabs(st.ch[k]) <= max_finite<T>());
-#pragma unroll
-                for (int i = 0; i < Sh::TS; ++i) bad |= !(fabs(st.s[i]) <= max_finite<T>());
-                if (bad) *nonfinite = 1;
-            }
+            // NaN / Inf check of what was just stored, on the registers (no pass over the output)
+            if (nonfinite != nullptr && tile_nonfinite<T, Sh>(st)) *nonfinite = 1;
         } else {
             const uint32_t slen = stride - (scalar ? 1 : 0);
             T* S = seg_out + vp * slen - 1;
             tile_store<T, Sh>(st, ix, S);
         }
+    }
+}
+
+// Shape of a fused log-signature launch: a path's units either fill CTAS_PER_PATH whole CTAs (a
+// thread-block cluster, so that their shared memories can be written by each other) or several
+// paths share one CTA.
+template <typename Sh, int WPB>
+struct LogSweepShape {
+    static constexpr int WPP = (Sh::UNITS + 31) / 32;
+    static constexpr int CTAS_PER_PATH = WPP >= WPB ? (WPP + WPB - 1) / WPB : 1;
+    static constexpr int PATHS_PER_CTA = WPP >= WPB ? 1 : WPB / WPP;
+    static constexpr int LOW = cgeom(Sh::D, Sh::N);   // coefficients of levels 0 .. N-1
+};
+
+// Forward sweep with the log-signature epilogue: computes log(signature) without the signature
+// ever going to global memory.  The units of a path sweep as in tile_forward_kernel; then every
+// unit publishes its coefficients BELOW level N into a shared-memory copy of those levels (a few
+// KB per path; when the path spans several CTAs these form a cluster and every unit writes into
+// all of their shared memories through distributed shared memory), the cluster synchronises, and
+// every unit turns the level-N coefficients it still holds in registers into their logarithm
+// (tile_log_top) while the threads share out the levels below N (log_low_prefix).
+// `rank` == nullptr: expanded logarithm in the layout of the signature (out_shift = 1 reserves the
+// scalar slot, which is 0).  Otherwise rank[p] is the output index of the word at scalar-free
+// position p when it is a Lyndon word and -1 when it is not: Lyndon-word coordinates.
+template <typename T, typename Sh, bool FLAGS, int WPB>
+__global__ void __launch_bounds__(WPB * 32)
+tile_forward_log_kernel(PathView<T> pv, T* __restrict__ out, uint64_t batch, uint32_t out_stride, uint32_t out_shift,
+                        const int32_t* __restrict__ rank, int* __restrict__ nonfinite) {
+    using Lay = LogSweepShape<Sh, WPB>;
+    constexpr int D = Sh::D, N = Sh::N, Q = Sh::Q;
+    constexpr int DP = RowPad<T, D>::DP;
+    constexpr int WPP = Lay::WPP, C = Lay::CTAS_PER_PATH, PPC = Lay::PATHS_PER_CTA, LOW = Lay::LOW;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * DP;
+    T* low_base = reinterpret_cast<T*>(smem_raw) + size_t(WPB) * kTileChunk * DP;
+
+    // which path, which warp of it, which copy of the lower levels
+    uint64_t b;
+    int wip, slot;
+    if constexpr (WPP >= WPB) {
+        b = blockIdx.x / C;
+        wip = int(blockIdx.x % C) * WPB + warp;
+        slot = 0;
+    } else {
+        slot = warp / WPP;
+        b = uint64_t(blockIdx.x) * PPC + slot;
+        wip = warp - slot * WPP;
+    }
+    const bool valid = b < batch && wip < WPP && slot < PPC;
+    const int u = wip * 32 + lane;
+    const bool active = valid && u < Sh::UNITS;
+    const UnitIndex<Sh> ix = decode_unit<Sh>(active ? u : 0);
+    T* low = low_base + size_t(slot < PPC ? slot : 0) * LOW;
+
+    TileState<T, Sh> st;
+    if (valid) tile_sweep_forward<T, Sh, FLAGS>(st, pv, pv.base + b * pv.path_stride, 0, pv.steps, zs, ix, lane);
+    if (active && nonfinite != nullptr && tile_nonfinite<T, Sh>(st)) *nonfinite = 1;
+
+    // levels below N of the whole path, in every CTA that holds units of it
+    if constexpr (C > 1) {
+        cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+        for (int r = 0; r < C; ++r) {
+            T* peer = cluster.map_shared_rank(low, r);
+            if (active) tile_publish_low<T, Sh>(st, ix, peer);
+            if (active && u == 0) peer[0] = T(1);
+        }
+        cluster.sync();
+    } else {
+        if (active) tile_publish_low<T, Sh>(st, ix, low);
+        if (active && u == 0) low[0] = T(1);
+        __syncthreads();
+    }
+
+    T* dst = out + b * uint64_t(out_stride);
+    auto emit = [&](int pos0, T value) {   // pos0: position in the scalar-free layout
+        if (rank == nullptr) dst[out_shift + pos0] = value;
+        else {
+            const int32_t r = rank[pos0];
+            if (r >= 0) dst[r] = value;
+        }
+    };
+    if (active) {
+        if (rank == nullptr && out_shift != 0 && u == 0) dst[0] = T(0);
+        tile_log_top<T, Sh>(st, ix, low);
+        constexpr int top = cgeom(D, N) - 1;   // scalar-free position of the first level-N word
+        if constexpr (Q >= 2) {
+#pragma unroll
+            for (int j = 0; j < Sh::nodes(Q - 1); ++j) {
+                const int row = ((ix.pw * D + ix.c0) * cpow(D, Q - 2) + j) * D;
+#pragma unroll
+                for (int e = 0; e < D; ++e) emit(top + row + e, st.s[Sh::off(Q) + j * D + e]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < Sh::G; ++j) emit(top + ix.pw * D + ix.c0 + j, st.s[j]);
+        }
+    }
+    // the levels below N: their prefixes are shared out over the threads that hold units of the path
+    if (valid) {
+        int first, stride;
+        if constexpr (C > 1) {
+            first = int(blockIdx.x % C) * (WPB * 32) + threadIdx.x;
+            stride = C * WPB * 32;
+        } else {
+            first = wip * 32 + lane;
+            stride = WPP * 32;
+        }
+        for (int prefix = first; prefix < cgeom(D, N - 1); prefix += stride)
+            log_low_prefix<T, D, N>(low, prefix, [&](int pos, T value) { emit(pos - 1, value); });
     }
 }
 

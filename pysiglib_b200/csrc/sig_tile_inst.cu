@@ -17,7 +17,7 @@
 namespace sigb200 {
 
 void SIG_CAT(register_tile_part_, SIG_TILE_PART)(std::vector<TileEntry>& table) {
-#define X(T, BWD, D, N, P, G, EST) table.push_back(make_tile_entry<T, D, N, P, G>(BWD != 0, EST));
+#define X(T, BWD, D, N, P, G, EST, LOG) table.push_back(make_tile_entry<T, D, N, P, G, BWD, LOG>(EST));
     SIG_CAT(SIG_TILE_PART_, SIG_TILE_PART)(X)
 #undef X
 }

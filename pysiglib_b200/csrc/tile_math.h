@@ -480,4 +480,130 @@ SIG_HD void tile_pullback(const TileState<T, Sh, TOP>& st, TileAdjoint<T, Sh>& a
     }
 }
 
+// ---- log-signature epilogue --------------------------------------------------------------------
+//
+// log S = sum_{k >= 1} (-1)^(k+1)/k x^(x)k with x = S - 1.  For a word w = u e (prefix u of length n1,
+// last letter e) the coefficient of x^(x)k splits by the position of the last cut, so
+//     log S[u e] = sum_{i = 0..n1} h[i] * S[u_{i+1} .. u_{n1} e],
+//     h[i] = sum_{m = 0..i} (-1)^m / (m + 1) * g_m[i],   g_m[i] = coefficient of x^(x)m at u_1 .. u_i
+// (g_0 = 1 at the empty word).  The weights h depend on the prefix only and involve coefficients
+// of levels below |w|, so a unit of the forward sweep can turn the level-N coefficients it holds
+// in registers into their logarithm as soon as the levels below N of the whole signature can be
+// read from somewhere: `low`, levels 0 .. N-1 in the scalar-term layout (low[0] = 1).
+// Same values as the tensor logarithm of the reference (siglib/cpsig/cp_tensor_log.h:47-122), summed
+// in a different order.
+
+// h[0 .. n1] for the prefix word of level n1 with index uidx inside that level (n1 <= N - 1).
+// pre[i] receives the index of u_1 .. u_i inside level i.  All loops have compile-time bounds and
+// are predicated on n1, so that with a constant n1 everything stays in registers.
+template <typename T, int D, int N>
+SIG_HD void log_prefix_weights(const T* low, int n1, int uidx, T* h, int* pre) {
+    int rest = uidx;
+#pragma unroll
+    for (int i = N - 1; i >= 0; --i) {
+        if (i <= n1) {
+            pre[i] = rest;
+            rest /= D;
+        }
+    }
+    T prev[N], cur[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        prev[i] = i == 0 ? T(1) : T(0);
+        h[i] = prev[i];
+        cur[i] = T(0);
+    }
+#pragma unroll
+    for (int m = 1; m < N; ++m) {
+        if (m <= n1) {
+            const T c = (m % 2 ? T(-1) : T(1)) / T(m + 1);
+#pragma unroll
+            for (int i = 1; i < N; ++i) {
+                if (i >= m && i <= n1) {
+                    T acc = T(0);
+#pragma unroll
+                    for (int ip = 0; ip < N - 1; ++ip)
+                        if (ip >= m - 1 && ip < i)
+                            acc = sig_fma(prev[ip], low[cgeom(D, i - ip) + pre[i] - pre[ip] * cpow(D, i - ip)], acc);
+                    cur[i] = acc;
+                    h[i] = sig_fma(c, acc, h[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) prev[i] = i >= m ? cur[i] : T(0);
+        }
+    }
+}
+
+// log S at the word u e of level n = n1 + 1 given the weights of u; `own` = S[u e] itself.
+template <typename T, int D, int N>
+SIG_HD T log_word(const T* low, int n1, const T* h, const int* pre, int e, T own) {
+    T acc = h[0] * own;
+#pragma unroll
+    for (int k = 1; k < N; ++k) {          // k = n1 - i + 1: length of the piece u_{i+1} .. u_{n1} e
+        const int i = n1 - k + 1;
+        if (i >= 1) acc = sig_fma(h[i], low[cgeom(D, k) + (pre[n1] - pre[i] * cpow(D, k - 1)) * D + e], acc);
+    }
+    return acc;
+}
+
+// The unit's coefficients below level N, written to `low` (scalar-term layout of levels 0 .. N-1).
+template <typename T, typename Sh>
+SIG_HD void tile_publish_low(const TileState<T, Sh>& st, const UnitIndex<Sh>& ix, T* low) {
+#pragma unroll
+    for (int k = 1; k <= Sh::P; ++k)
+        if (ix.chain_owner[k]) low[cgeom(Sh::D, k) + ix.pw / cpow(Sh::D, Sh::P - k)] = st.ch[k];
+#pragma unroll
+    for (int q = 1; q < Sh::Q; ++q) {
+        T* dst = low + cgeom(Sh::D, Sh::P + q) + (ix.pw * Sh::D + ix.c0) * cpow(Sh::D, q - 1);
+#pragma unroll
+        for (int j = 0; j < Sh::nodes(q); ++j) dst[j] = st.s[Sh::off(q) + j];
+    }
+}
+
+// Replaces the unit's level-N coefficients by those of log S (in place, in the registers).
+template <typename T, typename Sh>
+SIG_HD void tile_log_top(TileState<T, Sh>& st, const UnitIndex<Sh>& ix, const T* low) {
+    constexpr int D = Sh::D, N = Sh::N, Q = Sh::Q;
+    T h[N];
+    int pre[N];
+    if constexpr (Q >= 2) {
+#pragma unroll
+        for (int j = 0; j < Sh::nodes(Q - 1); ++j) {
+            const int uidx = (ix.pw * D + ix.c0) * cpow(D, Q - 2) + j;
+            log_prefix_weights<T, D, N>(low, N - 1, uidx, h, pre);
+#pragma unroll
+            for (int e = 0; e < D; ++e) {
+                T& own = st.s[Sh::off(Q) + j * D + e];
+                own = log_word<T, D, N>(low, N - 1, h, pre, e, own);
+            }
+        }
+    } else {
+        log_prefix_weights<T, D, N>(low, N - 1, ix.pw, h, pre);
+#pragma unroll
+        for (int j = 0; j < Sh::G; ++j) st.s[j] = log_word<T, D, N>(low, N - 1, h, pre, ix.c0 + j, st.s[j]);
+    }
+}
+
+// log S at the words of the levels below N that share the prefix number `prefix` (0 <= prefix <
+// cgeom(D, N - 1): prefixes of all lengths 0 .. N-2, shortest first), from `low` alone; calls
+// emit(position in the scalar-term layout, value) for each of the D words.
+template <typename T, int D, int N, typename Emit>
+SIG_HD void log_low_prefix(const T* low, int prefix, Emit&& emit) {
+    int n1 = 0, start = 0, count = 1;     // prefixes of length n1 are numbered start .. start + count - 1
+    while (prefix >= start + count) {
+        start += count;
+        count *= D;
+        ++n1;
+    }
+    T h[N];
+    int pre[N];
+    log_prefix_weights<T, D, N>(low, n1, prefix - start, h, pre);
+    const int level_offset = cgeom(D, n1 + 1);
+    for (int e = 0; e < D; ++e) {
+        const int pos = level_offset + (prefix - start) * D + e;
+        emit(pos, log_word<T, D, N>(low, n1, h, pre, e, low[pos]));
+    }
+}
+
 }  // namespace sigb200

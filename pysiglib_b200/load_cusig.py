@@ -117,6 +117,10 @@ def _bind(lib):
         f.argtypes = (ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real, c_bool,
                       c_void_p, c_int)
         f.restype = c_int
+        f = getattr(lib, "sigb200_log_sig_" + suffix)
+        f.argtypes = (ptr, ptr, c_uint64, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real, c_int, c_bool,
+                      c_void_p, c_int, POINTER(c_int))
+        f.restype = c_int
         f = getattr(lib, "sigb200_sig_backprop_noalloc_" + suffix)
         f.argtypes = (ptr, ptr, ptr, ptr, c_uint64, c_uint64, c_uint64, c_uint64, c_bool, c_bool, real, c_bool,
                       c_void_p, c_int)

@@ -9,16 +9,18 @@ Same names, parameters and layouts as the reference's operators (``pysiglib/log_
 
 Method 3 (from the path, without the signature) is not part of this build and raises
 ``NotImplementedError``."""
+import ctypes
+import warnings
 from typing import Union
 
 import numpy as np
 import torch
 
 from . import load_cusig
-from .data_handlers import Output
+from .data_handlers import Output, PathInput
 from .error_codes import err_msg
 from .param_checks import check_n_jobs, check_non_neg, check_type
-from .sig import _Sig, sig
+from .sig import NONFINITE_WARNING, _Sig, _current_stream, _finish_current_stream, sig
 from .sig_length import aug_dim, infer_scalar_term, log_sig_length, sig_length
 
 
@@ -84,6 +86,7 @@ def sig_to_log_sig(
     if a.batch_size == 0:
         return result.array
     check_n_jobs(n_jobs)
+    _finish_current_stream(a.array)
     code = load_cusig.fn("sig_to_log_sig_cuda", a.dtype)(a.pointer, result.pointer, a.batch_size, d, degree, method,
                                                          scalar_term)
     if code:
@@ -130,6 +133,7 @@ def sig_to_log_sig_backprop(
     if a.batch_size == 0:
         return result.array
     check_n_jobs(n_jobs)
+    _finish_current_stream(a.array)
     code = load_cusig.fn("sig_to_log_sig_backprop_cuda", a.dtype)(a.pointer, result.pointer, g.pointer, a.batch_size, d,
                                                                   degree, method, scalar_term)
     if code:
@@ -149,10 +153,40 @@ def log_sig(
         correction=None,
         n_jobs: int = 1
 ) -> Union[np.ndarray, torch.Tensor]:
-    """Log signature of a path: ``sig`` followed by ``sig_to_log_sig`` (methods 0, 1 and 2).
-    ``scalar_term`` only matters for method 0, whose result has the layout of the signature."""
+    """Log signature of a path (methods 0, 1 and 2): the reference composes ``sig`` and
+    ``sig_to_log_sig`` in Python (``pysiglib/log_sig.py:457``); here it is ONE native call in which the
+    signature is never written to an array the caller sees, and for shapes with a fused kernel never
+    leaves the GPU's SMs at all.  ``scalar_term`` only matters for method 0, whose result has the layout
+    of the signature.  With a ``correction`` the two-step composition is used.
+
+    A ``RuntimeWarning`` is issued when the underlying signature contains NaN or Inf, as ``sig`` does."""
     _check_method(method, "log_sig")
-    sig_ = sig(path, degree, scalar_term=scalar_term, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time,
-               horner=True, correction=correction, n_jobs=n_jobs)
-    return sig_to_log_sig(sig_, path.shape[-1], degree, time_aug=time_aug, lead_lag=lead_lag, method=method,
-                          n_jobs=n_jobs)
+    has_correction = correction is not None and (
+        correction.numel() if isinstance(correction, torch.Tensor) else np.size(correction)) > 0
+    if has_correction:
+        sig_ = sig(path, degree, scalar_term=scalar_term, time_aug=time_aug, lead_lag=lead_lag, end_time=end_time,
+                   horner=True, correction=correction, n_jobs=n_jobs)
+        return sig_to_log_sig(sig_, path.shape[-1], degree, time_aug=time_aug, lead_lag=lead_lag, method=method,
+                              n_jobs=n_jobs)
+    check_type(degree, "degree", int)
+    check_non_neg(degree, "degree")
+    check_type(time_aug, "time_aug", bool)
+    check_type(lead_lag, "lead_lag", bool)
+    check_type(end_time, "end_time", float)
+    check_type(scalar_term, "scalar_term", bool)
+    check_n_jobs(n_jobs)
+    data = PathInput(path, time_aug, lead_lag, end_time)
+    out_len = log_sig_length(data.dimension, degree) if method else sig_length(data.dimension, degree,
+                                                                               scalar_term=scalar_term)
+    result = Output(data, (out_len,))
+    if data.batch_size == 0:
+        return result.array
+    bad = ctypes.c_int(0)
+    code = load_cusig.fn("sigb200_log_sig", data.dtype)(
+        data.pointer, result.pointer, data.batch_size, data.data_dimension, data.data_length, degree, time_aug, lead_lag,
+        end_time, method, scalar_term, _current_stream(data.array), 1, ctypes.byref(bad))
+    if code:
+        raise Exception("Error in pysiglib.log_sig: " + err_msg(code))
+    if bad.value:
+        warnings.warn(NONFINITE_WARNING, RuntimeWarning, stacklevel=2)
+    return result.array

@@ -25,6 +25,21 @@ def _current_stream(array):
     return ctypes.c_void_p(None)
 
 
+def _finish_current_stream(*arrays):
+    """For the entry points that keep the reference's signature (no stream argument): they run on
+    the legacy default stream, which is not ordered after work queued on a non-blocking side
+    stream (every torch side stream is one).  If the caller's current stream on a tensor's device
+    is such a stream, wait for it, so the kernels never read an operand that is still being
+    produced; the calls themselves return only when their result is complete."""
+    seen = set()
+    for array in arrays:
+        if isinstance(array, torch.Tensor) and array.is_cuda and array.device not in seen:
+            seen.add(array.device)
+            stream = torch.cuda.current_stream(array.device)
+            if stream.cuda_stream != 0:
+                stream.synchronize()
+
+
 def sig(
         path: Union[np.ndarray, torch.Tensor],
         degree: int,
@@ -88,6 +103,7 @@ def sig(
 
     if corr.length:
         # the reference's own symbol carries the correction arguments (synchronous)
+        _finish_current_stream(data.array)
         code = load_cusig.fn("signature_cuda", data.dtype)(
             data.pointer, result.pointer, data.batch_size, data.data_dimension, data.data_length, degree,
             time_aug, lead_lag, end_time, horner, scalar_term, corr.pointer, corr.length, corr.batch_stride,
@@ -177,6 +193,7 @@ def sig_combine(
     if batch == 0 or a.array.shape[-1] == 0:
         return result.array
     from .sig_length import aug_dim
+    _finish_current_stream(a.array)
     code = load_cusig.fn("sig_combine_cuda", a.dtype)(
         a.pointer, b.pointer, result.pointer, batch, aug_dim(dimension, time_aug, lead_lag), degree, scalar_term)
     if code:
@@ -219,6 +236,7 @@ def sig_combine_backprop(
     if a.batch_size == 0 or a.array.shape[-1] == 0:
         return out1.array, out2.array
     from .sig_length import aug_dim
+    _finish_current_stream(a.array)
     code = load_cusig.fn("sig_combine_backprop_cuda", a.dtype)(
         d.pointer, out1.pointer, out2.pointer, a.pointer, b.pointer, a.batch_size,
         aug_dim(dimension, time_aug, lead_lag), degree, scalar_term)

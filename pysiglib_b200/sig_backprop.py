@@ -11,7 +11,7 @@ from . import load_cusig
 from .data_handlers import CorrectionInput, Output, PathInput, SigInput, check_same
 from .error_codes import err_msg
 from .param_checks import check_n_jobs, check_non_neg, check_type
-from .sig import _current_stream
+from .sig import _current_stream, _finish_current_stream
 from .sig_length import infer_scalar_term, sig_length
 
 
@@ -76,6 +76,7 @@ def sig_backprop(
     del scalar_term  # SigInput has already stripped the scalar slot
 
     if corr.length:
+        _finish_current_stream(data.array)
         code = load_cusig.fn("sig_backprop_cuda", data.dtype)(
             data.pointer, result.pointer, der_in.pointer, sig_in.pointer, data.batch_size, data.data_dimension,
             data.data_length, degree, time_aug, lead_lag, end_time, False, corr.pointer, corr.length,

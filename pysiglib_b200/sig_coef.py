@@ -14,7 +14,7 @@ from . import load_cusig
 from .data_handlers import Output, PathInput
 from .error_codes import err_msg
 from .param_checks import check_n_jobs, check_non_neg, check_type
-from .sig import _Sig
+from .sig import _Sig, _finish_current_stream
 from .sig_length import aug_dim
 from .transform_path import transform_path, transform_path_backprop
 
@@ -119,6 +119,7 @@ def sig_coef(
         return result.array
     check_n_jobs(n_jobs)
     keep, (idx_ptr, deg_ptr) = _word_arrays(words, data)
+    _finish_current_stream(data.array)
     code = load_cusig.fn("sig_coef_cuda", data.dtype)(
         data.pointer, result.pointer, idx_ptr, len(words), deg_ptr, data.batch_size, data.data_dimension,
         data.data_length, prefixes)
@@ -174,6 +175,7 @@ def sig_coef_backprop(
         return result.array
     check_n_jobs(n_jobs)
     keep, (idx_ptr, deg_ptr) = _word_arrays(words, data)
+    _finish_current_stream(data.array)
     code = load_cusig.fn("sig_coef_backprop_cuda", data.dtype)(
         data.pointer, result.pointer, c.pointer, g.pointer, idx_ptr, len(words), deg_ptr, data.batch_size,
         data.data_dimension, data.data_length)

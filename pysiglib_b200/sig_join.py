@@ -13,7 +13,7 @@ from . import load_cusig
 from .data_handlers import Output, check_same
 from .error_codes import err_msg
 from .param_checks import check_n_jobs, check_non_neg, check_type
-from .sig import _Sig
+from .sig import _Sig, _finish_current_stream
 from .sig_length import infer_scalar_term, sig_length
 
 
@@ -55,6 +55,7 @@ def linear_sig(
     result = Output(v, (sig_length(dimension, degree, scalar_term=scalar_term),))
     if v.batch_size == 0 or result.array.shape[-1] == 0:
         return result.array
+    _finish_current_stream(v.array)
     code = load_cusig.fn("linear_sig_cuda", v.dtype)(v.pointer, result.pointer, v.batch_size, dimension, degree,
                                                      scalar_term)
     if code:
@@ -93,6 +94,7 @@ def sig_join(
     result = Output(a, (a.array.shape[-1],))
     if a.batch_size == 0 or a.array.shape[-1] == 0:
         return result.array
+    _finish_current_stream(a.array)
     code = load_cusig.fn("sig_join_cuda", a.dtype)(a.pointer, v.pointer, result.pointer, a.batch_size, dimension,
                                                    degree, bool(prepend), scalar_term)
     if code:
@@ -129,6 +131,7 @@ def sig_join_backprop(
     d_sig, d_disp = Output(g, (a.array.shape[-1],)), Output(g, (dimension,))
     if g.batch_size == 0:
         return d_sig.array, d_disp.array
+    _finish_current_stream(g.array)
     code = load_cusig.fn("sig_join_backprop_cuda", g.dtype)(
         g.pointer, d_sig.pointer, d_disp.pointer, a.pointer, v.pointer, g.batch_size, dimension, degree,
         bool(prepend), scalar_term)

@@ -12,6 +12,7 @@ from . import load_cusig
 from .data_handlers import Output, PathInput
 from .error_codes import err_msg
 from .param_checks import check_n_jobs, check_type
+from .sig import _finish_current_stream
 
 
 def transform_path(
@@ -39,6 +40,7 @@ def transform_path(
     result = Output(data, (data.length, data.dimension))
     if data.batch_size == 0:
         return result.array
+    _finish_current_stream(data.array)
     code = load_cusig.fn("transform_path_cuda", data.dtype)(
         data.pointer, result.pointer, data.batch_size, data.data_dimension, data.data_length, time_aug, lead_lag,
         end_time)
@@ -71,6 +73,7 @@ def transform_path_backprop(
     result = Output(data, (length, dimension))
     if data.batch_size == 0 or length == 0 or dimension == 0:
         return result.array
+    _finish_current_stream(data.array)
     code = load_cusig.fn("transform_path_backprop_cuda", data.dtype)(
         data.pointer, result.pointer, data.batch_size, dimension, length, time_aug, lead_lag, end_time)
     if code:

@@ -71,12 +71,50 @@ static void backward_path(const T* path, int L, const T* sig, const T* seeds, T*
         }
 }
 
+// expanded log signature (scalar-free layout) through the epilogue of the fused forward sweep:
+// every unit sweeps the path, publishes its coefficients below level N, then turns its level-N
+// coefficients into their logarithm; the levels below N are taken from the published ones
+template <typename T, typename Sh>
+static void forward_log_path(const T* path, int L, T* out) {
+    constexpr int D = Sh::D, N = Sh::N;
+    std::vector<TileState<T, Sh>> states(Sh::UNITS);
+    std::vector<T> low(cgeom(D, N), T(0));
+    low[0] = T(1);
+    for (int u = 0; u < Sh::UNITS; ++u) {
+        const UnitIndex<Sh> ix = decode_unit<Sh>(u);
+        TileState<T, Sh>& st = states[u];
+        T zf[D], z[D], zg[Sh::G], zc[Sh::P + 1];
+        for (int step = 0; step + 1 < L; ++step) {
+            for (int c = 0; c < D; ++c) zf[c] = path[(step + 1) * D + c] - path[step * D + c];
+            gather_z<T, Sh>(zf, ix, z, zg, zc, T(1));
+            if (step == 0) tile_init_first<T, Sh>(st, z, zg, zc);
+            else tile_update<T, Sh>(st, z, zg, zc);
+        }
+        tile_publish_low<T, Sh>(st, ix, low.data());
+    }
+    T* S = out - 1;
+    for (int u = 0; u < Sh::UNITS; ++u) {
+        const UnitIndex<Sh> ix = decode_unit<Sh>(u);
+        tile_log_top<T, Sh>(states[u], ix, low.data());
+        // only the deepest tile level is final; tile_store also writes the others, overwritten below
+        tile_store<T, Sh>(states[u], ix, S);
+    }
+    for (int prefix = 0; prefix < cgeom(D, N - 1); ++prefix)
+        log_low_prefix<T, D, N>(low.data(), prefix, [&](int pos, T value) { S[pos] = value; });
+}
+
 #define HARNESS(D, N, P, G)                                                                              \
     extern "C" void fwd_f_##D##_##N##_##P##_##G(const float* p, int L, float* o) {                       \
         forward_path<float, TileShape<D, N, P, G>>(p, L, o);                                             \
     }                                                                                                    \
     extern "C" void fwd_d_##D##_##N##_##P##_##G(const double* p, int L, double* o) {                     \
         forward_path<double, TileShape<D, N, P, G>>(p, L, o);                                            \
+    }                                                                                                    \
+    extern "C" void log_f_##D##_##N##_##P##_##G(const float* p, int L, float* o) {                       \
+        forward_log_path<float, TileShape<D, N, P, G>>(p, L, o);                                         \
+    }                                                                                                    \
+    extern "C" void log_d_##D##_##N##_##P##_##G(const double* p, int L, double* o) {                     \
+        forward_log_path<double, TileShape<D, N, P, G>>(p, L, o);                                        \
     }                                                                                                    \
     extern "C" void bwd_f_##D##_##N##_##P##_##G(const float* p, int L, const float* s, const float* ds,  \
                                                 float* g) {                                              \

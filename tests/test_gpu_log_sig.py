@@ -182,3 +182,63 @@ def test_unbuilt_methods_and_errors():
     assert lib.prepare_log_sig_cuda(2, 3, 1, False) == 0
     assert lib.prepare_log_sig_cuda(2, 3, 2, False) == 0
     assert lib.prepare_log_sig_cuda(2, 3, 3, False) == 2
+
+
+FUSED_CASES = [  # (B, L, d, N, flags): shapes whose biggest forward tile carries the fused log-signature sweep
+    (5, 40, 16, 4, {}),                       # 16 warps per path: a cluster of 4 CTAs shares the lower levels
+    (9, 33, 8, 4, {}),                        # float32: one warp per path, four paths per CTA
+    (6, 30, 3, 4, {"time_aug": True}),
+    (3, 20, 4, 3, {"lead_lag": True}),
+    (300, 20, 16, 4, {}),
+    (70000, 5, 3, 3, {}),                     # more CTAs than one grid row of paths
+]
+
+
+@pytest.mark.parametrize("case", FUSED_CASES, ids=lambda c: "B%d_L%d_d%d_N%d%s" % (c[:4] + ("".join("_" + k for k in c[4]),)))
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("method", [0, 1, 2])
+def test_fused_log_sweep_matches_the_two_step_route_and_the_oracle(case, dtype, method):
+    """log_sig in one launch: the forward sweep publishes the levels below N in (distributed) shared
+    memory and turns its level-N registers into the logarithm; the signature never reaches global
+    memory.  Forced through the test hook (the automatic rule only picks it for short paths), checked
+    against the route through scratch and against the oracle."""
+    import pysiglib_b200
+    from pysiglib_b200 import load_cusig
+    B, L, d, N, kw = case
+    D = (2 * d if kw.get("lead_lag") else d) + (1 if kw.get("time_aug") else 0)
+    path = brownian_paths(B % 97 + L + d, B, L, d, dtype) * 1.2
+    x = torch.tensor(path, device="cuda")
+    scalar = method == 0 and B == 9
+    pysiglib_b200.prepare_log_sig(D, N, method)
+    load_cusig.set_kernel_policy(1)   # generic kernels: the signature goes to scratch, then the tensor-log kernels
+    try:
+        two_step = pysiglib_b200.log_sig(x, N, method=method, scalar_term=scalar, **kw)
+    finally:
+        load_cusig.set_kernel_policy(0)
+    load_cusig.set_tile_preference(1)
+    try:
+        before = load_cusig.launch_count()
+        fused = pysiglib_b200.log_sig(x, N, method=method, scalar_term=scalar, **kw)
+        launches = load_cusig.launch_count() - before
+    finally:
+        load_cusig.set_tile_preference(0)
+    assert launches == (2 if method == 2 else 1), "the fused sweep did not run (%d launches)" % launches
+    assert fused.shape == two_step.shape
+    n = min(B, 8)
+    sig64 = oracle.sig(path[:n].astype(np.float64), N, **kw)
+    want = oracle.sig_to_log_sig(sig64, D, N, method=method)
+    got, ref = fused[:n].cpu().numpy(), two_step[:n].cpu().numpy()
+    if scalar:
+        assert np.all(got[:, 0] == 0)
+        got, ref = got[:, 1:], ref[:, 1:]
+    tol = 1e-10 if dtype == np.float64 else 2e-5
+    if method == 0:
+        _assert_log_close(got, want, sig64, D, N, tol)
+        _assert_log_close(ref, want, sig64, D, N, tol)
+    else:
+        scale = np.maximum(np.abs(sig64).max(axis=1, keepdims=True), 1.0) * (1.0 if method == 1 else 10.0)
+        assert np.all(np.abs(got - want) <= tol * scale), np.abs(got - want).max()
+        assert np.all(np.abs(ref - want) <= tol * scale)
+    # the whole batch agrees with the two-step route to rounding
+    scale_all = float(two_step.abs().max()) + 1e-30
+    assert float((fused - two_step).abs().max()) <= (1e-11 if dtype == np.float64 else 3e-5) * max(scale_all, 1.0)

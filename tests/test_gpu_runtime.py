@@ -112,7 +112,7 @@ def _variants_of(d, N, dtype, backward):
         text = f.read()
     name = "float" if dtype == np.float32 else "double"
     return sorted({(int(p), int(g)) for p, g in
-                   re.findall(r"X\(%s, %d, %d, %d, (\d+), (\d+), \d+\)" % (name, 1 if backward else 0, d, N), text)})
+                   re.findall(r"X\(%s, %d, %d, %d, (\d+), (\d+), \d+, \d+\)" % (name, 1 if backward else 0, d, N), text)})
 
 
 @pytest.mark.parametrize("d,N", [(16, 4), (8, 4), (5, 7), (10, 5), (2, 12), (3, 6)])
@@ -227,3 +227,27 @@ def test_deep_degree_shapes_run_on_register_tiles(case):
     code, grad = _backward(dpath, torch.tensor(expect, device="cuda"), torch.tensor(seeds, device="cuda"), N, **kw)
     assert code == 0, load_cusig.last_error_message()
     assert_grad_parity(grad.cpu().numpy(), want, truth, tol)
+
+
+def test_operators_without_a_stream_argument_wait_for_the_callers_side_stream():
+    """sig_combine and friends keep the reference's signatures and run on the legacy default
+    stream; an operand still being produced on a torch side stream (non-blocking, so the legacy
+    stream does not wait for it) must be finished before they read it."""
+    import pysiglib_b200
+    d, N, B = 8, 4, 512
+    a_np = oracle.sig(brownian_paths(1, 4, 20, d, np.float32), N)
+    side = torch.cuda.Stream()
+    big = torch.randn((4096, 4096), device="cuda")
+    with torch.cuda.stream(side):
+        for _ in range(20):
+            big = big @ big * 1e-4            # keeps the side stream busy for a while
+        a = torch.tensor(np.tile(a_np, (B // 4, 1)), device="cuda") + big[0, 0] * 0.0
+        b = a.clone()
+        out = pysiglib_b200.sig_combine(a, b, d, N)
+        lin = pysiglib_b200.sig_to_log_sig(a, d, N, method=0)
+    side.synchronize()
+    want = oracle.sig_combine(a_np, a_np, d, N)
+    assert_sig_close(out[:4].cpu().numpy(), want, d, N, 1e-5)
+    # the same calls once nothing is in flight give bit-identical results
+    assert torch.equal(out, pysiglib_b200.sig_combine(a, b, d, N))
+    assert torch.equal(lin, pysiglib_b200.sig_to_log_sig(a, d, N, method=0))

@@ -61,3 +61,20 @@ def test_tile_forward_and_backward(harness, shape, dtype):
     want = oracle.sig_backprop(path, expect, seeds, N)
     tol = 1e-11 if dtype == np.float64 else 2e-4
     np.testing.assert_allclose(grad, want, rtol=tol, atol=tol * np.abs(want).max())
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_tile_log_epilogue(harness, shape):
+    """The log-signature epilogue of the fused forward sweep (log_prefix_weights / tile_log_top /
+    log_low_prefix) against the oracle's tensor logarithm of the same signature."""
+    D, N, P, G = shape
+    rng = np.random.default_rng(D * 77 + N * 5 + P)
+    L = 6
+    path = np.ascontiguousarray(rng.normal(scale=0.6, size=(L, D)))
+    n = oracle.sig_length(D, N)
+    out = np.zeros(n)
+    getattr(harness, "log_d_%d_%d_%d_%d" % (D, N, P, G))(path.ctypes.data_as(ctypes.POINTER(ctypes.c_double)), L,
+                                                       out.ctypes.data_as(ctypes.POINTER(ctypes.c_double)))
+    want = oracle.sig_to_log_sig(oracle.sig(path, N), D, N, method=0)
+    scale = np.abs(oracle.sig(path, N)).max()
+    np.testing.assert_allclose(out, want, rtol=1e-10, atol=1e-12 * max(scale, 1.0))
