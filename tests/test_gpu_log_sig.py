@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import assert_grad_close, assert_sig_close
+from conftest import assert_grad_close, assert_sig_close, brownian_paths
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
