@@ -38,7 +38,7 @@ def _tile_parts():
 
 def _units():
     """(object name, source, extra flags) for every translation unit."""
-    units = [(n + ".o", n + ".cu", []) for n in ("abi", "dispatch", "runtime", "sig_generic", "sig_tile_dispatch", "sig_algebra", "sig_log", "sig_coef", "noalloc")]
+    units = [(n + ".o", n + ".cu", []) for n in ("abi", "dispatch", "runtime", "sig_generic", "sig_tile_dispatch", "sig_algebra", "sig_log", "sig_coef", "sig_chen", "sig_log_stream", "noalloc")]
     for k in range(_tile_parts()):
         units.append(("sig_tile_inst_%d.o" % k, "sig_tile_inst.cu", ["-DSIG_TILE_PART=%d" % k]))
     return units

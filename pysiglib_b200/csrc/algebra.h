@@ -101,4 +101,14 @@ template <typename T>
 void transform_path_backprop_entry(const T* derivs, T* data_out, uint64_t batch, uint64_t dimension, uint64_t length,
                                    bool time_aug, bool lead_lag, T end_time, const CallOptions& opt);
 
+// The backward pass of the tensor logarithm for a whole batch in one launch, one CTA per signature
+// (sig_log_stream.cu).  x / dsig: first level-1 coefficients; g: the gradient in expanded layout
+// (rank == nullptr) or with respect to the Lyndon-word coordinates (rank[p]: coordinate at scalar-free
+// position p, -1 if none).  Returns false with nothing launched when the shape is not served (batch
+// below the SM count, dimension not a power of two, degree < 2, working set beyond shared memory).
+template <typename T>
+bool launch_log_adjoint_streamed(const T* x, uint64_t x_stride, const T* g, uint64_t g_stride, const int32_t* rank,
+                                 T* dsig, uint64_t dsig_stride, bool zero_scalar, uint64_t batch, uint64_t dim,
+                                 uint64_t degree, cudaStream_t stream);
+
 }  // namespace sigb200

@@ -474,6 +474,10 @@ void sig_combine_backprop_entry(const T* deriv, T* sig1_deriv, T* sig2_deriv, co
             SIG_CUDA_CHECK(cudaMemsetAsync(d2, 0, n * sizeof(T), stream));
         }
         if (degree == 0) return;
+        // big batches: both adjoints in one pass over the incoming gradient (sig_chen.cu)
+        if (launch_chen_adjoints_streamed<T>(dS + shift, s.stride, a + shift, s.stride, b + shift, s.stride, d1 + shift,
+                                             s.stride, d2 + shift, s.stride, s, stream))
+            return;
         launch_chen_left_adjoint<T>(dS + shift, s.stride, b + shift, s.stride, d1 + shift, s.stride, s, stream);
         launch_chen_right_adjoint<T>(dS + shift, s.stride, a + shift, s.stride, d2 + shift, s.stride, s, stream);
     };

@@ -81,6 +81,26 @@ uint64_t chen_combine_tmp_elems(const SigShape& s, int nseg);
 template <typename T>
 void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int nseg, cudaStream_t stream);
 
+// C = A (x) B with one CTA per signature (sig_chen.cu): the levels below N of both factors in shared
+// memory, the top level streamed with vector loads and stores.  A or B may be nullptr: that factor is
+// then exp(disp[b]), the signature of the straight segment with displacement disp[b] (dimension values
+// per signature), generated on the fly.  Returns false, with nothing launched, when the batch is too
+// small to fill the GPU that way or the lower levels do not fit shared memory.
+template <typename T>
+bool launch_chen_product_streamed(const T* A, uint64_t a_stride, const T* B, uint64_t b_stride, const T* disp, T* C,
+                                  uint64_t c_stride, const SigShape& s, cudaStream_t stream, bool write_scalar);
+
+// Both adjoints of C = A (x) B from dC (dA[u] = sum_v dC[u v] B[v], dB[v] = sum_u A[u] dC[u v]) in one
+// pass over dC, one CTA per signature; every pointer addresses a first level-1 coefficient.  Returns
+// false, with nothing launched, under the same conditions as launch_chen_product_streamed.
+// gen = 1 / 2: factor A / B is exp(disp[b]) (its pointers are ignored) and the adjoint of the
+// displacement goes to d_disp (batch x dim) instead.
+template <typename T>
+bool launch_chen_adjoints_streamed(const T* dC, uint64_t dc_stride, const T* A, uint64_t a_stride, const T* B,
+                                   uint64_t b_stride, T* dA, uint64_t da_stride, T* dB, uint64_t db_stride,
+                                   const SigShape& s, cudaStream_t stream, int gen = 0, const T* disp = nullptr,
+                                   T* d_disp = nullptr);
+
 // C = A (x) B and the adjoint of the left factor, dX[u] = sum_v dS[u v] A[v], for batches of
 // scalar-free signatures; every pointer addresses the first level-1 coefficient of path 0 and
 // has its own batch stride (in elements).

@@ -485,6 +485,10 @@ void sig_join_entry(const T* sig, const T* displacement, T* out, uint64_t batch,
     const uint64_t S = s.full_len - 1;
     auto run = [&](const T* a, const T* v, T* o, cudaStream_t st) {
         if (degree == 0) { launch_fill<T>(o, batch * s.stride, T(1), st); return; }
+        // big batches: one pass, the segment's signature exp(v) is generated inside the product kernel
+        if (launch_chen_product_streamed<T>(prepend ? nullptr : a + shift, s.stride, prepend ? a + shift : nullptr, s.stride,
+                                            v, o + shift, s.stride, s, st, scalar_term))
+            return;
         Scratch lin(batch * S * sizeof(T), st);
         launch_linear_sig<T>(v, lin.as<T>(), S, lv, batch, false, st);
         if (prepend) launch_chen_product<T>(lin.as<T>(), S, a + shift, s.stride, o + shift, s.stride, s, st, scalar_term);
@@ -523,6 +527,10 @@ void sig_join_backprop_entry(const T* d_out, T* d_sig, T* d_displacement, const 
             SIG_CUDA_CHECK(cudaMemsetAsync(dv, 0, batch * dimension * sizeof(T), st));
             return;
         }
+        // big batches: one pass over the incoming gradient, exp(v) and its adjoint never leave the SM
+        if (launch_chen_adjoints_streamed<T>(g + shift, s.stride, a + shift, s.stride, a + shift, s.stride, ds + shift,
+                                             s.stride, ds + shift, s.stride, s, st, prepend ? 1 : 2, v, dv))
+            return;
         Scratch tmp(2 * batch * S * sizeof(T), st);
         T* lin = tmp.as<T>();
         T* dlin = lin + batch * S;

@@ -638,6 +638,8 @@ void launch_chen_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_s
     check_generic_limits(s);
     const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
     if (s.batch == 0 || slen == 0) return;
+    // big batches: one CTA per signature, operands streamed once (sig_chen.cu)
+    if (launch_chen_product_streamed<T>(A, a_stride, B, b_stride, nullptr, C, c_stride, s, stream, write_scalar)) return;
     const dim3 grid = batch_walk_grid(slen, s.batch);
     chen_product_kernel<T><<<grid, kGenericThreads, 0, stream>>>(
         A, a_stride, B, b_stride, C, c_stride, write_scalar, s.batch, slen, make_fast_div(static_cast<uint32_t>(s.dim)),

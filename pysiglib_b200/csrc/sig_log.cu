@@ -599,7 +599,9 @@ void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs
     auto run = [&](const T* a, T* o, const T* g, cudaStream_t st) {
         LyndonTable table;
         BasisTable basis;
+        LyndonRank rank;
         if (method >= 1) table = lyndon_table(dimension, degree);
+        if (method >= 1) rank = lyndon_rank_table(dimension, degree);
         if (method == 2) basis = basis_table(dimension, degree);
         const uint64_t g_stride = method >= 1 ? table.count : stride;
         const uint64_t vectors = 3 + (N >= 2 ? N - 1 : 0);  // D, two adjoint buffers, R_2..R_N
@@ -624,6 +626,11 @@ void sig_to_log_sig_backprop_entry(const T* sig, T* out, const T* log_sig_derivs
                 check_launch("tensor log backward kernel");
                 gw = pulled;
             }
+            // big batches of power-of-two dimension: the whole backward in one kernel, one CTA per
+            // signature, with the recursion in shared memory (sig_log_stream.cu)
+            if (launch_log_adjoint_streamed<T>(x, stride, gw, g_stride, method >= 1 ? rank.device : nullptr, dsig, stride,
+                                               scalar_term, count, dimension, degree, st))
+                continue;
             log_seed_kernel<T><<<coeff_grid(lv.total(), count), kThreads, 0, st>>>(
                 gw, g_stride, D, dsig, stride, lv, count, method >= 1 ? table.device : nullptr, scalar_term);
             check_launch("tensor log backward kernel");
