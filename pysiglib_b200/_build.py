@@ -44,9 +44,8 @@ def _units():
     return units
 
 
-def _stamp(dev=False):
-    h = hashlib.sha256((" ".join(NVCC_FLAGS) + (" dev" if dev else "") +
-                        os.environ.get("SIGB200_NO_PACKED_F32", "0")).encode())
+def _stamp():
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
     for folder in (CSRC, os.path.join(CSRC, "bench")):
         for name in sorted(os.listdir(folder)):
             if name.endswith((".h", ".cuh", ".cu")):
@@ -62,7 +61,7 @@ def _unit_hash(unit):
     repository that the preprocessor pulls in (nvcc -M), so that an edit recompiles only
     the objects that can see it."""
     obj, src, extra = unit
-    cmd = [_nvcc()] + NVCC_FLAGS + extra + _EXTRA + ["-M", os.path.join(CSRC, src)]
+    cmd = [_nvcc()] + NVCC_FLAGS + extra + ["-M", os.path.join(CSRC, src)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc -M failed for %s:\n%s\n%s" % (src, proc.stdout, proc.stderr))
@@ -72,7 +71,7 @@ def _unit_hash(unit):
         path = os.path.realpath(tok)
         if path.startswith(root + os.sep):
             deps.add(path)
-    h = hashlib.sha256((" ".join(NVCC_FLAGS + extra + _EXTRA)).encode())
+    h = hashlib.sha256((" ".join(NVCC_FLAGS + extra)).encode())
     for path in sorted(deps):
         with open(path, "rb") as f:
             h.update(os.path.relpath(path, root).encode() + f.read())
@@ -88,7 +87,7 @@ def _compile(unit):
         with open(hash_path) as f:
             if f.read().strip() == digest:
                 return obj, False
-    cmd = [_nvcc()] + NVCC_FLAGS + extra + _EXTRA + ["-c", os.path.join(CSRC, src), "-o", obj_path]
+    cmd = [_nvcc()] + NVCC_FLAGS + extra + ["-c", os.path.join(CSRC, src), "-o", obj_path]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, proc.stdout, proc.stderr))
@@ -97,26 +96,15 @@ def _compile(unit):
     return obj, True
 
 
-_EXTRA = []
 _FORCE = [False]
 
 
-def build(force=False, jobs=None, verbose=False, dev=None):
-    """Compile every CUDA translation unit for sm_100a and link libcusig.so; returns its path.
-
-    dev=True (or SIGB200_TILE_DEV=1) compiles only the development subset of the
-    register-tile table (tile_table_dev.h) for quick iteration; the default is the full table."""
-    if dev is None:
-        dev = os.environ.get("SIGB200_TILE_DEV", "0") == "1"
-    _EXTRA[:] = ["-DSIG_TILE_DEV"] if dev else []
-    if os.environ.get("SIGB200_NO_PACKED_F32", "0") == "1":  # experiment switch: scalar FP32 rows
-        _EXTRA.append("-DSIG_NO_PACKED_F32")
+def build(force=False, jobs=None, verbose=False):
+    """Compile every CUDA translation unit for sm_100a and link libcusig.so; returns its path."""
     _FORCE[0] = bool(force)
-    global OBJ
-    OBJ = os.path.join(CSRC, "_build_dev" if dev else "_build")  # two caches: switching tables recompiles nothing
     os.makedirs(OBJ, exist_ok=True)
     os.makedirs(LIB_DIR, exist_ok=True)
-    stamp, stamp_file = _stamp(dev), os.path.join(LIB_DIR, "stamp.txt")
+    stamp, stamp_file = _stamp(), os.path.join(LIB_DIR, "stamp.txt")
     if not force and os.path.exists(LIB) and os.path.exists(stamp_file):
         with open(stamp_file) as f:
             if f.read().strip() == stamp:
@@ -147,6 +135,5 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--jobs", type=int, default=None)
-    ap.add_argument("--dev", action="store_true", help="compile only the development subset of the tile table")
     args = ap.parse_args()
-    print(build(force=args.force, jobs=args.jobs, verbose=True, dev=True if args.dev else None))
+    print(build(force=args.force, jobs=args.jobs, verbose=True))

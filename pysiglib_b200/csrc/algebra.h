@@ -101,6 +101,15 @@ template <typename T>
 void transform_path_backprop_entry(const T* derivs, T* data_out, uint64_t batch, uint64_t dimension, uint64_t length,
                                    bool time_aug, bool lead_lag, T end_time, const CallOptions& opt);
 
+// The tensor logarithm of a whole batch in one launch, one CTA per signature (sig_log_stream.cu): the
+// expanded tensor (lyndon == nullptr, count = its length) or the coordinates at the Lyndon words
+// (lyndon[i]: scalar-free position of coordinate i).  Returns false with nothing launched when the shape
+// is not served (batch below the SM count, degree < 2, levels below N beyond shared memory).
+template <typename T>
+bool launch_log_forward_streamed(const T* x, uint64_t x_stride, T* out, uint64_t out_stride, const uint32_t* lyndon,
+                                 uint32_t count, bool zero_scalar, uint64_t batch, uint64_t dim, uint64_t degree,
+                                 cudaStream_t stream);
+
 // The backward pass of the tensor logarithm for a whole batch in one launch, one CTA per signature
 // (sig_log_stream.cu).  x / dsig: first level-1 coefficients; g: the gradient in expanded layout
 // (rank == nullptr) or with respect to the Lyndon-word coordinates (rank[p]: coordinate at scalar-free

@@ -14,6 +14,12 @@ namespace sigb200 {
 namespace {
 
 constexpr int kChenThreads = 256;
+// CTA size, CTAs per SM and vector loads in flight per thread of the adjoint kernels.  Measured on
+// B200 at d = 16, degree 4 (sig_combine backward): 256 x 3 x 4 -> 1.25 ms; 512 threads x 2 CTAs -> 1.52-1.56 ms;
+// 8 loads in flight -> 1.38 ms.
+constexpr int kAdjointThreads = 256;
+constexpr int kAdjointCtas = 3;
+constexpr int kAdjointLoads = 4;
 constexpr int kChenSplits = 7;    // register-resident suffix sums of the adjoint kernel: degrees up to 8
 
 template <typename T> __device__ __forceinline__ T chen_fma(T a, T b, T c);
@@ -133,7 +139,7 @@ __device__ __forceinline__ void adjoint_levels_regular(const AdjointShared<T>& s
                                                        T* __restrict__ db_top, T a_direct, T b_direct, int gen, int N,
                                                        uint32_t d, int lgd, T (&lastv)[VEC]) {
     using P = typename Pack<T, VEC>::type;
-    constexpr int kBatch = 4;
+    constexpr int kBatch = kAdjointLoads;
     const uint32_t tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
     const uint32_t* li = sm.li;
     const uint32_t lgw = 31 - __clz(nt * VEC);

@@ -83,16 +83,14 @@ def variants(D, N, budget):
     return out
 
 
-# shapes of the development table (quick builds): benchmark configs and a few test shapes
-DEV = {(16, 4), (8, 4), (5, 7), (10, 5), (2, 12), (3, 4), (2, 6), (5, 3), (9, 4), (4, 4), (17, 3)}
-
-
-def emit(path, dev, parts_n):
+def emit(path, parts_n, only=None):
+    """Writes the table header.  only: a set of (D, N) pairs to restrict the table to (a library for
+    a fixed set of shapes builds in a fraction of the time), None for every covered shape."""
     entries = []  # (cost, text)
     for tname, (bf, bb) in BUDGET.items():
         for D in sorted(set(COVER) | set(DEEP)):
             for N in range(2, max(COVER.get(D, 0), DEEP.get(D, 0)) + 1):
-                if dev and (D, N) not in DEV:
+                if only is not None and (D, N) not in only:
                     continue
                 if D ** N >= 1 << 31:
                     continue
@@ -130,8 +128,7 @@ def emit(path, dev, parts_n):
 
 def main():
     here = os.path.dirname(os.path.abspath(__file__))
-    emit(os.path.join(here, "tile_table.h"), False, PARTS)
-    emit(os.path.join(here, "tile_table_dev.h"), True, PARTS)
+    emit(os.path.join(here, "tile_table.h"), PARTS)
 
 
 if __name__ == "__main__":

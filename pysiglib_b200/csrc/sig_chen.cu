@@ -281,7 +281,7 @@ __device__ __forceinline__ void adjoint_levels_generic(const AdjointShared<T>& s
 
 // NS = 0: generic shapes; NS > 0: regular shapes with at most NS splits (degree <= NS + 1), lgd = log2(d).
 template <typename T, int VEC, int NS>
-__global__ void __launch_bounds__(kChenThreads, NS > 0 && NS <= 3 ? 3 : 1)
+__global__ void __launch_bounds__(kAdjointThreads, NS > 0 && NS <= 3 ? kAdjointCtas : 1)
 chen_adjoints_cta_kernel(const T* __restrict__ dC, uint64_t dc_stride, const T* __restrict__ A, uint64_t a_stride,
                          const T* __restrict__ B, uint64_t b_stride, T* __restrict__ dA, uint64_t da_stride,
                          T* __restrict__ dB, uint64_t db_stride, const T* __restrict__ disp, T* __restrict__ d_disp,
@@ -442,19 +442,19 @@ bool launch_chen_adjoints_streamed(const T* dC, uint64_t dc_stride, const T* A, 
     // the register-resident path needs power-of-two dimensions (then every vector width that divides d
     // also divides the words per iteration) and at most kChenSplits splits; otherwise the generic path
     int lgd = -1;
-    if ((s.dim & (s.dim - 1)) == 0 && s.degree - 1 <= uint64_t(kChenSplits) && s.dim <= uint64_t(kChenThreads)) {
+    if ((s.dim & (s.dim - 1)) == 0 && s.degree - 1 <= uint64_t(kChenSplits) && s.dim <= uint64_t(kAdjointThreads)) {
         lgd = 0;
         while ((1ull << lgd) < s.dim) ++lgd;
     }
     auto run = [&](auto kernel, int vec) {
         // regular shapes: plus one table entry per iteration of every level (W = threads * vec words each)
-        const uint64_t entries = lgd >= 0 ? regular_order_entries(lev, s.degree, kChenThreads, vec) : 0;
+        const uint64_t entries = lgd >= 0 ? regular_order_entries(lev, s.degree, kAdjointThreads, vec) : 0;
         const size_t smem = base_smem + entries * sizeof(uint32_t);
         const unsigned per_sm = static_cast<unsigned>(std::max<size_t>(1, std::min<size_t>(8, (220 * 1024) / (smem + 1024))));
         const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(s.batch, uint64_t(sms) * per_sm));
         if (smem > 48 * 1024)
             SIG_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        kernel<<<grid, kChenThreads, smem, stream>>>(dC, dc_stride, A, a_stride, B, b_stride, dA, da_stride, dB, db_stride,
+        kernel<<<grid, kAdjointThreads, smem, stream>>>(dC, dc_stride, A, a_stride, B, b_stride, dA, da_stride, dB, db_stride,
                                                      disp, d_disp, gen, s.batch, static_cast<int>(s.degree),
                                                      static_cast<uint32_t>(s.dim), lgd, lev);
         SIG_CUDA_CHECK(cudaGetLastError());

@@ -462,6 +462,22 @@ void sig_to_log_sig_entry(const T* sig, T* out, uint64_t batch, uint64_t dimensi
         for (uint64_t b0 = 0; b0 < batch; b0 += chunk) {
             const uint64_t count = std::min(chunk, batch - b0);
             const T* x = a + b0 * in_stride + shift;
+            // big batches: one kernel, one CTA per signature, the recursion in shared memory
+            {
+                T* target = method == 2 ? ws.as<T>() + 2 * chunk * S
+                                        : o + b0 * out_stride + (method == 0 ? shift : 0);
+                if (launch_log_forward_streamed<T>(x, in_stride, target, out_stride, method >= 1 ? table.device : nullptr,
+                                                   method >= 1 ? table.count : static_cast<uint32_t>(S),
+                                                   method == 0 && scalar_term, count, dimension, degree, st)) {
+                    if (method == 2) {
+                        basis_spmv_kernel<T><<<coeff_grid(basis.rows, count), kThreads, 0, st>>>(
+                            target, out_stride, o + b0 * out_stride, out_stride, basis.row_ptr, basis.col, basis.val,
+                            basis.rows, count);
+                        check_launch("tensor log kernel");
+                    }
+                    continue;
+                }
+            }
             const T* r2 = degree >= 2 ? run_horner<T>(x, in_stride, ws.as<T>(), false, lv, count, st) : nullptr;
             if (method >= 1) {
                 // Lyndon-word coordinates, straight into the result (method 1) or into scratch (method 2)
@@ -541,6 +557,11 @@ void log_sig_entry(const T* path, T* out, uint64_t batch, uint64_t dimension, ui
                 cs.batch = count;
                 T* sig = ws.as<T>() + 2 * chunk * S;
                 forward_on_device<T>(dpath + b0 * length * dimension, sig, cs, end_time, st, flag);
+                if (launch_log_forward_streamed<T>(sig, S, target + b0 * out_len + (method == 0 ? shift : 0), out_len,
+                                                   method >= 1 ? table.device : nullptr,
+                                                   method >= 1 ? table.count : static_cast<uint32_t>(S), shift != 0, count,
+                                                   s.dim, degree, st))
+                    continue;
                 const T* r2 = degree >= 2 ? run_horner<T>(sig, S, ws.as<T>(), false, lv, count, st) : nullptr;
                 if (method >= 1) {
                     log_final_kernel<T><<<coeff_grid(table.count, count), kThreads, 0, st>>>(

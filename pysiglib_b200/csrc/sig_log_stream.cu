@@ -1,4 +1,4 @@
-// Backward pass of the tensor logarithm at HBM speed: one CTA per signature.
+// The tensor logarithm and its backward pass at HBM speed: one CTA per signature.
 //
 // Forward (sig_log.cu): with x the signature without its scalar term, R_{N+1} = 0,
 //     R_k = x / k - x (x) R_{k+1}   (k = N .. 2, needed on levels <= 1 + N - k),      y = x - x (x) R_2,
@@ -61,7 +61,7 @@ struct RankedGlobalLoader {
 };
 
 template <typename T, int VEC, int NS, bool RANKED>
-__global__ void __launch_bounds__(kChenThreads, NS <= 3 ? 3 : 1)
+__global__ void __launch_bounds__(kAdjointThreads, NS <= 3 ? kAdjointCtas : 1)
 log_adjoint_cta_kernel(const T* __restrict__ x, uint64_t x_stride, const T* __restrict__ g, uint64_t g_stride,
                        const int32_t* __restrict__ rank, T* __restrict__ dsig, uint64_t dsig_stride, bool zero_scalar,
                        uint64_t batch, int N, uint32_t d, int lgd, LevelIndex lev) {
@@ -168,9 +168,118 @@ log_adjoint_cta_kernel(const T* __restrict__ x, uint64_t x_stride, const T* __re
     }
 }
 
+// Forward: y = x - x (x) R_2 for one signature per CTA, any dimension.  -x and the running -R_k
+// (two buffers, R_k only needs R_{k+1}) live in shared memory on the levels below N; the outputs are
+// then one thread each: coordinate i is the word at scalar-free position lyndon[i] (or i itself for
+// the expanded layout), its value x[p] minus one product term per split, all operands of which are
+// below level N.  The signature's top level is read only where an output needs it.
+template <typename T>
+__global__ void __launch_bounds__(kChenThreads)
+log_forward_cta_kernel(const T* __restrict__ x, uint64_t x_stride, T* __restrict__ out, uint64_t out_stride,
+                       const uint32_t* __restrict__ lyndon, uint32_t count, bool zero_scalar, uint64_t batch, int N,
+                       uint32_t d, LevelIndex lev) {
+    extern __shared__ __align__(16) unsigned char log_smem[];
+    __shared__ uint32_t li[kMaxDegree + 2];
+    __shared__ uint32_t pw[kMaxDegree + 2];        // d^k
+    const uint32_t tid = threadIdx.x, nt = blockDim.x;
+    for (uint32_t i = tid; i < uint32_t(N + 2); i += nt) li[i] = lev.li[i];
+    if (tid == 0) {
+        uint32_t p = 1;
+        for (int k = 0; k <= N; ++k) {
+            pw[k] = p;
+            p *= d;
+        }
+    }
+    __syncthreads();
+    const uint32_t low_len = (li[N] + 3) & ~3u;
+    T* nx = reinterpret_cast<T*>(log_smem);        // -x, levels 1 .. N-1 (scalar-term addressing)
+    T* ra = nx + low_len;                          // -R_k, alternating
+    T* rb = ra + low_len;
+    const uint32_t low_count = li[N] - 1;
+
+    for (uint64_t b = blockIdx.x; b < batch; b += gridDim.x) {
+        __syncthreads();
+        const T* xb = x + b * x_stride;
+        for (uint32_t j = tid; j < low_count; j += nt) nx[1 + j] = -xb[j];
+        __syncthreads();
+        T* cur = ra;
+        T* next = rb;                              // holds -R_{k+1}
+        for (int k = N; k >= 2; --k) {
+            const uint32_t levels = 1 + N - k;
+            const T rk = T(1) / T(k);
+            for (uint32_t pos = 1 + tid; pos < li[levels + 1]; pos += nt) {
+                uint32_t t = 1;
+                while (pos >= li[t + 1]) ++t;
+                const uint32_t idx = pos - li[t];
+                T value = nx[pos] * rk;
+                if (k < N) {
+                    for (uint32_t i = t - 1; i >= 1; --i) {
+                        const uint32_t left = idx / pw[t - i];
+                        value = chen_fma(nx[li[i] + left], next[li[t - i] + idx - left * pw[t - i]], value);
+                    }
+                }
+                cur[pos] = value;
+            }
+            __syncthreads();
+            T* swap = cur;
+            cur = next;
+            next = swap;
+        }
+        const T* nr2 = next;                       // -R_2 on levels 1 .. N-1
+        T* ob = out + b * out_stride;
+        if (zero_scalar && tid == 0) ob[-1] = T(0);
+        for (uint32_t i = tid; i < count; i += nt) {
+            const uint32_t p = lyndon ? lyndon[i] : i;
+            uint32_t t = 1;
+            while (p + 1 >= li[t + 1]) ++t;
+            const uint32_t idx = p + 1 - li[t];
+            T value = xb[p];
+            // y = x - x (x) R_2 = x - (-x) (x) (-R_2)
+            for (uint32_t s = t - 1; s >= 1; --s) {
+                const uint32_t left = idx / pw[t - s];
+                value = chen_fma(-nx[li[s] + left], nr2[li[t - s] + idx - left * pw[t - s]], value);
+            }
+            ob[i] = value;
+        }
+    }
+}
+
 bool aligned_for(const void* p, size_t bytes) { return reinterpret_cast<uintptr_t>(p) % bytes == 0; }
 
 }  // namespace
+
+// y = log(1 + x) for a batch, one CTA per signature: the expanded tensor (lyndon == nullptr, count =
+// coefficients of the signature) or its Lyndon-word coordinates (lyndon[i]: scalar-free position of
+// coordinate i).  x / out address the first level-1 coefficient resp. the first output.  Returns false
+// with nothing launched for batches below the SM count, degree < 2 or levels below N beyond shared memory.
+template <typename T>
+bool launch_log_forward_streamed(const T* x, uint64_t x_stride, T* out, uint64_t out_stride, const uint32_t* lyndon,
+                                 uint32_t count, bool zero_scalar, uint64_t batch, uint64_t dim, uint64_t degree,
+                                 cudaStream_t stream) {
+    if (degree < 2 || degree > uint64_t(kMaxDegree) || dim < 1) return false;
+    const int sms = device_context(current_device()).sm_count;
+    if (batch < uint64_t(sms)) return false;
+    if (sig_length_full(dim, degree) >= (1ull << 31)) return false;
+    const LevelIndex lev = make_level_index(dim, degree);
+    const uint64_t low_len = (uint64_t(lev.li[degree]) + 3) & ~3ull;
+    const size_t smem = 3 * low_len * sizeof(T);
+    if (smem > 200 * 1024) return false;
+    const unsigned per_sm = static_cast<unsigned>(std::max<size_t>(1, std::min<size_t>(8, (220 * 1024) / (smem + 1024))));
+    const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(batch, uint64_t(sms) * per_sm));
+    if (smem > 48 * 1024)
+        SIG_CUDA_CHECK(cudaFuncSetAttribute(log_forward_cta_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    log_forward_cta_kernel<T><<<grid, kChenThreads, smem, stream>>>(x, x_stride, out, out_stride, lyndon, count, zero_scalar,
+                                                                    batch, static_cast<int>(degree),
+                                                                    static_cast<uint32_t>(dim), lev);
+    SIG_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+    return true;
+}
+
+template bool launch_log_forward_streamed<float>(const float*, uint64_t, float*, uint64_t, const uint32_t*, uint32_t, bool,
+                                                 uint64_t, uint64_t, uint64_t, cudaStream_t);
+template bool launch_log_forward_streamed<double>(const double*, uint64_t, double*, uint64_t, const uint32_t*, uint32_t, bool,
+                                                  uint64_t, uint64_t, uint64_t, cudaStream_t);
 
 // dLoss/d sig from dLoss/d log-signature for a batch, one CTA per signature.  x and dsig address first
 // level-1 coefficients; g is the gradient in expanded layout (rank == nullptr, first level-1 coefficient)
@@ -181,7 +290,7 @@ template <typename T>
 bool launch_log_adjoint_streamed(const T* x, uint64_t x_stride, const T* g, uint64_t g_stride, const int32_t* rank,
                                  T* dsig, uint64_t dsig_stride, bool zero_scalar, uint64_t batch, uint64_t dim,
                                  uint64_t degree, cudaStream_t stream) {
-    if (degree < 2 || degree - 1 > uint64_t(kChenSplits) || dim < 2 || dim > uint64_t(kChenThreads) || (dim & (dim - 1)) != 0)
+    if (degree < 2 || degree - 1 > uint64_t(kChenSplits) || dim < 2 || dim > uint64_t(kAdjointThreads) || (dim & (dim - 1)) != 0)
         return false;
     const int sms = device_context(current_device()).sm_count;
     if (batch < uint64_t(sms)) return false;
@@ -200,7 +309,7 @@ bool launch_log_adjoint_streamed(const T* x, uint64_t x_stride, const T* g, uint
     };
     bool launched = false;
     auto run = [&](auto kernel, int vec) {
-        const uint64_t entries = regular_order_entries(lev, degree, kChenThreads, vec);
+        const uint64_t entries = regular_order_entries(lev, degree, kAdjointThreads, vec);
         const uint64_t small_len = (uint64_t(lev.li[degree >= 3 ? degree - 1 : 2]) + 6) & ~3ull;
         const size_t smem = (3 * low_len + small_len + r_total) * sizeof(T) + entries * sizeof(uint32_t);
         if (smem > 200 * 1024) return;
@@ -208,7 +317,7 @@ bool launch_log_adjoint_streamed(const T* x, uint64_t x_stride, const T* g, uint
         const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(batch, uint64_t(sms) * per_sm));
         if (smem > 48 * 1024)
             SIG_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        kernel<<<grid, kChenThreads, smem, stream>>>(x, x_stride, g, g_stride, rank, dsig, dsig_stride, zero_scalar, batch,
+        kernel<<<grid, kAdjointThreads, smem, stream>>>(x, x_stride, g, g_stride, rank, dsig, dsig_stride, zero_scalar, batch,
                                                      static_cast<int>(degree), static_cast<uint32_t>(dim), lgd, lev);
         SIG_CUDA_CHECK(cudaGetLastError());
         count_launch();

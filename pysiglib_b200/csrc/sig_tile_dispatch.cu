@@ -9,11 +9,10 @@
 #include <tuple>
 
 #include "sig_tile_launch.cuh"
-#ifdef SIG_TILE_DEV
-#include "tile_table_dev.h"  // development subset (quick builds)
-#else
-#include "tile_table.h"
+#ifndef SIG_TILE_TABLE
+#define SIG_TILE_TABLE "tile_table.h"  // -DSIG_TILE_TABLE='"other.h"': a table restricted to the shapes a deployment needs
 #endif
+#include SIG_TILE_TABLE
 
 namespace sigb200 {
 

@@ -1,11 +1,10 @@
 // One part of the register-tile kernel table (tile_table.h).  This file is compiled
 // SIG_TILE_PARTS times with -DSIG_TILE_PART=<k> so the variants build in parallel.
 #include "sig_tile_launch.cuh"
-#ifdef SIG_TILE_DEV
-#include "tile_table_dev.h"  // development subset (quick builds)
-#else
-#include "tile_table.h"
+#ifndef SIG_TILE_TABLE
+#define SIG_TILE_TABLE "tile_table.h"  // -DSIG_TILE_TABLE='"other.h"': a table restricted to the shapes a deployment needs
 #endif
+#include SIG_TILE_TABLE
 
 #ifndef SIG_TILE_PART
 #error "compile with -DSIG_TILE_PART=<k>"

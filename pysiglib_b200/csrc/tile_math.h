@@ -58,7 +58,7 @@ template <> SIG_HD double sig_fma<double>(double a, double b, double c) { return
 // one issue slot performs two operations, which relieves the issue pressure of these
 // FMA-bound kernels; every element still gets one correctly rounded FMA, so results are
 // identical to the scalar form.  Host builds and double use the scalar loops.
-#if defined(__CUDA_ARCH__) && !defined(SIG_NO_PACKED_F32)
+#if defined(__CUDA_ARCH__)
 #define SIG_PACKED_F32 1
 #else
 #define SIG_PACKED_F32 0

@@ -244,32 +244,51 @@ def test_fused_log_sweep_matches_the_two_step_route_and_the_oracle(case, dtype, 
     assert float((fused - two_step).abs().max()) <= (1e-11 if dtype == np.float64 else 3e-5) * max(scale_all, 1.0)
 
 
-# Batches of at least one signature per SM and power-of-two dimensions take the one-kernel backward
-# (sig_log_stream.cu): partial levels, several iterations per level, register sums that are flushed
-# mid-level, every vector width (the scalar term shifts the alignment), every method.
+# Batches of at least one signature per SM take the one-CTA-per-signature kernels of sig_log_stream.cu:
+# the forward for any dimension, the backward for power-of-two dimensions (partial levels, several
+# iterations per level, register sums that are flushed mid-level, every vector width - the scalar term
+# shifts the alignment - and every method).
 STREAMED_CASES = [(150, 2, 2), (150, 2, 6), (200, 2, 8), (150, 4, 3), (150, 4, 5), (150, 4, 6), (150, 8, 3), (150, 8, 4),
-                  (150, 16, 2), (150, 16, 3), (148, 16, 4), (150, 32, 2)]
+                  (150, 16, 2), (150, 16, 3), (148, 16, 4), (150, 32, 2), (150, 3, 4), (150, 5, 3), (160, 6, 3), (150, 1, 4)]
 
 
 @pytest.mark.parametrize("B,d,N", STREAMED_CASES)
 @pytest.mark.parametrize("dtype", [np.float64, np.float32])
 @pytest.mark.parametrize("scalar_term", [False, True])
 @pytest.mark.parametrize("method", [0, 1, 2])
-def test_streamed_log_backprop(B, d, N, dtype, scalar_term, method):
+def test_streamed_log_and_backprop(B, d, N, dtype, scalar_term, method):
     import pysiglib_b200
     from pysiglib_b200 import load_cusig
     if method == 2 and d ** N > 70000:
         pytest.skip("the basis change of this shape is slow to prepare on the host")
     s = _sigs(B + d + N, B, d, N, dtype, scalar_term)
     st = torch.tensor(s, device="cuda")
+    pysiglib_b200.prepare_log_sig(d, N, method)
+    off = 1 if scalar_term else 0
+
+    before = load_cusig.launch_count()
+    got = pysiglib_b200.sig_to_log_sig(st, d, N, method=method)
+    launches = load_cusig.launch_count() - before
+    assert launches == (2 if method == 2 else 1), "expected the one-kernel forward, saw %d launches" % launches
+    want = oracle.sig_to_log_sig(s.astype(np.float64) if method == 2 else s, d, N, method=method)
+    rtol = 1e-10 if dtype == np.float64 else 1e-5
+    if method == 0:
+        _assert_log_close(got.cpu().numpy()[:, off:], want[:, off:], s[:, off:], d, N, rtol)
+        if scalar_term:
+            assert torch.all(got[:, 0] == 0)
+    else:
+        scale = np.maximum(np.abs(want).max(axis=1, keepdims=True),
+                           np.abs(s[:, off:off + d]).max(axis=1, keepdims=True).astype(np.float64) ** N / N)
+        assert (np.abs(got.cpu().numpy() - want) / scale).max() <= (1e-9 if dtype == np.float64 else 3e-5)
+
     M = s.shape[1] if method == 0 else pysiglib_b200.log_sig_length(d, N)
     w = np.random.default_rng(2).standard_normal((B, M)).astype(dtype)
-    pysiglib_b200.prepare_log_sig(d, N, method)
     want_g = oracle.sig_to_log_sig_backprop(s.astype(np.float64), w.astype(np.float64), d, N, method=method)
     before = load_cusig.launch_count()
     got_g = pysiglib_b200.sig_to_log_sig_backprop(st, torch.tensor(w, device="cuda"), d, N, method=method)
     launches = load_cusig.launch_count() - before
-    assert launches <= 2, "expected the one-kernel backward (plus the basis pull-back for method 2), saw %d launches" % launches
+    if d & (d - 1) == 0 and d >= 2:
+        assert launches <= 2, "expected the one-kernel backward (plus the basis pull-back for method 2), saw %d launches" % launches
     assert_grad_close(got_g.cpu().numpy()[:, None, :], want_g[:, None, :], 1e-10 if dtype == np.float64 else 1e-4)
     if scalar_term:
         assert not got_g[:, 0].any()
