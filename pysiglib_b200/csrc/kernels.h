@@ -81,6 +81,11 @@ uint64_t chen_combine_tmp_elems(const SigShape& s, int nseg);
 template <typename T>
 void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int nseg, cudaStream_t stream);
 
+// The same join in one launch, one CTA per path with the running product in shared memory
+// (sig_chen.cu); false, with nothing launched, when a signature does not fit there.
+template <typename T>
+bool launch_chen_chain(T* out, const T* seg, const SigShape& s, int nseg, cudaStream_t stream);
+
 // C = A (x) B with one CTA per signature (sig_chen.cu): the levels below N of both factors in shared
 // memory, the top level streamed with vector loads and stores.  A or B may be nullptr: that factor is
 // then exp(disp[b]), the signature of the straight segment with displacement disp[b] (dimension values

@@ -346,26 +346,67 @@ CorrectionArgs<T> make_args(const CorrectionView<T>& c, uint64_t data_dim) {
 
 // ----- path transform --------------------------------------------------------------------------
 
-// One thread per element of one transformed path, paths along grid.y; a path holds fewer than 2^32 values.
-template <typename T>
-__global__ void transform_path_kernel(const T* __restrict__ in, T* __restrict__ out, uint64_t batch, uint32_t d,
+// The transformed batch as one flat array: a thread takes VEC consecutive output values (they may
+// run over the end of a point or of a path: the (path, point, channel) position is decoded once by
+// division and then advanced with carries), gathers them and stores them with one vector store.  A
+// path holds fewer than 2^32 values; `out` is aligned to VEC values.
+template <typename T, int VEC>
+__global__ void transform_path_kernel(const T* __restrict__ in, T* __restrict__ out, uint64_t total, uint32_t d,
                                       uint32_t L, uint32_t dim, uint32_t len, bool time_aug, bool lead_lag, T dt) {
-    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= len * dim) return;
-    const uint32_t p = r / dim, ch = r - p * dim;
-    const bool is_time = time_aug && ch == dim - 1;
-    uint32_t src = 0;
-    if (!is_time) {
-        if (lead_lag) {
-            const uint32_t m = p >> 1, odd = p & 1;
-            src = ch < d ? m * d + ch : (m + odd) * d + (ch - d);
+    const uint32_t per = len * dim;
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x * VEC;
+    // (path, offset in the path) of the first value: one 64-bit division, then advanced by the
+    // (constant) grid stride with a carry
+    const uint64_t stride_b = stride / per;
+    const uint32_t stride_r = static_cast<uint32_t>(stride - stride_b * per);
+    uint64_t e0 = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
+    uint64_t b0 = e0 / per;
+    uint32_t r0 = static_cast<uint32_t>(e0 - b0 * per);
+    for (; e0 < total; e0 += stride, b0 += stride_b, r0 += stride_r) {
+        if (r0 >= per) {
+            r0 -= per;
+            ++b0;
+        }
+        uint32_t p = r0 / dim, ch = r0 - p * dim;
+        const T* path = in + b0 * (uint64_t(L) * d);
+        const uint32_t copied = lead_lag ? 2 * d : d;      // channels taken from the path; the rest is time
+        // channel ch of point p reads path[lead + ch] (ch < d) or path[lag + ch] (d <= ch < 2d, lead-lag)
+        uint32_t lead = lead_lag ? (p >> 1) * d : p * d;
+        uint32_t lag = lead_lag ? ((p >> 1) + (p & 1)) * d - d : 0;
+        T v[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            v[k] = T(0);
+            if (e0 + k < total) {
+                if (ch >= copied) v[k] = static_cast<T>(p) * dt;
+                else v[k] = path[(ch < d ? lead : lag) + ch];
+                if (++ch == dim) {
+                    ch = 0;
+                    if (++p == len) {
+                        p = 0;
+                        path += uint64_t(L) * d;
+                    }
+                    lead = lead_lag ? (p >> 1) * d : p * d;
+                    lag = lead_lag ? ((p >> 1) + (p & 1)) * d - d : 0;
+                }
+            }
+        }
+        if (e0 + VEC <= total) {
+            if constexpr (VEC == 4) {
+                if constexpr (sizeof(T) == 4) *reinterpret_cast<float4*>(out + e0) = make_float4(v[0], v[1], v[2], v[3]);
+                else {
+                    *reinterpret_cast<double2*>(out + e0) = make_double2(v[0], v[1]);
+                    *reinterpret_cast<double2*>(out + e0 + 2) = make_double2(v[2], v[3]);
+                }
+            } else {
+                out[e0] = v[0];
+            }
         } else {
-            src = p * d + ch;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k)
+                if (e0 + k < total) out[e0 + k] = v[k];
         }
     }
-    const T time = static_cast<T>(p) * dt;
-    for (uint64_t b = blockIdx.y; b < batch; b += gridDim.y)
-        out[b * len * dim + r] = is_time ? time : in[b * L * d + src];
 }
 
 template <typename T>
@@ -571,9 +612,17 @@ void transform_path_entry(const T* data_in, T* data_out, uint64_t batch, uint64_
     const uint64_t n_out = checked_mul(checked_mul(batch, s.len, "transformed path"), s.dim, "transformed path");
     if (s.len * s.dim >= (1ull << 32)) throw std::invalid_argument("transform_path_cuda: path too large");
     auto run = [&](const T* in, T* o, cudaStream_t st) {
-        const dim3 grid = batched_grid(s.len * s.dim, batch, kThreads);
-        transform_path_kernel<T><<<grid, kThreads, 0, st>>>(in, o, batch, uint32_t(dimension), uint32_t(length),
-                                                            uint32_t(s.dim), uint32_t(s.len), time_aug, lead_lag, dt);
+        const uint64_t total = n_out;
+        const bool wide = reinterpret_cast<uintptr_t>(o) % (4 * sizeof(T)) == 0;
+        const uint64_t threads = (total + (wide ? 3 : 0)) / (wide ? 4 : 1);
+        const int sms = device_context(current_device()).sm_count;
+        const unsigned grid = static_cast<unsigned>(std::min<uint64_t>((threads + kThreads - 1) / kThreads, uint64_t(sms) * 32));
+        if (wide)
+            transform_path_kernel<T, 4><<<grid, kThreads, 0, st>>>(in, o, total, uint32_t(dimension), uint32_t(length),
+                                                                   uint32_t(s.dim), uint32_t(s.len), time_aug, lead_lag, dt);
+        else
+            transform_path_kernel<T, 1><<<grid, kThreads, 0, st>>>(in, o, total, uint32_t(dimension), uint32_t(length),
+                                                                   uint32_t(s.dim), uint32_t(s.len), time_aug, lead_lag, dt);
         check_launch("transform_path kernel");
     };
     int device = -1;

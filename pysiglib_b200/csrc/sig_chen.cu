@@ -16,6 +16,8 @@
 // sig_generic.cu (kept for small batches and for signatures whose lower levels do not fit shared
 // memory); same sums, same order over the splits (siglib/cpsig/cp_sig_combine.h:34-66 is the
 // reference arithmetic, siglib/cusig/cu_sig_combine.cu:35-340 the reference kernels).
+#include <cuda_pipeline.h>
+
 #include <algorithm>
 #include <type_traits>
 
@@ -153,6 +155,96 @@ void launch_product(const T* A, uint64_t a_stride, const T* B, uint64_t b_stride
         static_cast<uint32_t>(s.dim), make_level_index(s.dim, s.degree));
     SIG_CUDA_CHECK(cudaGetLastError());
     count_launch();
+}
+
+// Joins the consecutive segment signatures of every path in one launch: one CTA per path keeps the
+// running product S in shared memory (levels below N twice, for the in-place update, and the whole top
+// level), and multiplies one segment after the other onto it from the right:
+//     S_N[w] += B_N[w] + sum_i S_i[prefix] B_{N-i}[suffix]   (every thread owns its words; reads only levels < N),
+//     then S_m for m < N into the second buffer, from the old lower levels.
+// seg: (batch, nseg, slen) scalar-free.  A segment comes in with asynchronous copies straight into
+// shared memory, all of them in flight together (the kernel serves small batches: it is bound by the
+// latency of those loads, not by their volume); the result is written once.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kChenThreads)
+chen_chain_cta_kernel(const T* __restrict__ seg, int nseg, T* __restrict__ out, uint64_t out_stride, bool out_scalar,
+                      uint64_t batch, int N, uint32_t d, LevelIndex lev) {
+    extern __shared__ __align__(16) unsigned char chen_smem[];
+    __shared__ uint32_t li[kMaxDegree + 2];
+    const uint32_t tid = threadIdx.x, nt = blockDim.x;
+    for (uint32_t i = tid; i < uint32_t(N + 2); i += nt) li[i] = lev.li[i];
+    __syncthreads();
+    const uint32_t low_len = (li[N] + 6) & ~3u;
+    const uint32_t top = li[N + 1] - li[N], low_count = li[N] - 1, slen = li[N + 1] - 1;
+    const uint32_t top_len = (top + 3) & ~3u;
+    T* s_top = reinterpret_cast<T*>(chen_smem);            // top level of the running product
+    T* b_top = s_top + top_len;                            // top level of the segment being multiplied on
+    T* s_low = b_top + top_len + (VEC - 1);                // levels below N, every level on a vector boundary
+    T* s_new = s_low + low_len;
+    T* b_low = s_new + low_len;
+    using P = typename Pack<T, VEC>::type;
+    auto fetch = [&](const T* src, T* low, T* top_dst) {   // one segment, every copy in flight at once
+        for (uint32_t j = tid; j < low_count; j += nt) __pipeline_memcpy_async(low + 1 + j, src + j, sizeof(T));
+        for (uint32_t idx = tid * VEC; idx < top; idx += nt * VEC)
+            __pipeline_memcpy_async(top_dst + idx, src + low_count + idx, VEC * sizeof(T));
+        __pipeline_commit();
+    };
+
+    for (uint64_t b = blockIdx.x; b < batch; b += gridDim.x) {
+        __syncthreads();
+        const T* first = seg + b * uint64_t(nseg) * slen;
+        if (tid == 0) s_low[0] = s_new[0] = b_low[0] = T(1);
+        fetch(first, s_low, s_top);
+        for (int k = 1; k < nseg; ++k) {
+            __syncthreads();                               // the previous round is done with b_low / b_top
+            fetch(first + uint64_t(k) * slen, b_low, b_top);
+            __pipeline_wait_prior(0);
+            __syncthreads();
+            for (uint32_t idx = tid * VEC; idx < top; idx += nt * VEC) {
+                T acc[VEC], bt[VEC];
+                unpack(*reinterpret_cast<const P*>(s_top + idx), acc);
+                unpack(*reinterpret_cast<const P*>(b_top + idx), bt);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) acc[v] += bt[v];
+                uint32_t left = idx, pw = 1;
+                for (int i = N - 1; i >= 1; --i) {
+                    left /= d;
+                    pw *= d;
+                    const T al = s_low[li[i] + left];
+                    T br[VEC];
+                    unpack(*reinterpret_cast<const P*>(b_low + li[N - i] + (idx - left * pw)), br);
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) acc[v] = chen_fma(al, br[v], acc[v]);
+                }
+                *reinterpret_cast<P*>(s_top + idx) = make_pack(acc);
+            }
+            for (uint32_t pos = 1 + tid; pos < li[N]; pos += nt) {
+                int m = 1;
+                while (pos >= li[m + 1]) ++m;
+                const uint32_t idx = pos - li[m];
+                T acc = s_low[pos] + b_low[pos];
+                uint32_t left = idx, pw = 1;
+                for (int i = m - 1; i >= 1; --i) {
+                    left /= d;
+                    pw *= d;
+                    acc = chen_fma(s_low[li[i] + left], b_low[li[m - i] + idx - left * pw], acc);
+                }
+                s_new[pos] = acc;
+            }
+            T* swap = s_low;
+            s_low = s_new;
+            s_new = swap;
+        }
+        __pipeline_wait_prior(0);
+        __syncthreads();
+        T* o = out + b * out_stride;
+        if (out_scalar) {
+            if (tid == 0) o[0] = T(1);
+            ++o;
+        }
+        for (uint32_t j = tid; j < low_count; j += nt) o[j] = s_low[1 + j];
+        for (uint32_t idx = tid; idx < top; idx += nt) o[low_count + idx] = s_top[idx];
+    }
 }
 
 // Both adjoints of C = A (x) B in one pass over dC (the backward of sig_combine and of sig_join):
@@ -413,6 +505,42 @@ bool launch_chen_product_streamed(const T* A, uint64_t a_stride, const T* B, uin
     else launch_product<T, 1>(A, a_stride, B, b_stride, disp, C, c_stride, write_scalar, s, smem, grid, stream);
     return true;
 }
+
+// out[b] = seg[b][0] (x) .. (x) seg[b][nseg-1] in one launch, one CTA per path (any batch size: the
+// caller is the time-segmented sweep of a small batch).  Returns false with nothing launched when the
+// running product does not fit shared memory.
+template <typename T>
+bool launch_chen_chain(T* out, const T* seg, const SigShape& s, int nseg, cudaStream_t stream) {
+    if (nseg < 2 || s.batch == 0 || s.degree < 2 || s.degree > uint64_t(kMaxDegree) || s.dim < 2 ||
+        s.full_len >= (1ull << 31))
+        return false;
+    const LevelIndex lev = make_level_index(s.dim, s.degree);
+    const uint64_t low_len = (uint64_t(lev.li[s.degree]) + 6) & ~3ull;
+    const uint64_t top = uint64_t(lev.li[s.degree + 1]) - lev.li[s.degree];
+    const size_t smem = (2 * ((top + 3) & ~3ull) + 3 * low_len + 4) * sizeof(T);
+    if (smem > 200 * 1024) return false;
+    const int sms = device_context(current_device()).sm_count;
+    const unsigned per_sm = static_cast<unsigned>(std::max<size_t>(1, std::min<size_t>(8, (220 * 1024) / (smem + 1024))));
+    const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(s.batch, uint64_t(sms) * per_sm));
+    const uint64_t slen = s.full_len - 1;
+    auto run = [&](auto kernel) {
+        if (smem > 48 * 1024)
+            SIG_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        kernel<<<grid, kChenThreads, smem, stream>>>(seg, nseg, out, s.stride, s.scalar_term, s.batch,
+                                                     static_cast<int>(s.degree), static_cast<uint32_t>(s.dim), lev);
+        SIG_CUDA_CHECK(cudaGetLastError());
+        count_launch();
+    };
+    constexpr int kWide = sizeof(T) == 4 ? 4 : 2;
+    auto fits = [&](int vec) { return s.dim % vec == 0 && aligned_to(seg, vec * sizeof(T)) && slen % vec == 0; };
+    if (fits(kWide)) run(chen_chain_cta_kernel<T, kWide>);
+    else if (fits(2)) run(chen_chain_cta_kernel<T, 2>);
+    else run(chen_chain_cta_kernel<T, 1>);
+    return true;
+}
+
+template bool launch_chen_chain<float>(float*, const float*, const SigShape&, int, cudaStream_t);
+template bool launch_chen_chain<double>(double*, const double*, const SigShape&, int, cudaStream_t);
 
 // dA and dB of C = A (x) B from dC in one launch, one CTA per signature.  Same contract as above:
 // false means nothing was launched.  The scalar slots (if the caller's layout has them) are not touched.

@@ -451,20 +451,22 @@ chen_right_adjoint_kernel(const T* __restrict__ dS, uint64_t ds_stride, const T*
     (dY + b * dy_stride - 1)[pos] = acc;
 }
 
+// Gradient with respect to the points from the gradient with respect to the increments
+// z_t = x_{t+1} - x_t:  dx_t = dz_{t-1} - dz_t.  Inside one path the flat index i = t * d + c of a
+// point coordinate is also the index of dz_t[c], so dx[i] = dz[i - d] - dz[i] with the two ends cut
+// off: no division.  Paths along grid.y.
 template <typename T>
-__global__ void increment_to_point_grad_kernel(const T* __restrict__ g, T* __restrict__ out, uint64_t total,
-                                               uint32_t L, uint32_t d) {
-    const uint64_t idx = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const uint64_t row = idx / d;  // b * L + t
-    const uint32_t c = static_cast<uint32_t>(idx - row * d);
-    const uint64_t b = row / L;
-    const uint32_t t = static_cast<uint32_t>(row - b * L);
-    const T* gb = g + b * uint64_t(L - 1) * d;
-    T v = T(0);
-    if (t > 0) v += gb[uint64_t(t - 1) * d + c];
-    if (t + 1 < L) v -= gb[uint64_t(t) * d + c];
-    out[idx] = v;
+__global__ void increment_to_point_grad_kernel(const T* __restrict__ g, T* __restrict__ out, uint64_t batch,
+                                               uint64_t per_path, uint64_t per_path_incr, uint32_t d) {
+    const uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= per_path) return;
+    for (uint64_t b = blockIdx.y; b < batch; b += gridDim.y) {
+        const T* gb = g + b * per_path_incr;
+        T v = T(0);
+        if (i >= d) v = gb[i - d];
+        if (i < per_path_incr) v -= gb[i];
+        out[b * per_path + i] = v;
+    }
 }
 
 template <typename T>
@@ -610,6 +612,7 @@ template <typename T>
 void launch_chen_combine(T* out, const T* seg, T* tmp, const SigShape& s, int nseg, cudaStream_t stream) {
     if (nseg <= 1 || s.batch == 0) return;
     check_generic_limits(s);
+    if (launch_chen_chain<T>(out, seg, s, nseg, stream)) return;   // one launch, running product in shared memory
     const uint32_t slen = static_cast<uint32_t>(s.full_len - 1);
     const LevelIndex lev = make_level_index(s.dim, s.degree);
     T* buf[2] = {tmp, tmp + s.batch * slen * uint64_t((nseg + 1) / 2)};
@@ -681,8 +684,10 @@ void launch_increment_to_point_grad(const T* incr_grad, T* out, uint64_t batch, 
                                     cudaStream_t stream) {
     const uint64_t total = checked_mul(batch, checked_mul(L, d, "path gradient"), "path gradient");
     if (total == 0) return;
-    increment_to_point_grad_kernel<T><<<grid_1d(total, 256), 256, 0, stream>>>(
-        incr_grad, out, total, static_cast<uint32_t>(L), static_cast<uint32_t>(d));
+    const uint64_t per_path = L * d;
+    const dim3 grid(grid_1d(per_path, 256), static_cast<unsigned>(std::min<uint64_t>(batch, 65535)));
+    increment_to_point_grad_kernel<T><<<grid, 256, 0, stream>>>(incr_grad, out, batch, per_path, (L - 1) * d,
+                                                                static_cast<uint32_t>(d));
     SIG_CUDA_CHECK(cudaGetLastError());
     count_launch();
 }
