@@ -84,22 +84,45 @@ void run_host_pipeline(uint64_t batch, const std::vector<HostOperand>& inputs, v
     uint64_t per_path = out_bytes_per_path;
     for (const auto& in : inputs) per_path += in.bytes_per_path;
     per_path = std::max<uint64_t>(per_path, 1);
-    // The first chunk's copy-in and the last chunk's copy-out are not hidden behind any kernel,
-    // so chunks are kept small: about 16 MiB of staged operands, at most 32 chunks, none above 2 GiB.
+    // The first chunk's copy-in and the last chunk's copy-out are not hidden behind any kernel, and every
+    // chunk boundary drains the GPU once (the kernels of the next chunk start when the last CTA of this
+    // one is done).  So the chunks ramp: one unit first, then 2, 4, ... up to 16 units in the middle, and
+    // down again at the end; a unit is about 8 MiB of staged operands, rounded to whole waves of the
+    // kernels compute() launches, and no chunk exceeds 2 GiB.
     const uint64_t total_bytes = per_path * batch;
-    const uint64_t n_target = std::min<uint64_t>(32, std::max<uint64_t>(1, total_bytes / (16ull << 20)));
-    uint64_t chunk = (batch + n_target - 1) / n_target;
-    if (wave_paths > 0 && n_target > 1) chunk = std::max<uint64_t>(1, (chunk + wave_paths / 2) / wave_paths) * wave_paths;
-    chunk = std::min<uint64_t>(chunk, std::max<uint64_t>(1, (2ull << 30) / per_path));
-    chunk = std::max<uint64_t>(std::min(chunk, batch), 1);
+    const uint64_t n_target = std::min<uint64_t>(64, std::max<uint64_t>(1, total_bytes / (8ull << 20)));
+    uint64_t unit = (batch + n_target - 1) / n_target;
+    if (wave_paths > 0 && n_target > 1) unit = std::max<uint64_t>(1, (unit + wave_paths / 2) / wave_paths) * wave_paths;
+    unit = std::min<uint64_t>(unit, std::max<uint64_t>(1, (2ull << 30) / per_path));
+    unit = std::max<uint64_t>(std::min(unit, batch), 1);
+    const uint64_t cap = std::max<uint64_t>(unit, std::min<uint64_t>(16 * unit, std::max<uint64_t>(1, (2ull << 30) / per_path)));
 
-    // staging slots: kept between calls, grown on demand; on out-of-memory the chunk is halved
+    // staging slots: kept between calls, grown on demand; on out-of-memory the largest chunk is halved
+    uint64_t chunk = cap;                                  // largest chunk = capacity of a slot, in paths
+    std::vector<uint64_t> sizes;
     uint64_t slot_bytes = 0;
     int n_buf = 1;
     for (;;) {
+        // up-ramp from the front, down-ramp from the back, the middle in chunks of `chunk`
+        sizes.clear();
+        std::vector<uint64_t> tail;
+        uint64_t left = batch, step = std::min(unit, chunk);
+        while (left > 0) {
+            const uint64_t front = std::min(step, left);
+            sizes.push_back(front);
+            left -= front;
+            if (left == 0) break;
+            if (step < chunk) {
+                const uint64_t back = std::min(step, left);
+                tail.push_back(back);
+                left -= back;
+                step = std::min(2 * step, chunk);
+            }
+        }
+        sizes.insert(sizes.end(), tail.rbegin(), tail.rend());
         slot_bytes = aligned(std::max<uint64_t>(out_bytes_per_path * chunk, 16));
         for (const auto& in : inputs) slot_bytes += aligned(std::max<uint64_t>(in.bytes_per_path * chunk, 16));
-        n_buf = (batch + chunk - 1) / chunk > 1 ? 2 : 1;
+        n_buf = sizes.size() > 1 ? 2 : 1;
         try {
             reserve_staging(ctx, slot_bytes, n_buf);
             break;
@@ -108,7 +131,7 @@ void run_host_pipeline(uint64_t batch, const std::vector<HostOperand>& inputs, v
             chunk = (chunk + 1) / 2;
         }
     }
-    const uint64_t n_chunks = (batch + chunk - 1) / chunk;
+    const uint64_t n_chunks = sizes.size();
 
     auto drain = [&]() {
         (void)cudaStreamSynchronize(ctx.copy_in);
@@ -120,10 +143,10 @@ void run_host_pipeline(uint64_t batch, const std::vector<HostOperand>& inputs, v
         SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_in, ctx.ready, 0));
         SIG_CUDA_CHECK(cudaStreamWaitEvent(ctx.copy_out, ctx.ready, 0));
         std::vector<void*> din(inputs.size());
-        for (uint64_t c = 0; c < n_chunks; ++c) {
+        uint64_t begin = 0;
+        for (uint64_t c = 0; c < n_chunks; begin += sizes[c], ++c) {
             StagingSlot& sl = ctx.slots[c % n_buf];
-            const uint64_t begin = c * chunk;
-            const uint64_t count = std::min(chunk, batch - begin);
+            const uint64_t count = sizes[c];
             unsigned char* cursor = static_cast<unsigned char*>(sl.buffer);
             void* dout = cursor;
             cursor += aligned(std::max<uint64_t>(out_bytes_per_path * chunk, 16));

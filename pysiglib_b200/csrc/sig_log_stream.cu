@@ -177,7 +177,7 @@ template <typename T>
 __global__ void __launch_bounds__(kChenThreads)
 log_forward_cta_kernel(const T* __restrict__ x, uint64_t x_stride, T* __restrict__ out, uint64_t out_stride,
                        const uint32_t* __restrict__ lyndon, uint32_t count, bool zero_scalar, uint64_t batch, int N,
-                       uint32_t d, LevelIndex lev) {
+                       uint32_t d, int lgd, LevelIndex lev) {
     extern __shared__ __align__(16) unsigned char log_smem[];
     __shared__ uint32_t li[kMaxDegree + 2];
     __shared__ uint32_t pw[kMaxDegree + 2];        // d^k
@@ -235,9 +235,16 @@ log_forward_cta_kernel(const T* __restrict__ x, uint64_t x_stride, T* __restrict
             const uint32_t idx = p + 1 - li[t];
             T value = xb[p];
             // y = x - x (x) R_2 = x - (-x) (x) (-R_2)
-            for (uint32_t s = t - 1; s >= 1; --s) {
-                const uint32_t left = idx / pw[t - s];
-                value = chen_fma(-nx[li[s] + left], nr2[li[t - s] + idx - left * pw[t - s]], value);
+            if (lgd >= 0) {                          // power-of-two dimension: shifts instead of divisions
+                for (uint32_t s = t - 1; s >= 1; --s) {
+                    const uint32_t sh = (t - s) * uint32_t(lgd);
+                    value = chen_fma(-nx[li[s] + (idx >> sh)], nr2[li[t - s] + (idx & ((1u << sh) - 1u))], value);
+                }
+            } else {
+                for (uint32_t s = t - 1; s >= 1; --s) {
+                    const uint32_t left = idx / pw[t - s];
+                    value = chen_fma(-nx[li[s] + left], nr2[li[t - s] + idx - left * pw[t - s]], value);
+                }
             }
             ob[i] = value;
         }
@@ -268,9 +275,14 @@ bool launch_log_forward_streamed(const T* x, uint64_t x_stride, T* out, uint64_t
     const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(batch, uint64_t(sms) * per_sm));
     if (smem > 48 * 1024)
         SIG_CUDA_CHECK(cudaFuncSetAttribute(log_forward_cta_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    int lgd = -1;
+    if ((dim & (dim - 1)) == 0 && dim >= 2) {
+        lgd = 0;
+        while ((1ull << lgd) < dim) ++lgd;
+    }
     log_forward_cta_kernel<T><<<grid, kChenThreads, smem, stream>>>(x, x_stride, out, out_stride, lyndon, count, zero_scalar,
                                                                     batch, static_cast<int>(degree),
-                                                                    static_cast<uint32_t>(dim), lev);
+                                                                    static_cast<uint32_t>(dim), lgd, lev);
     SIG_CUDA_CHECK(cudaGetLastError());
     count_launch();
     return true;
