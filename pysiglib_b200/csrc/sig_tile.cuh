@@ -23,6 +23,7 @@
 #pragma once
 
 #include <cooperative_groups.h>
+#include <cuda_pipeline.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -402,7 +403,8 @@ struct BackwardSmem {
     static constexpr int RS = DP2 >= 32 ? 1 : 32 / DP2;      // steps per reduction group
     static constexpr int ROWP = DP2 + (DP2 >= 4 ? 4 : 1);    // padded row: conflict-free stores
     static constexpr int SLAB = 32 * ROWP + 16;              // one step; +16 words de-phases the banks
-    static constexpr int PER_WARP = kTileChunk * (DP + D) + RS * SLAB;
+    static constexpr int RAW = ((kTileChunk + 1) * D + 3) / 4 * 4;   // points of the next chunk, copied in asynchronously
+    static constexpr int PER_WARP = kTileChunk * (DP + D) + RS * SLAB + RAW;
 };
 
 // Resident CTAs per SM the backward kernel is compiled for: shallow float tiles of up to 68 values fit
@@ -428,6 +430,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * Lay::PER_WARP;
     T* gbuf = zs + kTileChunk * DP;
     T* tbuf = gbuf + kTileChunk * D;
+    T* raw = tbuf + RS * SLAB;
 
     const int nseg = segs.nseg;
     const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
@@ -465,8 +468,8 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
         for (int i = 0; i < Sh::TS; ++i) ad.a[i] = T(0);
     }
 
-    // Warp-wide sum of one step's per-unit gradients into gbuf[step][letter] (zeroed at the
-    // start of the chunk).
+    // Warp-wide sum of one step's per-unit gradients into gbuf[step][letter] (every entry of the
+    // chunk is written exactly once, by the lane that sums its column).
     auto reduce_step = [&](T (&v)[DP2], const T* gg, const T* gc, int step, int cnt) {
         // (1) letters with static indices:
         // every lane parks its vector in its own row of tbuf; once the RS steps of a group are
@@ -526,7 +529,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
                         a2 += col[(r + 2) * ROWP];
                         a3 += col[(r + 3) * ROWP];
                     }
-                    atomicAdd(gbuf + (step + sl) * D + c, (a0 + a1) + (a2 + a3));
+                    gbuf[(step + sl) * D + c] = (a0 + a1) + (a2 + a3);   // the only writer of this (step, letter)
                 }
             } else {
 #pragma unroll
@@ -540,7 +543,7 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
                             a0 += col[(r + 0) * ROWP];
                             a1 += col[(r + 1) * ROWP];
                         }
-                        atomicAdd(gbuf + step * D + c, a0 + a1);
+                        gbuf[step * D + c] = a0 + a1;
                     }
                 }
             }
@@ -552,12 +555,37 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     // both were measured on B200 and cost a resident CTA per SM, 233 -> 293 ms on the C5 shape.)
     StepOperands<T, Sh> op;
     ChunkRegs<T, Sh> pre;
+    // Plain paths: the points of a chunk come into shared memory with asynchronous copies issued one
+    // chunk ahead (no registers held across the steps), so the global-memory latency of a chunk lies
+    // under the arithmetic of the chunk before it; the increments are then differences of shared values.
+    auto fetch_points = [&](int from, int count) {         // points from .. from + count
+        const T* src = x + size_t(from) * D;
+        for (int i = lane; i < (count + 1) * D; i += 32) __pipeline_memcpy_async(raw + i, src + i, sizeof(T));
+        __pipeline_commit();
+    };
+    if constexpr (!FLAGS) {
+        const int first = max(j_begin, j_end - kTileChunk);
+        if (j_end > j_begin) fetch_points(first, j_end - first);
+    }
     for (int j1 = j_end; j1 > j_begin;) {
         const int j0 = max(j_begin, j1 - kTileChunk);
         const int cnt = j1 - j0;
         __syncwarp();
-        commit_increments<T, Sh, FLAGS, false>(zs, pre, pv, x, j0, cnt, lane);
-        for (int i = lane; i < cnt * D; i += 32) gbuf[i] = T(0);
+        if constexpr (FLAGS) {
+            commit_increments<T, Sh, FLAGS, false>(zs, pre, pv, x, j0, cnt, lane);
+        } else {
+            __pipeline_wait_prior(0);
+            __syncwarp();
+            for (int i = lane; i < cnt * D; i += 32) {
+                const int step = i / D, c = i - step * D;
+                zs[step * DP + c] = raw[i + D] - raw[i];
+            }
+            __syncwarp();
+            if (j0 > j_begin) {
+                const int next = max(j_begin, j0 - kTileChunk);
+                fetch_points(next, j0 - next);
+            }
+        }
         __syncwarp();
         for (int step = cnt - 1; step >= 0; --step) {
             load_step<T, Sh, false>(op, zs + step * DP, ix);
