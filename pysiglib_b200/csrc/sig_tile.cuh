@@ -163,26 +163,85 @@ __device__ __forceinline__ void commit_increments(T* zs, const ChunkRegs<T, Sh>&
     }
 }
 
-// Forward sweep of one unit over the steps [j_begin, j_end) of the path starting at x; zs is the
-// warp's slice of shared memory.  The state is (re)initialised by the first step.
+// The raw points that the steps [j0, j0 + cnt) of a chunk need, staged in shared memory by asynchronous
+// copies (fetch) and turned into the chunk's increments once they have arrived (commit).  With lead-lag
+// the steps 2m, 2m + 1 both use the points m, m + 1; the time channel needs no data.
+template <typename T, bool FLAGS>
+struct ChunkPoints {
+    const PathView<T>& pv;
+    const T* x;
+    T* raw;
+    int lane;
+    __device__ __forceinline__ int first_point(int j0) const { return FLAGS && pv.lead_lag ? j0 >> 1 : j0; }
+    __device__ __forceinline__ void fetch(int j0, int cnt) const {
+        const int from = first_point(j0);
+        const int to = (FLAGS && pv.lead_lag ? (j0 + cnt - 1) >> 1 : j0 + cnt - 1) + 1;   // last point used
+        const T* src = x + size_t(from) * pv.d;
+        const int total = (to - from + 1) * pv.d;
+        for (int i = lane; i < total; i += 32) __pipeline_memcpy_async(raw + i, src + i, sizeof(T));
+        __pipeline_commit();
+    }
+    template <int D, int DP>
+    __device__ __forceinline__ void commit(T* zs, int j0, int cnt) const {
+        if constexpr (FLAGS) {
+            // the generic increment formula, reading the staged points through a shifted base pointer
+            const T* shifted = raw - size_t(first_point(j0)) * pv.d;
+            for (int i = lane; i < cnt * D; i += 32) {
+                const int step = i / D, c = i - step * D;
+                zs[step * DP + c] = pv.increment(shifted, j0 + step, c);
+            }
+        } else {
+            for (int i = lane; i < cnt * D; i += 32) {
+                const int step = i / D, c = i - step * D;
+                zs[step * DP + c] = raw[i + D] - raw[i];
+            }
+        }
+    }
+};
+
+// Shared memory of one warp of the forward kernels: the increments of the current chunk and, for
+// plain paths, the points of the next one (copied in asynchronously while the current chunk is swept).
+template <typename T, int D>
+struct ForwardSmem {
+    static constexpr int DP = RowPad<T, D>::DP;
+    static constexpr int RAW = ((kTileChunk + 1) * D + 3) / 4 * 4;
+    static constexpr int PER_WARP = kTileChunk * DP + RAW;
+};
+
+// Forward sweep of one unit over the steps [j_begin, j_end) of the path starting at x; zs / raw are the
+// warp's slices of shared memory.  The state is (re)initialised by the first step.
 template <typename T, typename Sh, bool FLAGS>
 __device__ __forceinline__ void tile_sweep_forward(TileState<T, Sh>& st, const PathView<T>& pv, const T* x, int j_begin,
-                                                   int j_end, T* zs, const UnitIndex<Sh>& ix, int lane) {
-    constexpr int DP = RowPad<T, Sh::D>::DP;
+                                                   int j_end, T* zs, T* raw, const UnitIndex<Sh>& ix, int lane) {
+    constexpr int D = Sh::D;
+    constexpr int DP = RowPad<T, D>::DP;
     StepOperands<T, Sh> op;
-    // Register prefetch of the next chunk: pays in float32 (measured +4..9 % on B200); in
-    // float64 the extra registers cost more than the hidden latency gains.
-    constexpr bool EAGER = !FLAGS && sizeof(T) == 4;
     constexpr bool OPERAND_PREFETCH = sizeof(T) == 4 && Sh::TS + 2 * (Sh::D + Sh::G + Sh::P) <= 170;
+    // float32 plain paths keep the register prefetch of the next chunk (measured on B200 against the
+    // asynchronous copies: C5 forward 48.3 vs 49.4 ms, C3 0.898 vs 0.913 ms); float64 and the flagged
+    // paths, where those registers are not to be had, stage the points through shared memory
+    // (C1 0.504 -> 0.481 ms, C2 0.580 -> 0.567 ms).
+    constexpr bool EAGER = !FLAGS && sizeof(T) == 4;
     ChunkRegs<T, Sh> pre;
-    prefetch_increments<T, Sh, EAGER>(pre, x, j_begin, min(kTileChunk, j_end - j_begin), lane);
+    const ChunkPoints<T, FLAGS> points{pv, x, raw, lane};
+    if constexpr (EAGER) prefetch_increments<T, Sh, EAGER>(pre, x, j_begin, min(kTileChunk, j_end - j_begin), lane);
+    else if (j_end > j_begin) points.fetch(j_begin, min(kTileChunk, j_end - j_begin));
     for (int j0 = j_begin; j0 < j_end; j0 += kTileChunk) {
         const int cnt = min(kTileChunk, j_end - j0);
         __syncwarp();
-        commit_increments<T, Sh, FLAGS, EAGER>(zs, pre, pv, x, j0, cnt, lane);
+        if constexpr (EAGER) {
+            commit_increments<T, Sh, FLAGS, EAGER>(zs, pre, pv, x, j0, cnt, lane);
+            __syncwarp();
+            if (j0 + kTileChunk < j_end)
+                prefetch_increments<T, Sh, EAGER>(pre, x, j0 + kTileChunk, min(kTileChunk, j_end - j0 - kTileChunk), lane);
+        } else {
+            __pipeline_wait_prior(0);
+            __syncwarp();
+            points.template commit<D, DP>(zs, j0, cnt);
+            __syncwarp();
+            if (j0 + kTileChunk < j_end) points.fetch(j0 + kTileChunk, min(kTileChunk, j_end - j0 - kTileChunk));
+        }
         __syncwarp();
-        if (j0 + kTileChunk < j_end)
-            prefetch_increments<T, Sh, EAGER>(pre, x, j0 + kTileChunk, min(kTileChunk, j_end - j0 - kTileChunk), lane);
         int step = 0;
         if (j0 == j_begin) {
             load_step<T, Sh, false>(op, zs, ix);
@@ -233,7 +292,8 @@ tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out
     constexpr int WPP = (Sh::UNITS + 31) / 32;  // warps per (path, segment)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * DP;
+    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * ForwardSmem<T, Sh::D>::PER_WARP;
+    T* raw = zs + kTileChunk * DP;
 
     const uint64_t gw = uint64_t(blockIdx.x) * WPB + warp;
     if (gw >= batch * uint64_t(nseg) * WPP) return;
@@ -248,7 +308,7 @@ tile_forward_kernel(PathView<T> pv, T* __restrict__ out, T* __restrict__ seg_out
     const T* x = pv.base + b * pv.path_stride;
 
     TileState<T, Sh> st;
-    tile_sweep_forward<T, Sh, FLAGS>(st, pv, x, j_begin, j_end, zs, ix, lane);
+    tile_sweep_forward<T, Sh, FLAGS>(st, pv, x, j_begin, j_end, zs, raw, ix, lane);
     if (active) {
         if (nseg == 1) {
             T* S = out + b * stride - (scalar ? 0 : 1);
@@ -295,8 +355,9 @@ tile_forward_log_kernel(PathView<T> pv, T* __restrict__ out, uint64_t batch, uin
     constexpr int WPP = Lay::WPP, C = Lay::CTAS_PER_PATH, PPC = Lay::PATHS_PER_CTA, LOW = Lay::LOW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * kTileChunk * DP;
-    T* low_base = reinterpret_cast<T*>(smem_raw) + size_t(WPB) * kTileChunk * DP;
+    T* zs = reinterpret_cast<T*>(smem_raw) + size_t(warp) * ForwardSmem<T, Sh::D>::PER_WARP;
+    T* raw = zs + kTileChunk * DP;
+    T* low_base = reinterpret_cast<T*>(smem_raw) + size_t(WPB) * ForwardSmem<T, Sh::D>::PER_WARP;
 
     // which path, which warp of it, which copy of the lower levels
     uint64_t b;
@@ -317,7 +378,7 @@ tile_forward_log_kernel(PathView<T> pv, T* __restrict__ out, uint64_t batch, uin
     T* low = low_base + size_t(slot < PPC ? slot : 0) * LOW;
 
     TileState<T, Sh> st;
-    if (valid) tile_sweep_forward<T, Sh, FLAGS>(st, pv, pv.base + b * pv.path_stride, 0, pv.steps, zs, ix, lane);
+    if (valid) tile_sweep_forward<T, Sh, FLAGS>(st, pv, pv.base + b * pv.path_stride, 0, pv.steps, zs, raw, ix, lane);
     if (active && nonfinite != nullptr && tile_nonfinite<T, Sh>(st)) *nonfinite = 1;
 
     // levels below N of the whole path, in every CTA that holds units of it
@@ -554,37 +615,25 @@ tile_backward_kernel(PathView<T> pv, const T* __restrict__ sig, const T* __restr
     // (Neither a register prefetch of the next chunk nor a one-step-late reduction pays here:
     // both were measured on B200 and cost a resident CTA per SM, 233 -> 293 ms on the C5 shape.)
     StepOperands<T, Sh> op;
-    ChunkRegs<T, Sh> pre;
-    // Plain paths: the points of a chunk come into shared memory with asynchronous copies issued one
-    // chunk ahead (no registers held across the steps), so the global-memory latency of a chunk lies
-    // under the arithmetic of the chunk before it; the increments are then differences of shared values.
-    auto fetch_points = [&](int from, int count) {         // points from .. from + count
-        const T* src = x + size_t(from) * D;
-        for (int i = lane; i < (count + 1) * D; i += 32) __pipeline_memcpy_async(raw + i, src + i, sizeof(T));
-        __pipeline_commit();
-    };
-    if constexpr (!FLAGS) {
+    // The points of a chunk come into shared memory with asynchronous copies issued one chunk ahead
+    // (no registers held across the steps), so the global-memory latency of a chunk lies under the
+    // arithmetic of the chunk before it; the increments are then built from shared values.
+    const ChunkPoints<T, FLAGS> points{pv, x, raw, lane};
+    if (j_end > j_begin) {
         const int first = max(j_begin, j_end - kTileChunk);
-        if (j_end > j_begin) fetch_points(first, j_end - first);
+        points.fetch(first, j_end - first);
     }
     for (int j1 = j_end; j1 > j_begin;) {
         const int j0 = max(j_begin, j1 - kTileChunk);
         const int cnt = j1 - j0;
         __syncwarp();
-        if constexpr (FLAGS) {
-            commit_increments<T, Sh, FLAGS, false>(zs, pre, pv, x, j0, cnt, lane);
-        } else {
-            __pipeline_wait_prior(0);
-            __syncwarp();
-            for (int i = lane; i < cnt * D; i += 32) {
-                const int step = i / D, c = i - step * D;
-                zs[step * DP + c] = raw[i + D] - raw[i];
-            }
-            __syncwarp();
-            if (j0 > j_begin) {
-                const int next = max(j_begin, j0 - kTileChunk);
-                fetch_points(next, j0 - next);
-            }
+        __pipeline_wait_prior(0);
+        __syncwarp();
+        points.template commit<D, DP>(zs, j0, cnt);
+        __syncwarp();
+        if (j0 > j_begin) {
+            const int next = max(j_begin, j0 - kTileChunk);
+            points.fetch(next, j0 - next);
         }
         __syncwarp();
         for (int step = cnt - 1; step >= 0; --step) {

@@ -52,7 +52,7 @@ void tile_forward_launch(const void* pv_, void* out, const void*, const void*, u
     using Sh = TileShape<D, N, P, G>;
     constexpr int W = kTileWarpsPerBlock;
     const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
-    const size_t smem = size_t(W) * kTileChunk * RowPad<T, D>::DP * sizeof(T);
+    const size_t smem = size_t(W) * ForwardSmem<T, D>::PER_WARP * sizeof(T);
     const unsigned grid = tile_grid(batch * uint64_t(nseg), Sh::UNITS);
     if (flags) {
         tile_set_smem(tile_forward_kernel<T, Sh, true, W>, smem);
@@ -98,7 +98,7 @@ bool tile_forward_log_launch(const void* pv_, void* out, uint64_t batch, uint32_
     constexpr int W = kTileWarpsPerBlock;
     using Lay = LogSweepShape<Sh, W>;
     const PathView<T>& pv = *static_cast<const PathView<T>*>(pv_);
-    const size_t smem = (size_t(W) * kTileChunk * RowPad<T, D>::DP + size_t(Lay::PATHS_PER_CTA) * Lay::LOW) * sizeof(T);
+    const size_t smem = (size_t(W) * ForwardSmem<T, D>::PER_WARP + size_t(Lay::PATHS_PER_CTA) * Lay::LOW) * sizeof(T);
     // deep tiles (many rows of level-N coefficients per unit) would turn the unrolled epilogue into
     // indexed register access; they take the two-step route
     constexpr bool shallow = Sh::Q <= 3 && (Sh::Q < 2 || Sh::nodes(Sh::Q - 1) <= 16);
@@ -144,7 +144,7 @@ inline int tile_occupancy_of(Kernel kernel, size_t smem) {
 template <typename T, int D, int N, int P, int G>
 int tile_forward_occupancy(bool flags) {
     using Sh = TileShape<D, N, P, G>;
-    const size_t smem = size_t(kTileWarpsPerBlock) * kTileChunk * RowPad<T, D>::DP * sizeof(T);
+    const size_t smem = size_t(kTileWarpsPerBlock) * ForwardSmem<T, D>::PER_WARP * sizeof(T);
     return flags ? tile_occupancy_of(tile_forward_kernel<T, Sh, true, kTileWarpsPerBlock>, smem)
                  : tile_occupancy_of(tile_forward_kernel<T, Sh, false, kTileWarpsPerBlock>, smem);
 }
