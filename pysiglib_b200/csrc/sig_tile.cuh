@@ -103,11 +103,9 @@ __device__ __forceinline__ void load_step(StepOperands<T, Sh>& op, const T* row,
     }
 }
 
-// Staging of the increments of augmented steps [j0, j0 + cnt) of path x into zs (row stride
-// DP), split in two so the global loads of the next chunk are in flight while the current
-// chunk is computed: prefetch() issues the loads into registers, commit() takes the
-// differences and writes them to shared memory.  With flags the increments are synthesised
-// from scattered points (increments.cuh) and everything happens in commit().
+// Register staging of the increments of steps [j0, j0 + cnt) of a plain float32 path (the forward
+// sweep): prefetch() issues the global loads of the next chunk into registers while the current chunk
+// is computed, commit() takes the differences and writes them to zs (row stride DP).
 template <typename T, typename Sh>
 struct ChunkRegs {
     static constexpr int K = (kTileChunk * Sh::D + 31) / 32;  // elements per lane and chunk
@@ -115,50 +113,32 @@ struct ChunkRegs {
     T hi[K];
 };
 
-// EAGER = false (flags, or prefetch switched off for the kernel): nothing is loaded here and
-// commit_increments() reads global memory itself.
-template <typename T, typename Sh, bool EAGER>
+template <typename T, typename Sh>
 __device__ __forceinline__ void prefetch_increments(ChunkRegs<T, Sh>& r, const T* x, int j0, int cnt, int lane) {
-    if constexpr (EAGER) {
-        constexpr int D = Sh::D;
-        const T* src = x + size_t(j0) * D;
-        const int total = cnt * D;
+    constexpr int D = Sh::D;
+    const T* src = x + size_t(j0) * D;
+    const int total = cnt * D;
 #pragma unroll
-        for (int k = 0; k < ChunkRegs<T, Sh>::K; ++k) {
-            const int i = lane + 32 * k;
-            if (i < total) {
-                r.lo[k] = src[i];
-                r.hi[k] = src[i + D];
-            }
+    for (int k = 0; k < ChunkRegs<T, Sh>::K; ++k) {
+        const int i = lane + 32 * k;
+        if (i < total) {
+            r.lo[k] = src[i];
+            r.hi[k] = src[i + D];
         }
     }
 }
 
-template <typename T, typename Sh, bool FLAGS, bool EAGER>
-__device__ __forceinline__ void commit_increments(T* zs, const ChunkRegs<T, Sh>& r, const PathView<T>& pv,
-                                                  const T* x, int j0, int cnt, int lane) {
+template <typename T, typename Sh>
+__device__ __forceinline__ void commit_increments(T* zs, const ChunkRegs<T, Sh>& r, int cnt, int lane) {
     constexpr int D = Sh::D;
     constexpr int DP = RowPad<T, D>::DP;
     const int total = cnt * D;
-    if constexpr (FLAGS) {
-        for (int i = lane; i < total; i += 32) {
-            const int step = i / D, c = i - step * D;
-            zs[step * DP + c] = pv.increment(x, j0 + step, c);
-        }
-    } else if constexpr (EAGER) {
 #pragma unroll
-        for (int k = 0; k < ChunkRegs<T, Sh>::K; ++k) {
-            const int i = lane + 32 * k;
-            if (i < total) {
-                const int step = i / D, c = i - step * D;
-                zs[step * DP + c] = r.hi[k] - r.lo[k];
-            }
-        }
-    } else {
-        const T* src = x + size_t(j0) * D;
-        for (int i = lane; i < total; i += 32) {
+    for (int k = 0; k < ChunkRegs<T, Sh>::K; ++k) {
+        const int i = lane + 32 * k;
+        if (i < total) {
             const int step = i / D, c = i - step * D;
-            zs[step * DP + c] = src[i + D] - src[i];
+            zs[step * DP + c] = r.hi[k] - r.lo[k];
         }
     }
 }
@@ -224,16 +204,16 @@ __device__ __forceinline__ void tile_sweep_forward(TileState<T, Sh>& st, const P
     constexpr bool EAGER = !FLAGS && sizeof(T) == 4;
     ChunkRegs<T, Sh> pre;
     const ChunkPoints<T, FLAGS> points{pv, x, raw, lane};
-    if constexpr (EAGER) prefetch_increments<T, Sh, EAGER>(pre, x, j_begin, min(kTileChunk, j_end - j_begin), lane);
+    if constexpr (EAGER) prefetch_increments<T, Sh>(pre, x, j_begin, min(kTileChunk, j_end - j_begin), lane);
     else if (j_end > j_begin) points.fetch(j_begin, min(kTileChunk, j_end - j_begin));
     for (int j0 = j_begin; j0 < j_end; j0 += kTileChunk) {
         const int cnt = min(kTileChunk, j_end - j0);
         __syncwarp();
         if constexpr (EAGER) {
-            commit_increments<T, Sh, FLAGS, EAGER>(zs, pre, pv, x, j0, cnt, lane);
+            commit_increments<T, Sh>(zs, pre, cnt, lane);
             __syncwarp();
             if (j0 + kTileChunk < j_end)
-                prefetch_increments<T, Sh, EAGER>(pre, x, j0 + kTileChunk, min(kTileChunk, j_end - j0 - kTileChunk), lane);
+                prefetch_increments<T, Sh>(pre, x, j0 + kTileChunk, min(kTileChunk, j_end - j0 - kTileChunk), lane);
         } else {
             __pipeline_wait_prior(0);
             __syncwarp();
