@@ -75,6 +75,8 @@ struct DenseGlobalLoader {
     const T* g;
     __device__ __forceinline__ P vec(uint32_t pos) const { return *reinterpret_cast<const P*>(g + pos); }
     __device__ __forceinline__ T one(uint32_t c) const { return g[c]; }
+    // hint: the line holding position pos will be read a few iterations from now
+    __device__ __forceinline__ void prefetch(uint32_t pos) const { asm volatile("prefetch.global.L2 [%0];" ::"l"(g + pos)); }
 };
 
 // ... and an array in shared memory with scalar-term addressing (q[1 + position], every level on a
@@ -85,6 +87,7 @@ struct SharedLoader {
     const T* q;
     __device__ __forceinline__ P vec(uint32_t pos) const { return *reinterpret_cast<const P*>(q + 1 + pos); }
     __device__ __forceinline__ T one(uint32_t c) const { return q[1 + c]; }
+    __device__ __forceinline__ void prefetch(uint32_t) const {}
 };
 
 template <typename T>
@@ -209,6 +212,9 @@ __device__ __forceinline__ void adjoint_levels_regular(const AdjointShared<T>& s
                 const uint32_t idx = (its[u] << lgw) + first;
                 v[u] = P{};
                 if (n0 + u < iters && idx < words) v[u] = load.vec(li_m - 1 + idx);
+                // the same words of the next batch: into L2 now (one lane per 128-byte line)
+                if (n0 + kBatch + u < iters && (first * sizeof(T)) % 128 == 0)
+                    load.prefetch(li_m - 1 + (order[n0 + kBatch + u] << lgw) + first);
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {

@@ -58,6 +58,7 @@ struct RankedGlobalLoader {
         const int r = rank[c];
         return r >= 0 ? g[r] : T(0);
     }
+    __device__ __forceinline__ void prefetch(uint32_t) const {}
 };
 
 template <typename T, int VEC, int NS, bool RANKED>
