@@ -219,7 +219,9 @@ __global__ void correction_forward_kernel(PathView<T> pv, CorrectionArgs<T> c, T
     const uint64_t b = batch_offset + blockIdx.x;
     const T* x = pv.base + b * pv.path_stride;
     const T* corr_path = c.ptr + b * c.batch_stride;
-    T* ws = scratch + uint64_t(blockIdx.x) * 6 * S;
+    // the six working vectors of the path: shared memory when they fit (scratch == nullptr), else global scratch
+    extern __shared__ __align__(16) unsigned char correction_smem[];
+    T* ws = scratch ? scratch + uint64_t(blockIdx.x) * 6 * S : reinterpret_cast<T*>(correction_smem);
     T *X = ws, *powers = ws + S, *E = ws + 3 * uint64_t(S), *cur = ws + 4 * uint64_t(S), *nxt = ws + 5 * uint64_t(S);
 
     for (int step = 0; step < pv.steps; ++step) {
@@ -263,7 +265,8 @@ __global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, 
     const T* x = pv.base + b * pv.path_stride;
     const T* corr_path = c.ptr + b * c.batch_stride;
     const uint64_t npow = N > 3 ? N - 1 : 2;
-    T* ws = scratch + uint64_t(blockIdx.x) * backward_vectors(N) * S;
+    // working vectors: behind g / g_next in shared memory when they fit (scratch == nullptr), else global scratch
+    T* ws = scratch ? scratch + uint64_t(blockIdx.x) * backward_vectors(N) * S : g + ((2 * lv.dim + 3) & ~3u);
     T* X = ws;
     T* powers = ws + S;                      // P_2 .. P_N
     T* E = powers + npow * S;
@@ -338,6 +341,7 @@ __global__ void correction_backward_kernel(PathView<T> pv, CorrectionArgs<T> c, 
 }
 
 constexpr uint64_t kScratchBudget = 1ull << 30;  // bytes of per-path working vectors held at once
+constexpr uint64_t kCorrectionSharedBytes = 96 * 1024;  // working vectors of one path up to this size live in shared memory
 
 template <typename T>
 CorrectionArgs<T> make_args(const CorrectionView<T>& c, uint64_t data_dim) {
@@ -456,13 +460,19 @@ void correction_forward_on_device(const T* path, T* out, const SigShape& s, T en
     const Levels lv = checked_levels(s.dim, s.degree, "signature_cuda (correction)");
     const PathView<T> pv = make_path_view<T>(path, s.data_dim, s.data_len, s.time_aug, false, end_time);
     const uint64_t per_path = 6 * lv.total() * sizeof(T);
+    // small signatures keep the working vectors of a path in shared memory (every phase of a segment
+    // then waits on shared-memory instead of L2 round trips); larger ones use pooled global scratch
+    const bool in_shared = per_path <= kCorrectionSharedBytes;
+    if (in_shared && per_path > 48 * 1024)
+        SIG_CUDA_CHECK(cudaFuncSetAttribute(correction_forward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            int(per_path)));
     const uint64_t chunk = std::max<uint64_t>(1, std::min<uint64_t>(std::min<uint64_t>(s.batch, 0x7fffffffull),
-                                                                   kScratchBudget / std::max<uint64_t>(per_path, 1)));
-    Scratch ws(chunk * per_path, stream);
+                                                                   in_shared ? s.batch : kScratchBudget / std::max<uint64_t>(per_path, 1)));
+    Scratch ws(in_shared ? 0 : chunk * per_path, stream);
     for (uint64_t b0 = 0; b0 < s.batch; b0 += chunk) {
         const uint64_t count = std::min(chunk, s.batch - b0);
-        correction_forward_kernel<T><<<static_cast<unsigned>(count), kThreads, 0, stream>>>(
-            pv, make_args(c, s.data_dim), out, s.stride, s.scalar_term, ws.as<T>(), lv, b0);
+        correction_forward_kernel<T><<<static_cast<unsigned>(count), kThreads, in_shared ? per_path : 0, stream>>>(
+            pv, make_args(c, s.data_dim), out, s.stride, s.scalar_term, in_shared ? nullptr : ws.as<T>(), lv, b0);
         check_launch("corrected signature kernel");
     }
 }
@@ -472,16 +482,22 @@ void correction_backward_on_device(const T* path, T* out, const T* sig_derivs, c
                                    T end_time, const CorrectionView<T>& c, cudaStream_t stream) {
     const Levels lv = checked_levels(s.dim, s.degree, "sig_backprop_cuda (correction)");
     const PathView<T> pv = make_path_view<T>(path, s.data_dim, s.data_len, s.time_aug, false, end_time);
-    const size_t smem = 2 * s.dim * sizeof(T);
-    if (smem > 48 * 1024) throw std::invalid_argument("sig_backprop_cuda (correction): dimension too large");
+    const size_t g_bytes = ((2 * s.dim + 3) & ~3ull) * sizeof(T);
+    if (g_bytes > 48 * 1024) throw std::invalid_argument("sig_backprop_cuda (correction): dimension too large");
     const uint64_t per_path = backward_vectors(lv.degree) * lv.total() * sizeof(T);
+    const bool in_shared = per_path + g_bytes <= kCorrectionSharedBytes;
+    const size_t smem = g_bytes + (in_shared ? per_path : 0);
+    if (smem > 48 * 1024)
+        SIG_CUDA_CHECK(cudaFuncSetAttribute(correction_backward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            int(smem)));
     const uint64_t chunk = std::max<uint64_t>(1, std::min<uint64_t>(std::min<uint64_t>(s.batch, 0x7fffffffull),
-                                                                   kScratchBudget / std::max<uint64_t>(per_path, 1)));
-    Scratch ws(chunk * per_path, stream);
+                                                                   in_shared ? s.batch : kScratchBudget / std::max<uint64_t>(per_path, 1)));
+    Scratch ws(in_shared ? 0 : chunk * per_path, stream);
     for (uint64_t b0 = 0; b0 < s.batch; b0 += chunk) {
         const uint64_t count = std::min(chunk, s.batch - b0);
         correction_backward_kernel<T><<<static_cast<unsigned>(count), kThreads, smem, stream>>>(
-            pv, make_args(c, s.data_dim), sig, sig_derivs, s.stride, s.scalar_term, out, ws.as<T>(), lv, b0);
+            pv, make_args(c, s.data_dim), sig, sig_derivs, s.stride, s.scalar_term, out, in_shared ? nullptr : ws.as<T>(), lv,
+            b0);
         check_launch("corrected signature backward kernel");
     }
 }
