@@ -246,6 +246,117 @@ __global__ void correction_forward_kernel(PathView<T> pv, CorrectionArgs<T> c, T
     for (uint32_t j = threadIdx.x; j < S; j += blockDim.x) o[j] = cur[j];
 }
 
+// The splits of the coefficients a thread owns, decoded once: coefficient j = threadIdx.x + k * blockDim.x
+// (k < K) of level t is the word u v for every left length 1 .. t-1, and a product needs A[off[left] + u]
+// and B[off[t-left] + v].  The per-coefficient formulas of algebra_math.h decode these with two integer
+// divisions per term and phase; for signatures of at most K * blockDim.x coefficients a thread keeps
+// the index pairs of its coefficients in registers instead and every phase is loads and FMAs only.
+template <int K, int NS>
+struct SplitCache {
+    uint32_t level[K];          // 0: slot unused
+    uint32_t ia[K][NS];         // [left - 1]
+    uint32_t ib[K][NS];
+
+    __device__ void build(const Levels& lv) {
+        const uint32_t S = lv.total();
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const uint32_t j = threadIdx.x + k * blockDim.x;
+            level[k] = 0;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) ia[k][i] = ib[k][i] = 0;
+            if (j < S) {
+                const uint32_t t = lv.level_of(j), w = j - lv.off[t];
+                level[k] = t;
+                uint32_t right_size = lv.dim;   // d^(t - left), from left = t - 1 down
+#pragma unroll
+                for (int i = NS - 1; i >= 0; --i) {
+                    const uint32_t left = i + 1;
+                    if (left <= t - 1) {
+                        const uint32_t u = w / right_size, v = w - u * right_size;
+                        ia[k][i] = lv.off[left] + u;
+                        ib[k][i] = lv.off[t - left] + v;
+                        right_size *= lv.dim;
+                    }
+                }
+            }
+        }
+    }
+};
+
+// The forward sweep of correction_forward_kernel with the cached splits; same sums in the same order.
+// Requires lv.total() <= K * blockDim.x and lv.degree - 1 <= NS; working vectors in shared memory.
+template <typename T, int K, int NS>
+__global__ void correction_forward_cached_kernel(PathView<T> pv, CorrectionArgs<T> c, T* __restrict__ out,
+                                                 uint64_t out_stride, bool scalar_term, Levels lv,
+                                                 uint64_t batch_offset) {
+    extern __shared__ __align__(16) unsigned char correction_smem[];
+    const uint32_t S = lv.total(), N = lv.degree, nt = blockDim.x;
+    const uint64_t b = batch_offset + blockIdx.x;
+    const T* x = pv.base + b * pv.path_stride;
+    const T* corr_path = c.ptr + b * c.batch_stride;
+    T* ws = reinterpret_cast<T*>(correction_smem);
+    T *X = ws, *powers = ws + S, *E = ws + 3 * S, *cur = ws + 4 * S, *nxt = ws + 5 * S;
+    SplitCache<K, NS> sp;
+    sp.build(lv);
+
+    for (int step = 0; step < pv.steps; ++step) {
+        build_segment_log(X, pv, x, step, c, corr_path, lv);
+        // E = exp(X) = X + sum_n P_n, P_n = X (x) P_{n-1} / n on levels >= n
+#pragma unroll
+        for (int k = 0; k < K; ++k)
+            if (sp.level[k]) E[threadIdx.x + k * nt] = X[threadIdx.x + k * nt];
+        const T* prev = X;
+        for (uint32_t n = 2; n <= N; ++n) {
+            T* pw = powers + uint64_t(n & 1) * S;
+            const T inv_n = T(1) / static_cast<T>(n);
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const uint32_t t = sp.level[k];
+                if (t) {
+                    T acc = T(0);
+                    if (t >= n) {
+#pragma unroll
+                        for (int i = 0; i < NS; ++i)          // left = 1 .. t - (n - 1)
+                            if (uint32_t(i) + n <= t) acc = alg_fma(prev[sp.ib[k][i]], X[sp.ia[k][i]] * inv_n, acc);
+                    }
+                    const uint32_t j = threadIdx.x + k * nt;
+                    pw[j] = acc;
+                    E[j] += acc;
+                }
+            }
+            __syncthreads();
+            prev = pw;
+        }
+        __syncthreads();
+        // running signature times exp(X)
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const uint32_t t = sp.level[k];
+            if (t) {
+                const uint32_t j = threadIdx.x + k * nt;
+                if (step == 0) {
+                    nxt[j] = E[j];
+                } else {
+                    T acc = cur[j];
+#pragma unroll
+                    for (int i = NS - 1; i >= 0; --i)          // left = t - 1 .. 1
+                        if (uint32_t(i) + 1 < t) acc = alg_fma(E[sp.ib[k][i]], cur[sp.ia[k][i]], acc);
+                    nxt[j] = acc + E[j];
+                }
+            }
+        }
+        __syncthreads();
+        T* tmp = cur; cur = nxt; nxt = tmp;
+    }
+    T* o = out + b * out_stride;
+    if (scalar_term) {
+        if (threadIdx.x == 0) o[0] = T(1);
+        ++o;
+    }
+    for (uint32_t j = threadIdx.x; j < S; j += nt) o[j] = cur[j];
+}
+
 // Buffers per path: X, P_2..P_N (at least 2), E, Einv, S x2, dS x2, dE, dP x2.
 __host__ __device__ inline uint64_t backward_vectors(uint32_t degree) {
     return 10 + (degree > 3 ? degree - 1 : 2);
@@ -463,6 +574,21 @@ void correction_forward_on_device(const T* path, T* out, const SigShape& s, T en
     // small signatures keep the working vectors of a path in shared memory (every phase of a segment
     // then waits on shared-memory instead of L2 round trips); larger ones use pooled global scratch
     const bool in_shared = per_path <= kCorrectionSharedBytes;
+    // small signatures: every thread keeps the splits of its (at most four) coefficients in registers
+    constexpr int kSplits = 5;
+    if (in_shared && per_path <= 48 * 1024 && lv.total() <= 4 * kThreads && lv.degree >= 1 && lv.degree - 1 <= kSplits) {
+        for (uint64_t b0 = 0; b0 < s.batch; b0 += 0x7fffffffull) {
+            const uint64_t count = std::min<uint64_t>(0x7fffffffull, s.batch - b0);
+            if (lv.total() <= 2 * kThreads)
+                correction_forward_cached_kernel<T, 2, kSplits><<<static_cast<unsigned>(count), kThreads, per_path, stream>>>(
+                    pv, make_args(c, s.data_dim), out, s.stride, s.scalar_term, lv, b0);
+            else
+                correction_forward_cached_kernel<T, 4, kSplits><<<static_cast<unsigned>(count), kThreads, per_path, stream>>>(
+                    pv, make_args(c, s.data_dim), out, s.stride, s.scalar_term, lv, b0);
+            check_launch("corrected signature kernel");
+        }
+        return;
+    }
     if (in_shared && per_path > 48 * 1024)
         SIG_CUDA_CHECK(cudaFuncSetAttribute(correction_forward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             int(per_path)));
