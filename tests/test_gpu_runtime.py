@@ -132,7 +132,7 @@ def test_every_compiled_variant_of_a_shape_agrees_with_the_oracle(d, N, dtype):
     dpath = torch.tensor(path, device="cuda")
     try:
         for P, G in fwd:
-            for segments in (1, 2):
+            for segments in (1, 2, 3, 5):   # the join of 3 and 5 segments runs several rounds of the chain kernel
                 load_cusig.set_forced_plan(False, P, G, segments)
                 plan = load_cusig.describe_plan(B, d, L, N, dtype=name)
                 assert "P=%d,G=%d" % (P, G) in plan and "segments=%d" % segments in plan, plan
