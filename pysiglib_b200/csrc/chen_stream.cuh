@@ -73,6 +73,8 @@ template <typename T, int VEC>
 struct DenseGlobalLoader {
     using P = typename Pack<T, VEC>::type;
     const T* g;
+    static constexpr bool kTwoPhase = false;
+    struct Handle {};
     __device__ __forceinline__ P vec(uint32_t pos) const { return *reinterpret_cast<const P*>(g + pos); }
     __device__ __forceinline__ T one(uint32_t c) const { return g[c]; }
     // hint: the line holding position pos will be read a few iterations from now
@@ -85,6 +87,8 @@ template <typename T, int VEC>
 struct SharedLoader {
     using P = typename Pack<T, VEC>::type;
     const T* q;
+    static constexpr bool kTwoPhase = false;
+    struct Handle {};
     __device__ __forceinline__ P vec(uint32_t pos) const { return *reinterpret_cast<const P*>(q + 1 + pos); }
     __device__ __forceinline__ T one(uint32_t c) const { return q[1 + c]; }
     __device__ __forceinline__ void prefetch(uint32_t) const {}
@@ -203,6 +207,15 @@ __device__ __forceinline__ void adjoint_levels_regular(const AdjointShared<T>& s
                 acc[q][k] = T(0);
             }
         };
+        // loaders that read through an index table issue the table reads one batch ahead
+        typename Loader::Handle ahead[kBatch];
+        if constexpr (Loader::kTwoPhase) {
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const uint32_t idx = ((uint32_t(u) < iters ? order[u] : 0u) << lgw) + first;
+                ahead[u] = load.issue(li_m - 1 + (idx < words ? idx : 0u));
+            }
+        }
         for (uint32_t n0 = 0; n0 < iters; n0 += kBatch) {
             P v[kBatch];
             uint32_t its[kBatch];
@@ -211,10 +224,22 @@ __device__ __forceinline__ void adjoint_levels_regular(const AdjointShared<T>& s
                 its[u] = n0 + u < iters ? order[n0 + u] : 0u;
                 const uint32_t idx = (its[u] << lgw) + first;
                 v[u] = P{};
-                if (n0 + u < iters && idx < words) v[u] = load.vec(li_m - 1 + idx);
-                // the same words of the next batch: into L2 now (one lane per 128-byte line)
-                if (n0 + kBatch + u < iters && (first * sizeof(T)) % 128 == 0)
-                    load.prefetch(li_m - 1 + (order[n0 + kBatch + u] << lgw) + first);
+                if constexpr (Loader::kTwoPhase) {
+                    if (n0 + u < iters && idx < words) v[u] = load.finish(ahead[u]);
+                } else {
+                    if (n0 + u < iters && idx < words) v[u] = load.vec(li_m - 1 + idx);
+                    // the same words of the next batch: into L2 now (one lane per 128-byte line)
+                    if (n0 + kBatch + u < iters && (first * sizeof(T)) % 128 == 0)
+                        load.prefetch(li_m - 1 + (order[n0 + kBatch + u] << lgw) + first);
+                }
+            }
+            if constexpr (Loader::kTwoPhase) {
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const uint32_t nn = n0 + kBatch + u;
+                    const uint32_t idx = ((nn < iters ? order[nn] : 0u) << lgw) + first;
+                    ahead[u] = load.issue(li_m - 1 + (idx < words ? idx : 0u));
+                }
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {

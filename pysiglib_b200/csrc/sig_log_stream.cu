@@ -46,14 +46,22 @@ struct RankedGlobalLoader {
     using P = typename Pack<T, VEC>::type;
     const T* g;
     const int32_t* rank;
-    __device__ __forceinline__ P vec(uint32_t pos) const {
+    // two phases: the ranks of a vector are read one batch of iterations before the coordinates they
+    // point to, so the two dependent memory round trips of a vector do not add up inside one batch
+    static constexpr bool kTwoPhase = true;
+    using Handle = typename IntPack<VEC>::type;
+    __device__ __forceinline__ Handle issue(uint32_t pos) const {
+        return *reinterpret_cast<const Handle*>(rank + pos);
+    }
+    __device__ __forceinline__ P finish(const Handle& h) const {
         int r[VEC];
-        unpack_int(*reinterpret_cast<const typename IntPack<VEC>::type*>(rank + pos), r);
+        unpack_int(h, r);
         T out[VEC];
 #pragma unroll
         for (int k = 0; k < VEC; ++k) out[k] = r[k] >= 0 ? g[r[k]] : T(0);
         return make_pack(out);
     }
+    __device__ __forceinline__ P vec(uint32_t pos) const { return finish(issue(pos)); }
     __device__ __forceinline__ T one(uint32_t c) const {
         const int r = rank[c];
         return r >= 0 ? g[r] : T(0);
@@ -64,8 +72,8 @@ struct RankedGlobalLoader {
 template <typename T, int VEC, int NS, bool RANKED>
 __global__ void __launch_bounds__(kAdjointThreads, NS <= 3 ? kAdjointCtas : 1)
 log_adjoint_cta_kernel(const T* __restrict__ x, uint64_t x_stride, const T* __restrict__ g, uint64_t g_stride,
-                       const int32_t* __restrict__ rank, T* __restrict__ dsig, uint64_t dsig_stride, bool zero_scalar,
-                       uint64_t batch, int N, uint32_t d, int lgd, LevelIndex lev) {
+                       uint32_t g_len, const int32_t* __restrict__ rank, T* __restrict__ dsig, uint64_t dsig_stride,
+                       bool zero_scalar, uint64_t batch, int N, uint32_t d, int lgd, LevelIndex lev) {
     extern __shared__ __align__(16) unsigned char log_smem[];
     __shared__ uint32_t li[kMaxDegree + 2];
     __shared__ uint32_t ord_off[kMaxDegree + 2];
@@ -108,6 +116,25 @@ log_adjoint_cta_kernel(const T* __restrict__ x, uint64_t x_stride, const T* __re
     for (uint64_t b = blockIdx.x; b < batch; b += gridDim.x) {
         __syncthreads();
         const T* xb = x + b * x_stride;
+        // What this CTA reads in scattered order or right at the start of a signature (the coordinate row
+        // behind the rank table, a few tens of KB, and the levels below N of the signature) is pulled into
+        // L2 one signature ahead, one 128-byte line per thread and round.
+        {
+            constexpr uint32_t kLine = 128 / sizeof(T);
+            auto pull = [&](uint64_t which) {
+                if (which >= batch) return;
+                if constexpr (RANKED) {
+                    const T* gb = g + which * g_stride;
+                    for (uint32_t i = tid * kLine; i < g_len; i += nt * kLine)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(gb + i));
+                }
+                const T* xn = x + which * x_stride;
+                for (uint32_t i = tid * kLine; i < low_count; i += nt * kLine)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(xn + i));
+            };
+            if (b == blockIdx.x) pull(b);
+            pull(b + gridDim.x);
+        }
         for (uint32_t j = tid; j < low_count; j += nt) nx[1 + j] = -xb[j];
         for (uint32_t j = tid; j < li[N]; j += nt) ds[j] = q0[j] = T(0);
         __syncthreads();
@@ -303,6 +330,8 @@ template <typename T>
 bool launch_log_adjoint_streamed(const T* x, uint64_t x_stride, const T* g, uint64_t g_stride, const int32_t* rank,
                                  T* dsig, uint64_t dsig_stride, bool zero_scalar, uint64_t batch, uint64_t dim,
                                  uint64_t degree, cudaStream_t stream) {
+    // coordinates per signature when g is indexed through the rank table (its stride is their count)
+    const uint32_t g_len = static_cast<uint32_t>(std::min<uint64_t>(g_stride, 0xffffffffull));
     if (degree < 2 || degree - 1 > uint64_t(kChenSplits) || dim < 2 || dim > uint64_t(kAdjointThreads) || (dim & (dim - 1)) != 0)
         return false;
     const int sms = device_context(current_device()).sm_count;
@@ -330,7 +359,7 @@ bool launch_log_adjoint_streamed(const T* x, uint64_t x_stride, const T* g, uint
         const unsigned grid = static_cast<unsigned>(std::min<uint64_t>(batch, uint64_t(sms) * per_sm));
         if (smem > 48 * 1024)
             SIG_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        kernel<<<grid, kAdjointThreads, smem, stream>>>(x, x_stride, g, g_stride, rank, dsig, dsig_stride, zero_scalar, batch,
+        kernel<<<grid, kAdjointThreads, smem, stream>>>(x, x_stride, g, g_stride, g_len, rank, dsig, dsig_stride, zero_scalar, batch,
                                                      static_cast<int>(degree), static_cast<uint32_t>(dim), lgd, lev);
         SIG_CUDA_CHECK(cudaGetLastError());
         count_launch();
