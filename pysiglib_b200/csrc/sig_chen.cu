@@ -107,6 +107,13 @@ chen_product_cta_kernel(const T* __restrict__ A, uint64_t a_stride, const T* __r
         const T rn = T(1) / T(N);
         for (uint32_t idx = tid * VEC; idx < top; idx += nt * VEC) {
             T acc[VEC];
+            // two streamed factors: the lines this thread's group reads two iterations from now go into L2
+            // (one lane per 128 bytes).  Measured on B200, d = 16, degree 4: 0.83 ms without, 0.69 / 0.675 /
+            // 0.69 / 0.78 ms at distances 1 / 2 / 3 / 6; with one generated factor the hint costs 2 %.
+            if (a_top && b_top && (tid * VEC * sizeof(T)) % 128 == 0 && idx + 2 * nt * VEC < top) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(a_top + idx + 2 * nt * VEC));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(b_top + idx + 2 * nt * VEC));
+            }
             const uint32_t q = idx / d, c0 = idx - q * d;      // prefix of length N-1, first last letter
             if (a_top) {
                 const P va = *reinterpret_cast<const P*>(a_top + idx);
