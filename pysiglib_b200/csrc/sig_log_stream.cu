@@ -256,25 +256,42 @@ log_forward_cta_kernel(const T* __restrict__ x, uint64_t x_stride, T* __restrict
         const T* nr2 = next;                       // -R_2 on levels 1 .. N-1
         T* ob = out + b * out_stride;
         if (zero_scalar && tid == 0) ob[-1] = T(0);
-        for (uint32_t i = tid; i < count; i += nt) {
-            const uint32_t p = lyndon ? lyndon[i] : i;
-            uint32_t t = 1;
-            while (p + 1 >= li[t + 1]) ++t;
-            const uint32_t idx = p + 1 - li[t];
-            T value = xb[p];
-            // y = x - x (x) R_2 = x - (-x) (x) (-R_2)
-            if (lgd >= 0) {                          // power-of-two dimension: shifts instead of divisions
-                for (uint32_t s = t - 1; s >= 1; --s) {
-                    const uint32_t sh = (t - s) * uint32_t(lgd);
-                    value = chen_fma(-nx[li[s] + (idx >> sh)], nr2[li[t - s] + (idx & ((1u << sh) - 1u))], value);
-                }
-            } else {
-                for (uint32_t s = t - 1; s >= 1; --s) {
-                    const uint32_t left = idx / pw[t - s];
-                    value = chen_fma(-nx[li[s] + left], nr2[li[t - s] + idx - left * pw[t - s]], value);
-                }
+        // kOutputs coordinates per thread and round: their position reads and then their (scattered) value
+        // reads are issued together, so a round waits out one memory latency of each kind instead of kOutputs
+        constexpr int kOutputs = 4;
+        for (uint32_t i0 = tid; i0 < count; i0 += kOutputs * nt) {
+            uint32_t pos[kOutputs];
+            T val[kOutputs];
+#pragma unroll
+            for (int k = 0; k < kOutputs; ++k) {
+                const uint32_t i = i0 + k * nt;
+                pos[k] = i < count ? (lyndon ? lyndon[i] : i) : 0u;
             }
-            ob[i] = value;
+#pragma unroll
+            for (int k = 0; k < kOutputs; ++k) val[k] = xb[pos[k]];
+#pragma unroll
+            for (int k = 0; k < kOutputs; ++k) {
+                const uint32_t i = i0 + k * nt;
+                if (i >= count) break;
+                const uint32_t p = pos[k];
+                uint32_t t = 1;
+                while (p + 1 >= li[t + 1]) ++t;
+                const uint32_t idx = p + 1 - li[t];
+                T value = val[k];
+                // y = x - x (x) R_2 = x - (-x) (x) (-R_2)
+                if (lgd >= 0) {                          // power-of-two dimension: shifts instead of divisions
+                    for (uint32_t s = t - 1; s >= 1; --s) {
+                        const uint32_t sh = (t - s) * uint32_t(lgd);
+                        value = chen_fma(-nx[li[s] + (idx >> sh)], nr2[li[t - s] + (idx & ((1u << sh) - 1u))], value);
+                    }
+                } else {
+                    for (uint32_t s = t - 1; s >= 1; --s) {
+                        const uint32_t left = idx / pw[t - s];
+                        value = chen_fma(-nx[li[s] + left], nr2[li[t - s] + idx - left * pw[t - s]], value);
+                    }
+                }
+                ob[i] = value;
+            }
         }
     }
 }
